@@ -1,0 +1,57 @@
+"""Runtime knobs of the engine (not of the architecture).
+
+Names and meanings follow ``emberserve/config.py:258-312`` where the reference has
+them: ``block_size`` (tokens per cache page, 16), ``num_gpu_blocks`` (pages; None =
+derive from free memory), ``gpu_memory_utilization`` (0.90), ``max_num_seqs`` (256),
+``max_num_batched_tokens`` (token budget of a step, 8192), ``max_model_len`` (4096),
+``enable_chunked_prefill``, ``seed``.  The device is always one CUDA GPU.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+_DTYPES = {
+    "float32": torch.float32, "fp32": torch.float32,
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+}
+
+
+def dtype_from_str(name: str) -> torch.dtype:
+    """``float32`` (the true 32-bit path) or ``bfloat16`` (the serving path)."""
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {name!r}; choose float32 or bfloat16") from None
+
+
+@dataclass
+class EngineConfig:
+    model_dir: str | None = None
+    device: str = "cuda:0"
+    dtype: torch.dtype = torch.bfloat16
+    block_size: int = 16
+    num_gpu_blocks: int | None = None
+    gpu_memory_utilization: float = 0.90
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 4096
+    enable_chunked_prefill: bool = True
+    # Replay pure-decode steps from CUDA graphs (one per batch-size bucket).
+    enable_cuda_graphs: bool = True
+    seed: int = 0
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if isinstance(self.dtype, str):
+            self.dtype = dtype_from_str(self.dtype)
+        if self.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"unsupported dtype {self.dtype}; choose float32 or bfloat16")
+        if self.block_size <= 0:
+            raise ValueError("block_size must be positive")
+        if self.max_num_seqs <= 0 or self.max_num_batched_tokens <= 0 or self.max_model_len <= 1:
+            raise ValueError("max_num_seqs, max_num_batched_tokens and max_model_len must be positive")
+        if not 0.0 < self.gpu_memory_utilization <= 1.0:
+            raise ValueError("gpu_memory_utilization must be in (0, 1]")

@@ -1,0 +1,247 @@
+// Row-wise kernels of the decoder: embedding gather, residual add + RMSNorm, SiLU-gate,
+// rotary table, and rotary encoding fused with the write of keys and values into the
+// paged cache.  All arithmetic is 32-bit; the storage type T is float (the true 32-bit
+// path) or bfloat16 (the serving path).
+//
+// Formulas (reference, by file within emberserve):
+//   RMSNorm            model/ops.py:51-55    y = w * cast(x * rsqrt(mean(x^2) + eps))
+//   residual + norm    model/ops.py:58-63    residual += x, then RMSNorm(residual)
+//   rotary (NeoX)      model/ops.py:66-81    o1 = x1*c - x2*s ; o2 = x2*c + x1*s
+//   rotary table       model/rope.py:68-82   angle = pos * inv_freq[i]  (float32)
+//   SiLU gate          model/ops.py:84-87    silu(gate) * up
+//   cache write        kv/cache.py:54-61     slot = page * page_size + pos % page_size
+// The residual stream is kept in 32 bits here (the reference rounds it to the
+// activation type after every add); the norm's output is rounded to T before the
+// multiplication by the weight, as the reference does.
+#include "common.cuh"
+
+namespace ems {
+
+// ---------------------------------------------------------------------------------------
+// embedding: residual[n, :] = float(table[tokens[n], :])
+
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                 float* __restrict__ residual, int H) {
+    const size_t n = blockIdx.x;
+    const T* src = table + (size_t)tokens[n] * H;
+    float* dst = residual + n * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+// ---------------------------------------------------------------------------------------
+// residual add + RMSNorm.  One block per output row.  Each thread touches the same
+// columns in both passes, so it re-reads only what it wrote itself.
+
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* residual,
+                                   const void* __restrict__ weight, int w_dtype,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H,
+                                   float eps, int write_residual) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : r;
+    float* res = residual + src * H;
+    const T* dl = delta ? delta + src * H : nullptr;
+    const bool store = dl && write_residual;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float s = res[i];
+        if (dl) s += to_f32<T>(dl[i]);
+        if (store) res[i] = s;
+        ss += s * s;
+    }
+    const float total = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+    T* o = out + r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float s = res[i];
+        if (dl && !store) s += to_f32<T>(dl[i]);
+        const float y = round_to<T>(s * rstd);
+        o[i] = from_f32<T>(y * load_any(weight, w_dtype, i));
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    const size_t n = blockIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const float g = to_f32<T>(gate_up[n * 2 * I + i]);
+    const float u = to_f32<T>(gate_up[n * 2 * I + I + i]);
+    const float act = g / (1.0f + expf(-g));
+    out[n * I + i] = from_f32<T>(act * u);
+}
+
+// ---------------------------------------------------------------------------------------
+// table[pos, i, 0] = cos(pos * inv_freq[i]); table[pos, i, 1] = sin(...)
+
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ table,
+                                  int max_pos, int half) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)max_pos * half) return;
+    const int pos = (int)(idx / half), i = (int)(idx % half);
+    const float angle = (float)pos * inv_freq[i];
+    table[2 * idx] = cosf(angle);
+    table[2 * idx + 1] = sinf(angle);
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotary encoding of q (in place) and k, and the write of k and v into the cache pages.
+// qkv row: [q: nh*D | k: nkv*D | v: nkv*D].  Dimension i < rot/2 pairs with i + rot/2;
+// dimensions >= rot are copied.  Cache layout: [page, kv_head, slot_in_page, D].
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int nh, int nkv, int D,
+                                     const int* __restrict__ positions,
+                                     const int* __restrict__ row_of_token,
+                                     const float* __restrict__ table, int rot,
+                                     T* __restrict__ kcache, T* __restrict__ vcache,
+                                     const int* __restrict__ block_tables, int bt_stride,
+                                     int page_size, int write_kv) {
+    const size_t n = blockIdx.x;
+    const int pos = positions[n];
+    const int half = rot / 2;
+    T* row = qkv + n * (size_t)(nh + 2 * nkv) * D;
+    const float* cs = table ? table + (size_t)pos * half * 2 : nullptr;
+
+    // q heads, in place
+    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        T* x = row + (size_t)h * D;
+        const float c = cs[2 * i], s = cs[2 * i + 1];
+        const float x1 = to_f32<T>(x[i]), x2 = to_f32<T>(x[i + half]);
+        x[i] = from_f32<T>(x1 * c - x2 * s);
+        x[i + half] = from_f32<T>(x2 * c + x1 * s);
+    }
+    if (!write_kv) return;
+
+    const int page = block_tables[(size_t)row_of_token[n] * bt_stride + pos / page_size];
+    const int slot = pos % page_size;
+    const T* k = row + (size_t)nh * D;
+    const T* v = k + (size_t)nkv * D;
+    // rotated part of k
+    for (int idx = threadIdx.x; idx < nkv * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const T* x = k + (size_t)h * D;
+        T* dst = kcache + (((size_t)page * nkv + h) * page_size + slot) * D;
+        const float c = cs[2 * i], s = cs[2 * i + 1];
+        const float x1 = to_f32<T>(x[i]), x2 = to_f32<T>(x[i + half]);
+        dst[i] = from_f32<T>(x1 * c - x2 * s);
+        dst[i + half] = from_f32<T>(x2 * c + x1 * s);
+    }
+    // unrotated tail of k, and all of v
+    const int tail = D - rot;
+    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
+        const int h = idx / tail, i = rot + idx % tail;
+        kcache[(((size_t)page * nkv + h) * page_size + slot) * D + i] = k[(size_t)h * D + i];
+    }
+    for (int idx = threadIdx.x; idx < nkv * D; idx += blockDim.x) {
+        const int h = idx / D, i = idx % D;
+        vcache[(((size_t)page * nkv + h) * page_size + slot) * D + i] = v[idx];
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// dst[i] = float(src[i])   (logits of the bfloat16 path to 32 bits)
+
+template <typename T>
+__global__ void to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = to_f32<T>(src[i]);
+}
+
+}  // namespace ems
+
+using namespace ems;
+
+EMS_EXPORT int ems_embedding(const void* table, int dtype, const int* tokens, float* residual,
+                             int N, int H, cudaStream_t stream) {
+    if (N <= 0) return EMS_OK;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == EMS_F32)
+        embedding_kernel<float><<<N, threads, 0, stream>>>((const float*)table, tokens, residual, H);
+    else if (dtype == EMS_BF16)
+        embedding_kernel<bf16><<<N, threads, 0, stream>>>((const bf16*)table, tokens, residual, H);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+// delta may be null (first layer: the embedding is the residual).  rows may be null (all
+// rows, out row r = residual row r) or hold `num_out` residual row indices (compact out).
+EMS_EXPORT int ems_add_rmsnorm(const void* delta, float* residual, const void* weight, int w_dtype,
+                               void* out, int dtype, const int* rows, int num_out, int H, float eps,
+                               int write_residual, cudaStream_t stream) {
+    if (num_out <= 0) return EMS_OK;
+    if (w_dtype != EMS_F32 && w_dtype != EMS_BF16) return EMS_ERR_DTYPE;
+    // The block size is a function of H alone, so a row's sum never depends on the batch.
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (dtype == EMS_F32)
+        add_rmsnorm_kernel<float><<<num_out, threads, 0, stream>>>(
+            (const float*)delta, residual, weight, w_dtype, (float*)out, rows, H, eps, write_residual);
+    else if (dtype == EMS_BF16)
+        add_rmsnorm_kernel<bf16><<<num_out, threads, 0, stream>>>(
+            (const bf16*)delta, residual, weight, w_dtype, (bf16*)out, rows, H, eps, write_residual);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_silu_mul(const void* gate_up, void* out, int dtype, int N, int I,
+                            cudaStream_t stream) {
+    if (N <= 0) return EMS_OK;
+    const int threads = 256;
+    const dim3 grid(N, (I + threads - 1) / threads);
+    if (grid.y > 65535) return EMS_ERR_SHAPE;
+    if (dtype == EMS_F32)
+        silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, I);
+    else if (dtype == EMS_BF16)
+        silu_mul_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_rope_table(const float* inv_freq, float* table, int max_pos, int half,
+                              cudaStream_t stream) {
+    const size_t total = (size_t)max_pos * half;
+    if (total == 0) return EMS_OK;
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, table, max_pos, half);
+    return launch_status();
+}
+
+EMS_EXPORT int ems_rope_kv_write(void* qkv, int dtype, int N, int nh, int nkv, int D,
+                                 const int* positions, const int* row_of_token, const float* table,
+                                 int rotary_dim, void* kcache, void* vcache, const int* block_tables,
+                                 int bt_stride, int page_size, int write_kv, cudaStream_t stream) {
+    if (N <= 0) return EMS_OK;
+    if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1)) return EMS_ERR_SHAPE;
+    if (rotary_dim > 0 && table == nullptr) return EMS_ERR_SHAPE;
+    if (dtype == EMS_F32)
+        rope_kv_write_kernel<float><<<N, 128, 0, stream>>>(
+            (float*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (float*)kcache,
+            (float*)vcache, block_tables, bt_stride, page_size, write_kv);
+    else if (dtype == EMS_BF16)
+        rope_kv_write_kernel<bf16><<<N, 128, 0, stream>>>(
+            (bf16*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (bf16*)kcache,
+            (bf16*)vcache, block_tables, bt_stride, page_size, write_kv);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_to_f32(const void* src, int dtype, float* dst, long long n, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == EMS_BF16)
+        to_f32_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)src, dst, (size_t)n);
+    else if (dtype == EMS_F32)
+        to_f32_kernel<float><<<blocks, 256, 0, stream>>>((const float*)src, dst, (size_t)n);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}

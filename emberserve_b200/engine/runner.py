@@ -1,0 +1,265 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step(rows)`` takes any mix of rows: portions of prompts of any length
+beside single decoded tokens.  It runs only the tokens it is given, as one packed batch,
+against what earlier steps left in the cache, writes their keys and values there, and
+returns float32 logits at the wanted places.  It is a pure function of (weights, cache
+contents, rows): the scheduler, the replay tool and the tests all call this one function.
+
+The reference's equivalent is ``LLMEngine._plan_inputs`` / ``_materialize`` / ``_forward``
+(``emberserve/engine.py:917-1016,752-763``) and ``step_logits`` (``:883-900``): packed
+tokens, positions, block tables and logit rows, copied to the device from pinned memory.
+Here all of a step's integers travel in ONE int32 buffer, and slot numbers are not sent
+at all: the cache-write kernel derives them from the block tables.
+
+Pages are reserved by the caller through ``runner.cache`` (``admit`` / ``extend``) before
+the step; the step commits what it computed, which lets windowed groups give pages back.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from emberserve_b200.cache.manager import CacheManager, plan_groups
+from emberserve_b200.cache.storage import CacheStorage
+from emberserve_b200.config.model import ModelConfig
+from emberserve_b200.parts.base import PagedKV, StepContext
+from emberserve_b200.parts.decoder import Decoder
+from emberserve_b200.parts.linear import strict_matmul_precision
+from emberserve_b200.registry import build_decoder, load_config
+from emberserve_b200.weights.loader import init_random_on_device, load_weights
+
+# Memory kept free for everything that is not the cache when its size is derived from
+# free memory (``emberserve/engine.py:117-138``: workspace, activations, logits).
+_WORKSPACE_BYTES = 1 << 30
+_MIN_PAGES = 64
+
+
+@dataclass
+class StepRow:
+    seq_id: int
+    tokens: list[int]
+    start: int  # tokens of the request already in the cache
+    want: list[int] = field(default_factory=list)  # places among `tokens` whose logits are wanted
+
+
+class ScratchArena:
+    """Named buffers that live across steps; a request for more than a buffer holds
+    replaces it with a larger one."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self._bufs: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+        self.frozen = False  # set while CUDA graphs hold pointers into the buffers
+
+    def __call__(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= s
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < numel:
+            if self.frozen and buf is not None:
+                raise RuntimeError(f"scratch buffer {name!r} would move while graphs hold it")
+            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:numel].view(shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    def __init__(self, config: ModelConfig, decoder: Decoder, dtype: torch.dtype,
+                 device: str | torch.device = "cuda:0", page_size: int = 16,
+                 num_pages: int | None = None, num_state_slots: int = 256,
+                 gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES) -> None:
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path "
+                               f"(device={device!r}, cuda available={torch.cuda.is_available()})")
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype must be float32 or bfloat16, got {dtype}")
+        if decoder.embed is None:
+            raise RuntimeError("the decoder has no weights bound; load or initialise them first")
+        strict_matmul_precision()
+        self.config = config
+        self.decoder = decoder
+        self.dtype = dtype
+        self.page_size = page_size
+        self.vocab_size = decoder.spec.vocab_size
+        self.max_positions = decoder.spec.max_positions
+        self.groups = plan_groups(decoder.cache_entries())
+        paged = [g for g in self.groups if g.paged]
+        if num_pages is None:
+            num_pages = self._pages_from_free_memory(paged, gpu_memory_utilization, reserve_bytes)
+        self.num_pages = num_pages
+        has_state = any(not g.paged for g in self.groups)
+        self.cache = CacheManager(self.groups, num_pages, page_size,
+                                  num_state_slots if has_state else 0)
+        self.storage = CacheStorage(self.groups, [num_pages] * len(paged), page_size,
+                                    num_state_slots if has_state else 0, dtype, self.device)
+        self.scratch = ScratchArena(self.device)
+        self._meta_dev = torch.empty(1 << 12, dtype=torch.int32, device=self.device)
+        self._meta_host = [torch.empty(1 << 12, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._meta_events: list[torch.cuda.Event | None] = [None, None]
+        self._meta_turn = 0
+        self.steps_run = 0
+
+    # ---- construction ----------------------------------------------------------------------
+    @classmethod
+    def from_dir(cls, model_dir: str | os.PathLike, dtype: torch.dtype,
+                 device: str | torch.device = "cuda:0", **kw) -> "ModelRunner":
+        if not torch.cuda.is_available():
+            raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path")
+        config = load_config(model_dir)
+        decoder = build_decoder(config)
+        load_weights(decoder, model_dir, device, dtype)
+        return cls(config, decoder, dtype, device, **kw)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig, seed: int, dtype: torch.dtype,
+                    device: str | torch.device = "cuda:0", **kw) -> "ModelRunner":
+        if not torch.cuda.is_available():
+            raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path")
+        decoder = build_decoder(config)
+        init_random_on_device(decoder, seed, device, dtype)
+        return cls(config, decoder, dtype, device, **kw)
+
+    def _bytes_per_page(self, paged) -> int:
+        esize = torch.empty((), dtype=self.dtype).element_size()
+        total = 0
+        for g in paged:
+            need: PagedKV = g.need
+            total += len(g.entries) * 2 * need.num_kv_heads * self.page_size * need.head_dim * esize
+        return total
+
+    def _pages_from_free_memory(self, paged, utilization: float, reserve: int) -> int:
+        """``emberserve/engine.py:141-153``: (free * utilization - reserve) // bytes per page."""
+        if not paged:
+            return _MIN_PAGES
+        free, _ = torch.cuda.mem_get_info(self.device)
+        usable = int(free * utilization) - reserve
+        return max(_MIN_PAGES, usable // self._bytes_per_page(paged))
+
+    # ---- one step ----------------------------------------------------------------------------
+    def _check_rows(self, rows: list[StepRow]) -> None:
+        seen: set[int] = set()
+        for r in rows:
+            if r.seq_id in seen:
+                raise ValueError(f"request {r.seq_id} appears twice in one step")
+            seen.add(r.seq_id)
+            if not r.tokens:
+                raise ValueError(f"request {r.seq_id} brings no tokens")
+            if not self.cache.has_sequence(r.seq_id):
+                raise ValueError(f"request {r.seq_id} has no pages; admit it first")
+            if r.start != self.cache.committed(r.seq_id):
+                raise ValueError(f"request {r.seq_id}: step starts at {r.start} but the cache "
+                                 f"holds {self.cache.committed(r.seq_id)} tokens")
+            end = r.start + len(r.tokens)
+            if end > self.cache.num_tokens(r.seq_id):
+                raise ValueError(f"request {r.seq_id}: {end} tokens but pages for "
+                                 f"{self.cache.num_tokens(r.seq_id)}; extend it first")
+            if end > self.max_positions:
+                raise ValueError(f"request {r.seq_id}: position {end - 1} exceeds "
+                                 f"max_position_embeddings={self.max_positions}")
+            if min(r.tokens) < 0 or max(r.tokens) >= self.vocab_size:
+                raise ValueError(f"request {r.seq_id}: token id out of vocabulary "
+                                 f"(vocab_size {self.vocab_size})")
+            for w in r.want:
+                if not 0 <= w < len(r.tokens):
+                    raise ValueError(f"request {r.seq_id}: wanted place {w} outside its "
+                                     f"{len(r.tokens)} tokens")
+
+    def _pack(self, rows: list[StepRow]) -> tuple[StepContext, list[torch.Tensor], torch.Tensor | None,
+                                                  torch.Tensor, int]:
+        b = len(rows)
+        q_lens = [len(r.tokens) for r in rows]
+        starts = [r.start for r in rows]
+        n = sum(q_lens)
+        cu = np.zeros(b + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=cu[1:])
+        tokens = np.concatenate([np.asarray(r.tokens, dtype=np.int32) for r in rows])
+        positions = np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in zip(starts, q_lens)])
+        row_of = np.repeat(np.arange(b, dtype=np.int32), q_lens)
+        want = np.asarray([cu[i] + w for i, r in enumerate(rows) for w in r.want], dtype=np.int32)
+        num_want = int(want.size)
+        npaged = len(self.cache.pools)
+        tables = []
+        for k in range(npaged):
+            per_row = [self.cache.table(r.seq_id, k) for r in rows]
+            width = max(1, max(len(t) for t in per_row))
+            arr = np.zeros((b, width), dtype=np.int32)
+            for i, t in enumerate(per_row):
+                arr[i, :len(t)] = t
+            np.maximum(arr, 0, out=arr)  # pages given back (-1) are never read; keep ids valid
+            tables.append(arr)
+        slots = np.asarray([max(0, self.cache.state_slot(r.seq_id)) for r in rows], dtype=np.int32)
+
+        sections = [tokens, positions, row_of, cu, np.asarray(starts, dtype=np.int32), want, slots]
+        sections += [t.reshape(-1) for t in tables]
+        offsets, total = [], 0
+        for s in sections:
+            offsets.append(total)
+            total += _align4(int(s.size))
+        total = max(total, 4)
+        if total > self._meta_dev.numel():
+            cap = 1 << (total - 1).bit_length()
+            if self.scratch.frozen:
+                raise RuntimeError("step metadata would outgrow the buffer that graphs hold")
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._meta_events = [None, None]
+        turn = self._meta_turn
+        self._meta_turn ^= 1
+        if self._meta_events[turn] is not None:
+            self._meta_events[turn].synchronize()  # the copy that last read this buffer is done
+        host = self._meta_host[turn]
+        hv = host.numpy()
+        for off, s in zip(offsets, sections):
+            hv[off:off + s.size] = s
+        self._meta_dev[:total].copy_(host[:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._meta_events[turn] = ev
+
+        def dev(i: int) -> torch.Tensor:
+            return self._meta_dev[offsets[i]:offsets[i] + sections[i].size]
+
+        ctx = StepContext(
+            num_tokens=n, num_rows=b, dtype=self.dtype, device=self.device,
+            tokens=dev(0), positions=dev(1), row_of_token=dev(2), cu_q=dev(3), starts=dev(4),
+            q_lens=q_lens, start_list=starts, max_q_len=max(q_lens),
+            max_ctx_len=max(s + q for s, q in zip(starts, q_lens)), scratch=self.scratch)
+        bt = [dev(7 + k).view(b, tables[k].shape[1]) for k in range(npaged)]
+        return ctx, bt, dev(6), dev(5), num_want
+
+    @torch.inference_mode()
+    def step(self, rows: list[StepRow]) -> torch.Tensor:
+        """Run one step.  Returns float32 logits ``[wanted, vocab]`` in the order of the
+        rows and of each row's `want`; the tensor is scratch memory of the runner and is
+        valid until the next step."""
+        if not rows:
+            return torch.empty(0, self.vocab_size, dtype=torch.float32, device=self.device)
+        self._check_rows(rows)
+        with torch.cuda.device(self.device):
+            fresh = self.cache.take_fresh_slots()
+            if fresh:
+                self.storage.zero_slots(fresh)
+            ctx, block_tables, slots, want_rows, num_want = self._pack(rows)
+            handles = [None if call.cache is None else
+                       self.storage.handle(call.cache, call.write, block_tables, slots)
+                       for call in self.decoder.spec.order]
+            logits = self.decoder.forward(ctx, handles, want_rows, num_want)
+        for r in rows:
+            self.cache.commit(r.seq_id, r.start + len(r.tokens))
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,237 @@
+"""Python face of the hand-written CUDA kernels (``csrc/*.cu``), through ctypes.
+
+Every function here takes CUDA tensors, checks what the kernel assumes (device,
+contiguity, dtypes) and launches on the current torch stream.  There is no CPU path and
+no library fallback: a missing or unbuildable extension, a tensor that is not on the
+GPU, or a non-zero status from a launcher raises.
+
+The launchers are plain ``extern "C"`` symbols taking raw pointers, so they are
+captured by CUDA graphs like any other launch and allocate nothing themselves.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from emberserve_b200 import build
+
+_ERRORS = {
+    1: "unknown element type",
+    2: "a size this kernel does not take",
+    3: "the CUDA launch failed",
+    4: "scratch buffer missing or too small",
+    5: "pointer or stride not aligned as the kernel needs",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib_handle: ctypes.CDLL | None = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded extension; built on first use.  Raises if it cannot be had."""
+    global _lib_handle
+    if _lib_handle is None:
+        path = build.ensure_built()
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as e:  # pragma: no cover - depends on the machine
+            raise KernelError(f"cannot load the emberserve_b200 CUDA extension {path}: {e}") from e
+        _declare(lib)
+        _lib_handle = lib
+    return _lib_handle
+
+
+def library_path() -> str:
+    library()
+    return str(build.ensure_built(verbose=False))
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    P, I, L, F = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "ems_embedding": [P, I, P, P, I, I, P],
+        "ems_add_rmsnorm": [P, P, P, I, P, I, P, I, I, F, I, P],
+        "ems_silu_mul": [P, P, I, I, I, P],
+        "ems_rope_table": [P, P, I, I, P],
+        "ems_rope_kv_write": [P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, P],
+        "ems_to_f32": [P, I, P, L, P],
+        "ems_paged_attention": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I, P, L, P],
+        "ems_argmax": [P, P, I, I, P],
+        "ems_repetition_penalty": [P, I, I, P, P, P, P],
+        "ems_sample": [P, I, I, P, P, P, P, P, P, P],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+    lib.ems_paged_attention_scratch_bytes.argtypes = [I, I, I, I]
+    lib.ems_paged_attention_scratch_bytes.restype = c_longlong
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'status {code}')}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: torch.Tensor | None, name: str = "tensor") -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t.data_ptr()
+
+
+def _i32(t: torch.Tensor | None, name: str) -> int | None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+    return _ptr(t, name)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ---------------------------------------------------------------------------------------
+
+
+def embedding(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[n, :] = float32(table[tokens[n], :])"""
+    n, h = residual.shape
+    assert table.shape[1] == h and residual.dtype == torch.float32 and tokens.numel() >= n
+    _check(library().ems_embedding(_ptr(table, "table"), _dt(table), _i32(tokens, "tokens"),
+                                   _ptr(residual, "residual"), n, h, _stream()), "embedding")
+
+
+def add_rmsnorm(delta: torch.Tensor | None, residual: torch.Tensor, weight: torch.Tensor,
+                out: torch.Tensor, eps: float, rows: torch.Tensor | None = None,
+                num_rows: int | None = None) -> None:
+    """residual += delta (32-bit); out = weight * round(residual * rsqrt(mean(residual^2) + eps)).
+    With `rows`, only residual rows rows[0..num_rows) are normalised into out[0..num_rows)
+    and the residual is not written."""
+    h = residual.shape[-1]
+    assert residual.dtype == torch.float32 and weight.numel() == h and out.shape[-1] == h
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape[-1] == h
+    n_out = residual.shape[0] if rows is None else (rows.numel() if num_rows is None else num_rows)
+    if delta is not None and rows is None:
+        assert delta.shape[0] >= n_out
+    _check(library().ems_add_rmsnorm(_ptr(delta, "delta"), _ptr(residual, "residual"),
+                                     _ptr(weight, "weight"), _dt(weight), _ptr(out, "out"), _dt(out),
+                                     _i32(rows, "rows"), n_out, h, float(eps),
+                                     0 if rows is not None else 1, _stream()), "add_rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]"""
+    n, i = out.shape
+    assert gate_up.shape == (n, 2 * i) and gate_up.dtype == out.dtype
+    _check(library().ems_silu_mul(_ptr(gate_up, "gate_up"), _ptr(out, "out"), _dt(out), n, i,
+                                  _stream()), "silu_mul")
+
+
+def rope_table(inv_freq: torch.Tensor, max_pos: int) -> torch.Tensor:
+    """[max_pos, half, 2] float32 table of (cos, sin) of pos * inv_freq[i], both 32-bit."""
+    assert inv_freq.dtype == torch.float32
+    half = inv_freq.numel()
+    table = torch.empty(max_pos, half, 2, dtype=torch.float32, device=inv_freq.device)
+    _check(library().ems_rope_table(_ptr(inv_freq, "inv_freq"), _ptr(table), max_pos, half,
+                                    _stream()), "rope_table")
+    return table
+
+
+def rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                  positions: torch.Tensor, row_of_token: torch.Tensor,
+                  table: torch.Tensor | None, rotary_dim: int,
+                  kcache: torch.Tensor | None, vcache: torch.Tensor | None,
+                  block_tables: torch.Tensor | None, page_size: int, write_kv: bool = True) -> None:
+    """Rotate q (in place) and k by the table rows of `positions`; store k and v of every
+    token at its page slot.  qkv: [N, (nh + 2 nkv) D]; caches [pages, nkv, page_size, D]."""
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim
+    if write_kv:
+        assert kcache is not None and vcache is not None and block_tables is not None
+        assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype
+        assert kcache.shape[1:] == (num_kv_heads, page_size, head_dim)
+    bt_stride = block_tables.shape[1] if block_tables is not None else 0
+    _check(library().ems_rope_kv_write(
+        _ptr(qkv, "qkv"), _dt(qkv), n, num_heads, num_kv_heads, head_dim,
+        _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _ptr(table, "table"),
+        rotary_dim, _ptr(kcache, "kcache"), _ptr(vcache, "vcache"),
+        _i32(block_tables, "block_tables"), bt_stride, page_size, 1 if write_kv else 0, _stream()),
+        "rope_kv_write")
+
+
+def to_f32(src: torch.Tensor, dst: torch.Tensor) -> None:
+    assert dst.dtype == torch.float32 and dst.numel() >= src.numel()
+    _check(library().ems_to_f32(_ptr(src, "src"), _dt(src), _ptr(dst, "dst"), src.numel(), _stream()),
+           "to_f32")
+
+
+def attention_scratch_bytes(num_tokens: int, num_heads: int, head_dim: int, splits: int) -> int:
+    return int(library().ems_paged_attention_scratch_bytes(num_tokens, num_heads, head_dim, splits))
+
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                    block_tables: torch.Tensor, cu_q: torch.Tensor, starts: torch.Tensor,
+                    num_rows: int, num_tokens: int, num_heads: int, num_kv_heads: int,
+                    head_dim: int, scale: float, max_q_len: int, window: int | None = None,
+                    splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """Causal grouped-query attention of every packed query over its request's pages.
+    `q` is a [N, stride] tensor whose first nh*D columns are the queries (a view of the
+    qkv buffer is fine); `out` is [N, nh*D]."""
+    assert q.stride(1) == 1 and out.is_contiguous() and q.dtype == out.dtype == kcache.dtype
+    page_size = kcache.shape[2]
+    assert kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_paged_attention(
+        q.data_ptr(), q.stride(0), _ptr(out, "out"), _dt(out), _ptr(kcache, "kcache"),
+        _ptr(vcache, "vcache"), _i32(block_tables, "block_tables"), block_tables.shape[1], page_size,
+        _i32(cu_q, "cu_q"), _i32(starts, "starts"), num_rows, num_tokens, num_heads, num_kv_heads,
+        head_dim, int(window or 0), float(scale), max_q_len, splits,
+        _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
+        _stream()), "paged_attention")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    r, v = logits.shape
+    assert logits.dtype == torch.float32
+    _check(library().ems_argmax(_ptr(logits, "logits"), _i32(out, "out"), r, v, _stream()), "argmax")
+
+
+def repetition_penalty(logits: torch.Tensor, row_ptr: torch.Tensor, token_ids: torch.Tensor,
+                       penalty: torch.Tensor) -> None:
+    r, v = logits.shape
+    assert logits.dtype == torch.float32 and penalty.dtype == torch.float32
+    _check(library().ems_repetition_penalty(_ptr(logits, "logits"), r, v, _i32(row_ptr, "row_ptr"),
+                                            _i32(token_ids, "token_ids"), _ptr(penalty, "penalty"),
+                                            _stream()), "repetition_penalty")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """One token per row: argmax where temperature == 0, else a seeded draw."""
+    r, v = logits.shape
+    assert logits.dtype == torch.float32 and temperature.dtype == torch.float32
+    assert top_p.dtype == torch.float32 and seeds.dtype == torch.int64 and counters.dtype == torch.int64
+    _check(library().ems_sample(_ptr(logits, "logits"), r, v, _ptr(temperature, "temperature"),
+                                _i32(top_k, "top_k"), _ptr(top_p, "top_p"), _ptr(seeds, "seeds"),
+                                _ptr(counters, "counters"), _i32(out, "out"), _stream()), "sample")

@@ -1,0 +1,121 @@
+"""Grouped-query causal attention over a paged cache (the mixer of Qwen2).
+
+``qkv = x Wqkv^T + b`` with columns ``[q | k | v]`` (``emberserve/model/qwen2.py:70-78,
+93-100``), rotary encoding of q and k, write of k and v into the cache pages, causal
+softmax attention of every query over its request's keys with query head h reading KV
+head ``h // groups`` and scale ``1/sqrt(head_dim)`` (``emberserve/attn/base.py:105-128``),
+then ``o = attn Wo^T`` without bias (``qwen2.py:113-114``).  A window of W keys, if the
+spec has one, hides keys at positions ``<= p - W`` from the query at position p.
+
+The part never touches the cache manager: it gets a ``PagedKVHandle`` for the step and
+hands the block tables to the kernels (``attn/base.py:79-91`` is the same contract).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from emberserve_b200 import kernels as K
+from emberserve_b200.parts.base import (Mixer, PagedKV, PagedKVHandle, ParamSpec, Source,
+                                        StepContext, register_part)
+from emberserve_b200.parts.linear import linear
+
+# Blocks wanted in flight before keys are split among several blocks of a decode step:
+# two per SM of a B200.
+_TARGET_BLOCKS = 2 * 148
+_MAX_SPLITS = 16
+_MIN_KEYS_PER_SPLIT = 256
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    qkv_bias: bool
+    position: Any  # spec of a position encoding (rotary), or None
+    # checkpoint names of the four projections, without ".weight" / ".bias"
+    q_name: str
+    k_name: str
+    v_name: str
+    o_name: str
+    window: int | None = None
+    scale: float | None = None  # None = head_dim ** -0.5
+    kind: str = "gqa_attention"
+
+
+def decode_splits(num_rows: int, num_kv_heads: int, max_ctx: int) -> int:
+    """How many blocks share the keys of one (request, KV head) in a decode step.  A
+    function of shapes only (``emberserve/attn/paged_triton.py:259-281`` has the same idea)."""
+    blocks = max(1, num_rows * num_kv_heads)
+    want = -(-_TARGET_BLOCKS // blocks)
+    cap = max(1, max_ctx // _MIN_KEYS_PER_SPLIT)
+    return max(1, min(_MAX_SPLITS, want, cap))
+
+
+@register_part("mixer", "gqa_attention")
+class GQAttention(Mixer):
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    bqkv: torch.Tensor | None = None
+
+    def __init__(self, spec: AttentionSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if spec.head_dim % 16 or spec.head_dim > 256:
+            raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take multiples "
+                             f"of 16 up to 256")
+        self.q_size = spec.num_heads * spec.head_dim
+        self.kv_size = spec.num_kv_heads * spec.head_dim
+        self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
+        self.position = self.shared.get("position", spec.position) if spec.position is not None else None
+
+    def cache_need(self) -> PagedKV:
+        s: AttentionSpec = self.spec
+        return PagedKV(s.num_kv_heads, s.head_dim, s.window)
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: AttentionSpec = self.spec
+        q, kv = self.q_size, self.kv_size
+        rows = [(s.q_name, (0, q)), (s.k_name, (q, q + kv)), (s.v_name, (q + kv, q + 2 * kv))]
+        specs = {
+            "wqkv": ParamSpec((q + 2 * kv, s.hidden), [Source(n + ".weight", r) for n, r in rows]),
+            "wo": ParamSpec((s.hidden, q), [Source(s.o_name + ".weight")]),
+        }
+        if s.qkv_bias:
+            specs["bqkv"] = ParamSpec((q + 2 * kv,), [Source(n + ".bias", r) for n, r in rows],
+                                      init="bias")
+        return specs
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVHandle) -> torch.Tensor:
+        s: AttentionSpec = self.spec
+        n = ctx.num_tokens
+        qkv = ctx.scratch("qkv", (n, self.q_size + 2 * self.kv_size), ctx.dtype)
+        linear(x, self.wqkv, self.bqkv, qkv)
+        table, rot = (None, 0)
+        if self.position is not None:
+            r = self.position.rotary(ctx.device)
+            if r is not None:
+                table, rot = r
+        K.rope_kv_write(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions,
+                        ctx.row_of_token, table, rot, cache.k, cache.v, cache.block_tables,
+                        cache.page_size, write_kv=cache.write)
+        out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
+        splits, scratch = 1, None
+        if ctx.max_q_len == 1:
+            splits = ctx.extra.get("decode_splits") or decode_splits(
+                ctx.num_rows, s.num_kv_heads, ctx.max_ctx_len)
+            if splits > 1:
+                nbytes = K.attention_scratch_bytes(n, s.num_heads, s.head_dim, splits)
+                scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)
+        K.paged_attention(qkv, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts,
+                          ctx.num_rows, n, s.num_heads, s.num_kv_heads, s.head_dim, self.scale,
+                          ctx.max_q_len, window=cache.window, splits=splits, scratch=scratch)
+        y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
+        linear(out, self.wo, None, y)
+        return y

@@ -1,0 +1,41 @@
+"""RMSNorm fused with the residual add that precedes it.
+
+``y = weight * cast(r * rsqrt(mean(r^2) + eps))`` with ``r = residual + delta``
+(``emberserve/model/ops.py:51-63``, ``emberserve/model/qwen2.py:30-45``).  The residual
+stream is held in 32 bits; the sum and the statistics are 32-bit.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from emberserve_b200 import kernels as K
+from emberserve_b200.parts.base import Norm, ParamSpec, Source, StepContext, register_part
+
+
+@dataclass(frozen=True)
+class RMSNormSpec:
+    dim: int
+    eps: float
+    weight_name: str  # checkpoint tensor of the gain, [dim]
+    kind: str = "rmsnorm"
+
+
+@register_part("norm", "rmsnorm")
+class RMSNorm(Norm):
+    weight: torch.Tensor
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: RMSNormSpec = self.spec
+        return {"weight": ParamSpec((s.dim,), [Source(s.weight_name)], init="ones")}
+
+    def forward(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
+                rows: torch.Tensor | None = None, num_rows: int | None = None,
+                out_name: str = "normed") -> torch.Tensor:
+        s: RMSNormSpec = self.spec
+        n = residual.shape[0] if rows is None else (rows.numel() if num_rows is None else num_rows)
+        out = ctx.scratch(out_name, (n, s.dim), ctx.dtype)
+        K.add_rmsnorm(delta, residual, self.weight, out, s.eps, rows=rows, num_rows=num_rows)
+        return out
