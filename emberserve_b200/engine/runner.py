@@ -18,6 +18,7 @@ the step; the step commits what it computed, which lets windowed groups give pag
 
 from __future__ import annotations
 
+import contextlib
 import os
 from dataclasses import dataclass, field
 
@@ -78,14 +79,19 @@ def _align4(n: int) -> int:
 
 
 class ModelRunner:
+    # The product runs on a CUDA GPU only.  Tests of the host-side logic subclass the runner
+    # with this switched off and the kernels replaced by their plain references.
+    _require_cuda = True
+
     def __init__(self, config: ModelConfig, decoder: Decoder, dtype: torch.dtype,
                  device: str | torch.device = "cuda:0", page_size: int = 16,
                  num_pages: int | None = None, num_state_slots: int = 256,
                  gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES) -> None:
         self.device = torch.device(device)
-        if self.device.type != "cuda" or not torch.cuda.is_available():
+        if self._require_cuda and (self.device.type != "cuda" or not torch.cuda.is_available()):
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path "
                                f"(device={device!r}, cuda available={torch.cuda.is_available()})")
+        self._on_cuda = self.device.type == "cuda"
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"dtype must be float32 or bfloat16, got {dtype}")
         if decoder.embed is None:
@@ -109,7 +115,8 @@ class ModelRunner:
                                     num_state_slots if has_state else 0, dtype, self.device)
         self.scratch = ScratchArena(self.device)
         self._meta_dev = torch.empty(1 << 12, dtype=torch.int32, device=self.device)
-        self._meta_host = [torch.empty(1 << 12, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._meta_host = [torch.empty(1 << 12, dtype=torch.int32, pin_memory=self._on_cuda)
+                           for _ in range(2)]
         self._meta_events: list[torch.cuda.Event | None] = [None, None]
         self._meta_turn = 0
         self.steps_run = 0
@@ -118,7 +125,7 @@ class ModelRunner:
     @classmethod
     def from_dir(cls, model_dir: str | os.PathLike, dtype: torch.dtype,
                  device: str | torch.device = "cuda:0", **kw) -> "ModelRunner":
-        if not torch.cuda.is_available():
+        if cls._require_cuda and not torch.cuda.is_available():
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path")
         config = load_config(model_dir)
         decoder = build_decoder(config)
@@ -128,7 +135,7 @@ class ModelRunner:
     @classmethod
     def from_random(cls, config: ModelConfig, seed: int, dtype: torch.dtype,
                     device: str | torch.device = "cuda:0", **kw) -> "ModelRunner":
-        if not torch.cuda.is_available():
+        if cls._require_cuda and not torch.cuda.is_available():
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path")
         decoder = build_decoder(config)
         init_random_on_device(decoder, seed, device, dtype)
@@ -146,6 +153,8 @@ class ModelRunner:
         """``emberserve/engine.py:141-153``: (free * utilization - reserve) // bytes per page."""
         if not paged:
             return _MIN_PAGES
+        if not self._on_cuda:
+            return 2048  # the reference's fixed page count off the GPU (emberserve/engine.py:194-207)
         free, _ = torch.cuda.mem_get_info(self.device)
         usable = int(free * utilization) - reserve
         return max(_MIN_PAGES, usable // self._bytes_per_page(paged))
@@ -216,7 +225,8 @@ class ModelRunner:
             if self.scratch.frozen:
                 raise RuntimeError("step metadata would outgrow the buffer that graphs hold")
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._meta_host = [torch.empty(cap, dtype=torch.int32, pin_memory=self._on_cuda)
+                               for _ in range(2)]
             self._meta_events = [None, None]
         turn = self._meta_turn
         self._meta_turn ^= 1
@@ -227,9 +237,10 @@ class ModelRunner:
         for off, s in zip(offsets, sections):
             hv[off:off + s.size] = s
         self._meta_dev[:total].copy_(host[:total], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._meta_events[turn] = ev
+        if self._on_cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._meta_events[turn] = ev
 
         def dev(i: int) -> torch.Tensor:
             return self._meta_dev[offsets[i]:offsets[i] + sections[i].size]
@@ -250,7 +261,7 @@ class ModelRunner:
         if not rows:
             return torch.empty(0, self.vocab_size, dtype=torch.float32, device=self.device)
         self._check_rows(rows)
-        with torch.cuda.device(self.device):
+        with (torch.cuda.device(self.device) if self._on_cuda else contextlib.nullcontext()):
             fresh = self.cache.take_fresh_slots()
             if fresh:
                 self.storage.zero_slots(fresh)

@@ -1,0 +1,318 @@
+"""Each CUDA kernel alone against its plain restatement (kernel_refs.py), in 32-bit and in
+bfloat16, at sizes other than the engine's test models: widths and vocabularies that are
+no power of two, head sizes in steps of 16, odd group counts, several page sizes."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def K():
+    from emberserve_b200 import kernels
+
+    return kernels
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def test_extension_is_loaded_from_the_tree():
+    import os
+
+    path = K().library_path()
+    assert os.path.basename(path) == "libemberserve_b200.so"
+    with open(f"/proc/{os.getpid()}/maps") as f:
+        assert any("libemberserve_b200.so" in line for line in f)
+
+
+def test_kernels_refuse_cpu_tensors():
+    k = K()
+    with pytest.raises(k.KernelError):
+        k.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,h,v", [(1, 48, 77), (37, 3584, 1000), (5, 1000, 333)])
+def test_embedding(dtype, n, h, v):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(v, h, device=dev(), generator=g).to(dtype)
+    tokens = torch.randint(0, v, (n + 3,), device=dev(), generator=g).to(torch.int32)
+    got = torch.full((n, h), 7.0, device=dev())
+    want = torch.empty_like(got)
+    K().embedding(table, tokens, got)
+    ref.embedding(table, tokens, want)
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,h,eps", [(1, 64, 1e-6), (9, 1000, 1e-5), (33, 3584, 1e-6), (4, 5120, 3e-6)])
+@pytest.mark.parametrize("wdtype", ["same", "f32"])
+def test_add_rmsnorm(dtype, n, h, eps, wdtype):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    delta = (torch.randn(n, h, device=dev(), generator=g) * 2).to(dtype)
+    res0 = torch.randn(n, h, device=dev(), generator=g) * 3
+    w = (1 + 0.1 * torch.randn(h, device=dev(), generator=g)).to(dtype if wdtype == "same" else torch.float32)
+    for d in (delta, None):
+        res_a, res_b = res0.clone(), res0.clone()
+        out_a = torch.empty(n, h, dtype=dtype, device=dev())
+        out_b = torch.empty_like(out_a)
+        K().add_rmsnorm(d, res_a, w, out_a, eps)
+        ref.add_rmsnorm(d, res_b, w, out_b, eps)
+        assert torch.allclose(res_a, res_b, rtol=0, atol=0 if d is None else 1e-6)
+        torch.testing.assert_close(out_a.float(), out_b.float(), **tol(dtype))
+    # gathered rows: compact output, residual untouched, a row may be wanted twice
+    rows = torch.tensor([n - 1, 0, n - 1, 7][: max(1, min(4, n + 1))], device=dev(), dtype=torch.int32) % n
+    rows_buf = torch.cat([rows, torch.full((5,), 10**6, device=dev(), dtype=torch.int32)])
+    res_a = res0.clone()
+    out_a = torch.empty(rows.numel(), h, dtype=dtype, device=dev())
+    out_b = torch.empty_like(out_a)
+    K().add_rmsnorm(delta, res_a, w, out_a, eps, rows=rows_buf, num_rows=rows.numel())
+    ref.add_rmsnorm(delta, res0.clone(), w, out_b, eps, rows=rows_buf, num_rows=rows.numel())
+    assert torch.equal(res_a, res0)
+    torch.testing.assert_close(out_a.float(), out_b.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,i", [(1, 16), (7, 4864), (130, 18944), (3, 1001)])
+def test_silu_mul(dtype, n, i):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    gu = (torch.randn(n, 2 * i, device=dev(), generator=g) * 3).to(dtype)
+    got = torch.empty(n, i, dtype=dtype, device=dev())
+    want = torch.empty_like(got)
+    K().silu_mul(gu, got)
+    ref.silu_mul(gu, want)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("half,theta,max_pos", [(8, 1e4, 128), (64, 1e6, 4096), (24, 5e4, 777)])
+def test_rope_table(half, theta, max_pos):
+    from emberserve_b200.parts.rope import inv_frequencies
+
+    inv = inv_frequencies(2 * half, theta).to(dev())
+    got = K().rope_table(inv, max_pos)
+    want = ref.rope_table(inv, max_pos)
+    assert got.shape == (max_pos, half, 2)
+    # cos/sin of the same float32 angle: only the last bits of the two libraries differ
+    torch.testing.assert_close(got, want, rtol=0, atol=2e-6)
+    ang64 = torch.arange(max_pos, dtype=torch.float32)[:, None] * inv.cpu()[None, :]
+    torch.testing.assert_close(got[..., 0].cpu().double(), ang64.double().cos(), rtol=0, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot,ps", [(4, 2, 16, 16, 4), (7, 1, 48, 48, 16), (28, 4, 128, 128, 16),
+                                             (3, 3, 32, 16, 8), (5, 1, 80, 0, 1)])
+def test_rope_kv_write(dtype, nh, nkv, d, rot, ps):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    b, max_pos = 3, 200
+    q_lens, starts = [5, 1, 9], [3, 150, 0]
+    n = sum(q_lens)
+    positions = torch.cat([torch.arange(s, s + q) for s, q in zip(starts, q_lens)]).to(dev(), torch.int32)
+    row_of = torch.repeat_interleave(torch.arange(b), torch.tensor(q_lens)).to(dev(), torch.int32)
+    width = max_pos // ps + 1
+    pages = b * width  # every row has pages of its own
+    bt = torch.randperm(pages, device=dev(), generator=g).view(b, width).to(torch.int32)
+    table = None
+    if rot:
+        from emberserve_b200.parts.rope import inv_frequencies
+
+        table = K().rope_table(inv_frequencies(rot, 1e4).to(dev()), max_pos)
+    qkv = torch.randn(n, (nh + 2 * nkv) * d, device=dev(), generator=g).to(dtype)
+    caches = [torch.full((pages, nkv, ps, d), 9.0, dtype=dtype, device=dev()) for _ in range(4)]
+    qa, qb = qkv.clone(), qkv.clone()
+    K().rope_kv_write(qa, nh, nkv, d, positions, row_of, table, rot, caches[0], caches[1], bt, ps)
+    ref.rope_kv_write(qb, nh, nkv, d, positions, row_of, table, rot, caches[2], caches[3], bt, ps)
+    t = tol(dtype)
+    torch.testing.assert_close(qa.float(), qb.float(), **t)
+    torch.testing.assert_close(caches[0].float(), caches[2].float(), **t)
+    assert torch.equal(caches[1], caches[3])  # values are copied, bit for bit
+    # without the write only q changes
+    qc = qkv.clone()
+    K().rope_kv_write(qc, nh, nkv, d, positions, row_of, table, rot, None, None, None, ps, write_kv=False)
+    assert torch.equal(qc[:, : nh * d], qa[:, : nh * d])
+    assert torch.equal(qc[:, nh * d:], qkv[:, nh * d:])
+
+
+def _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, splits, seed=4, peaky=False):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    b = len(q_lens)
+    n = sum(q_lens)
+    ctx = [s + q for s, q in zip(starts, q_lens)]
+    width = max(-(-c // ps) for c in ctx) + 2
+    pages = b * width + 5
+    perm = torch.randperm(pages, device=dev(), generator=g)[: b * width].view(b, width).to(torch.int32)
+    kc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    vc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    stride = (nh + 2 * nkv) * d
+    qkv = torch.randn(n, stride, device=dev(), generator=g)
+    if peaky:
+        qkv *= 4.0  # sharp softmax: single far keys carry the result
+    qkv = qkv.to(dtype)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=dev(), dtype=torch.int32)
+    st = torch.tensor(starts, device=dev(), dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    got = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    want = torch.empty_like(got)
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(K().attention_scratch_bytes(n, nh, d, splits) // 4, device=dev())
+    K().paged_attention(qkv, got, kc, vc, perm, cu, st, b, n, nh, nkv, d, scale, max(q_lens),
+                        window=window, splits=splits, scratch=scratch)
+    ref.paged_attention(qkv, want, kc, vc, perm, cu, st, b, n, nh, nkv, d, scale, max(q_lens),
+                        window=window, compute_dtype=torch.float64)
+    return got.float(), want.float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,ps", [(4, 2, 16, 4), (3, 1, 32, 8), (7, 1, 48, 16), (28, 4, 128, 16),
+                                         (6, 6, 80, 16), (2, 1, 256, 32), (14, 2, 64, 1)])
+def test_paged_attention_mixed_rows(dtype, nh, nkv, d, ps):
+    """Prompt portions beside decoded tokens, contexts that end inside and at the edge of a
+    page and of a key tile."""
+    q_lens = [37, 1, 2, 1, 64, 5]
+    starts = [0, 63, 30, 128, 17, 95]
+    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, None, 1)
+    torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else tol(dtype)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 32, 33, 100])
+def test_paged_attention_window(dtype, window):
+    got, want = _attention_case(dtype, 7, 1, 48, 16, [40, 1, 3, 1], [0, 77, 64, 31], window, 1, peaky=True)
+    torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else tol(dtype)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [2, 3, 16])
+@pytest.mark.parametrize("window", [None, 70])
+def test_paged_attention_decode_splits(dtype, splits, window):
+    """Decode rows with the keys split over several blocks; short contexts leave some
+    splits empty."""
+    q_lens = [1] * 6
+    starts = [0, 1, 31, 32, 700, 255]
+    got, want = _attention_case(dtype, 28, 4, 128, 16, q_lens, starts, window, splits, peaky=True)
+    torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else tol(dtype)))
+
+
+def test_paged_attention_far_key_stands_out():
+    """One far key among hundreds carries the whole result: its score is made to dominate,
+    so a kernel that skipped or misplaced it would be plainly wrong."""
+    dtype = torch.float32
+    nh, nkv, d, ps, ctx = 4, 1, 64, 16, 600
+    for far in (0, 15, 16, 511, 512, 598):
+        g = torch.Generator(device="cuda").manual_seed(far)
+        pages = 64
+        perm = torch.randperm(pages, device=dev(), generator=g)[None, :].to(torch.int32)
+        kc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g) * 0.1
+        vc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g)
+        q = torch.randn(1, (nh + 2) * d, device=dev(), generator=g)
+        page, slot = int(perm[0, far // ps]), far % ps
+        kc[page, 0, slot] = q[0, :d] * 50.0  # head 0 points at key `far`
+        cu = torch.tensor([0, 1], device=dev(), dtype=torch.int32)
+        st = torch.tensor([ctx - 1], device=dev(), dtype=torch.int32)
+        out = torch.empty(1, nh * d, device=dev())
+        for splits in (1, 4):
+            scratch = torch.empty(max(1, K().attention_scratch_bytes(1, nh, d, splits) // 4), device=dev())
+            K().paged_attention(q, out, kc, vc, perm, cu, st, 1, 1, nh, nkv, d, 1.0, 1, splits=splits,
+                                scratch=scratch)
+            torch.testing.assert_close(out[0, :d], vc[page, 0, slot], rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("r,v", [(1, 7), (5, 1000), (64, 152064), (3, 151936)])
+def test_argmax(r, v):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(r, v, device=dev(), generator=g)
+    logits[0, v // 2] = logits[0, v - 1] = 99.0  # a tie: the first index wins
+    got = torch.empty(r, dtype=torch.int32, device=dev())
+    K().argmax(logits, got)
+    assert got.tolist() == torch.argmax(logits, -1).tolist()
+    assert got[0].item() == v // 2
+
+
+def test_repetition_penalty():
+    g = torch.Generator(device="cuda").manual_seed(6)
+    r, v = 3, 500
+    logits = torch.randn(r, v, device=dev(), generator=g)
+    ids = [[1, 5, 5, 499], [], [0, 7, 250]]
+    ptr = torch.tensor([0, 4, 4, 7], dtype=torch.int32, device=dev())
+    flat = torch.tensor([t for row in ids for t in row], dtype=torch.int32, device=dev())
+    pen = torch.tensor([1.3, 2.0, 0.7], device=dev())
+    want = logits.clone().cpu()
+    ref.repetition_penalty(want, ptr.cpu(), flat.cpu(), pen.cpu())
+    # the kernel sees each token once: the host passes the set (emberserve/sampling.py:42-53)
+    uniq = [sorted(set(row)) for row in ids]
+    ptr_u = torch.tensor([0, 3, 3, 6], dtype=torch.int32, device=dev())
+    flat_u = torch.tensor([t for row in uniq for t in row], dtype=torch.int32, device=dev())
+    K().repetition_penalty(logits, ptr_u, flat_u, pen)
+    torch.testing.assert_close(logits.cpu(), want)
+
+
+@pytest.mark.parametrize("v", [320, 5000, 152064])
+def test_sample_matches_restated_draw(v):
+    """Temperature, top-k and top-p rows against the restated draw (same Philox uniform,
+    same kept set, inverse CDF in index order)."""
+    g = torch.Generator(device="cuda").manual_seed(7)
+    rows = [(0.0, -1, 1.0), (0.8, -1, 1.0), (1.0, 5, 1.0), (0.7, -1, 0.9), (1.3, 50, 0.5), (0.5, 1, 1.0),
+            (1.0, -1, 0.01)]
+    r = len(rows)
+    logits = torch.randn(r, v, device=dev(), generator=g) * 3
+    temp = torch.tensor([x[0] for x in rows], device=dev())
+    tk = torch.tensor([x[1] for x in rows], device=dev(), dtype=torch.int32)
+    tp = torch.tensor([x[2] for x in rows], device=dev())
+    agree = total = 0
+    for counter in range(6):
+        seeds = torch.tensor([1234 + i for i in range(r)], dtype=torch.int64, device=dev())
+        ctrs = torch.full((r,), counter, dtype=torch.int64, device=dev())
+        got = torch.empty(r, dtype=torch.int32, device=dev())
+        K().sample(logits, temp, tk, tp, seeds, ctrs, got)
+        want = torch.empty(r, dtype=torch.int32)
+        ref.sample(logits.cpu(), temp.cpu(), tk.cpu(), tp.cpu(), seeds.cpu(), ctrs.cpu(), want)
+        keep_ok = True
+        for i, (t, k, p) in enumerate(rows):
+            if t > 0:
+                keep = ref.kept_mask(logits[i].cpu() / t, k, p)
+                keep_ok &= bool(keep[got[i].item()])
+        assert keep_ok, "a token outside the kept set was drawn"
+        agree += sum(int(a == b) for a, b in zip(got.tolist(), want.tolist()))
+        total += r
+        assert got[0].item() == int(torch.argmax(logits[0]))
+        assert got[5].item() == int(torch.argmax(logits[5]))  # top_k = 1
+    # 32-bit against 64-bit cumulative sums may disagree on a boundary now and then
+    assert agree >= total - 2
+
+
+def test_sample_distribution_and_seeds():
+    """Draws follow softmax(logits / T); the same (seed, counter) gives the same token."""
+    v, n = 11, 4000
+    logits = torch.tensor([[0.5, 1.0, -1.0, 2.0, 0.0, 0.3, -2.0, 1.5, 0.7, -0.5, 1.1]], device=dev())
+    logits = logits.repeat(n, 1)
+    temp = torch.full((n,), 0.9, device=dev())
+    tk = torch.full((n,), -1, dtype=torch.int32, device=dev())
+    tp = torch.ones(n, device=dev())
+    seeds = torch.arange(n, dtype=torch.int64, device=dev())
+    ctrs = torch.zeros(n, dtype=torch.int64, device=dev())
+    out = torch.empty(n, dtype=torch.int32, device=dev())
+    K().sample(logits, temp, tk, tp, seeds, ctrs, out)
+    again = torch.empty_like(out)
+    K().sample(logits, temp, tk, tp, seeds, ctrs, again)
+    assert torch.equal(out, again)
+    freq = torch.bincount(out.long().cpu(), minlength=v).double() / n
+    probs = torch.softmax(logits[0].double().cpu() / 0.9, -1)
+    assert float((freq - probs).abs().max()) < 0.03
+    for i in (0, 17, 999):
+        u = ref.uniform_of(i, 0)
+        want = int(torch.searchsorted(torch.cumsum(probs, 0), torch.tensor(u, dtype=torch.float64), right=True))
+        assert abs(out[i].item() - want) <= 0 or abs(float(torch.cumsum(probs, 0)[min(want, v - 1)]) - u) < 1e-5
