@@ -85,8 +85,8 @@ class ModelRunner:
 
     def __init__(self, config: ModelConfig, decoder: Decoder, dtype: torch.dtype,
                  device: str | torch.device = "cuda:0", page_size: int = 16,
-                 num_pages: int | None = None, num_state_slots: int = 256,
-                 gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES) -> None:
+                 num_pages: int | None = None, max_pages: int | None = None,
+                 num_state_slots: int = 256, gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES) -> None:
         self.device = torch.device(device)
         if self._require_cuda and (self.device.type != "cuda" or not torch.cuda.is_available()):
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path "
@@ -107,6 +107,8 @@ class ModelRunner:
         paged = [g for g in self.groups if g.paged]
         if num_pages is None:
             num_pages = self._pages_from_free_memory(paged, gpu_memory_utilization, reserve_bytes)
+            if max_pages is not None:
+                num_pages = max(_MIN_PAGES, min(num_pages, max_pages))
         self.num_pages = num_pages
         has_state = any(not g.paged for g in self.groups)
         self.cache = CacheManager(self.groups, num_pages, page_size,
