@@ -1,0 +1,377 @@
+"""Decode and prefill throughput of the engine on one B200, Qwen2.5-7B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with contexts
+that end at 4,096 tokens, timed on the device with CUDA events over exactly K decode
+steps of the engine's step function (bfloat16, seeded random weights of the full
+28-layer shape, uniform random token ids).  ``e2e`` is the same through the public
+``LLMEngine.step()`` loop: host token ids in (one pinned host-to-device copy per step)
+and sampled tokens out (one device-to-host copy per step).  ``prefill`` is one
+2,048-token prompt in one step; ``points`` holds decode at batch 1 and 64; ``roofline``
+divides the bytes a decode step has to read (every weight once, the cache of the live
+requests) by its time and by the measured copy bandwidth.
+
+A decode step reads far more than the 126 MB of L2 (14 GB of weights), so consecutive
+timed steps never find their inputs cached: "inputs larger than L2" in ``config``.
+
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` through its own
+``LLMEngine`` for the same metric and shape, or prints why it cannot.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+# Layer sizes of the Qwen2.5-7B shape (third configuration of the baseline description).
+SHAPE_7B = dict(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1_000_000.0,
+                tie_word_embeddings=False, attention_bias=True, eos_token_id=151645)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+# The reference publishes no B200 number for this metric; its A100 fp16 figure for the
+# same shape at batch 8 (10.64 ms per step) is quoted for context only.
+A100_FP16_B8_TOK_S = 752.0
+
+CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        d = json.loads(path.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    def __init__(self) -> None:
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", "0"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        self.file.flush()
+        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.strip()]
+        os.unlink(self.file.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(names, r[5:9]):
+                if cell.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = [s for s in sm if s >= 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def model_bytes_and_flops(cfg, layers: int) -> dict:
+    h, i, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    per_layer = h * (q + 2 * kv) + (q + 2 * kv) + q * h + 3 * h * i + 2 * h
+    return {"layer_params": per_layer, "weight_bytes": 2 * (layers * per_layer + v * h + h),
+            "kv_bytes_per_token": 2 * layers * 2 * kv,
+            "linear_flops_per_token": 2 * layers * (h * (q + 2 * kv) + q * h + 3 * h * i),
+            "attn_flops_causal": lambda t: layers * 4 * q * t * t / 2, "head_flops": 2 * v * h}
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from emberserve_b200 import kernels as K
+    from emberserve_b200.config.engine import EngineConfig
+    from emberserve_b200.config.model import Qwen2Config
+    from emberserve_b200.engine.llm_engine import LLMEngine
+    from emberserve_b200.engine.runner import ModelRunner, StepRow
+    from emberserve_b200.sampling.params import SamplingParams
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA GPU"
+    peaks = measured_peaks()
+    shape = dict(SHAPE_7B)
+    full_layers = shape["num_hidden_layers"]
+    shape["num_hidden_layers"] = args.layers or full_layers
+    cfg = Qwen2Config.from_dict(dict(shape, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    layers = cfg.num_hidden_layers
+    K.library()
+    torch.manual_seed(0)
+    max_b = max(64, args.batch)
+    pages = max_b * (CONTEXT // PAGE_SIZE + 1) + PREFILL_TOKENS // PAGE_SIZE + 64
+    runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0",
+                                     page_size=PAGE_SIZE, num_pages=pages)
+    for t in runner.storage.tensors:  # keys and values of the "earlier" tokens: random, not zero
+        t.normal_(0, 1)
+    m = model_bytes_and_flops(cfg, layers)
+    gen = torch.Generator().manual_seed(1)
+
+    def rand_tokens(n):
+        return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+
+    def decode(batch: int, steps: int, warmup: int, sample_clocks: bool = False) -> dict:
+        """Device time of exactly `steps` decode steps at `batch`, contexts ending at CONTEXT."""
+        start_ctx = CONTEXT - (steps + warmup)
+        seqs = list(range(1000, 1000 + batch))
+        for s in seqs:
+            runner.cache.admit(s, start_ctx)
+            runner.cache.commit(s, start_ctx)
+        toks = [rand_tokens(steps + warmup) for _ in seqs]
+        out = torch.empty(batch, dtype=torch.int32, device="cuda:0")
+
+        def one(i):
+            rows = []
+            for s, t in zip(seqs, toks):
+                runner.cache.extend(s, start_ctx + i + 1)
+                rows.append(StepRow(s, [t[i]], start_ctx + i, [0]))
+            K.argmax(runner.step(rows), out)
+
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        launches0 = K.launch_count()
+        clocks = ClockSampler() if sample_clocks else None
+        if clocks:
+            clocks.__enter__()
+            time.sleep(0.3)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        if clocks:
+            time.sleep(0.2)
+            clocks.__exit__()
+        ms = ev0.elapsed_time(ev1) / steps
+        for s in seqs:
+            runner.cache.release(s)
+        mean_ctx = start_ctx + warmup + (steps + 1) / 2
+        nbytes = m["weight_bytes"] + batch * mean_ctx * m["kv_bytes_per_token"]
+        return {"ms": ms, "tok_s": batch * 1e3 / ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
+                "launches": K.launch_count() - launches0,
+                "clocks": clocks.summary() if clocks else None}
+
+    def prefill(iters: int = 3) -> dict:
+        times = []
+        for it in range(iters + 1):
+            runner.cache.admit(5000 + it, PREFILL_TOKENS)
+            rows = [StepRow(5000 + it, rand_tokens(PREFILL_TOKENS), 0, [PREFILL_TOKENS - 1])]
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            runner.step(rows)
+            ev1.record()
+            torch.cuda.synchronize()
+            runner.cache.release(5000 + it)
+            if it:
+                times.append(ev0.elapsed_time(ev1))
+        ms = statistics.mean(times)
+        flops = (PREFILL_TOKENS * m["linear_flops_per_token"] + m["attn_flops_causal"](PREFILL_TOKENS)
+                 + m["head_flops"])
+        return {"value": PREFILL_TOKENS * 1e3 / ms, "tokens": PREFILL_TOKENS, "ms": ms,
+                "frac": flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / ms / 1e9}
+
+    def end_to_end(batch: int, steps: int, warmup: int) -> dict:
+        """The same decode steps through LLMEngine.step(): schedule, pack, copy in, run,
+        sample, copy out, stop-check."""
+        ecfg = EngineConfig(dtype=torch.bfloat16, block_size=PAGE_SIZE, max_model_len=CONTEXT + 64,
+                            max_num_batched_tokens=8192, max_num_seqs=max_b)
+        engine = LLMEngine.from_runner(runner, ecfg)
+        prompt_len = CONTEXT - (steps + warmup) - 1
+        for b in range(batch):
+            engine.add_request(f"bench-{b}", rand_tokens(prompt_len),
+                               SamplingParams(max_tokens=steps + warmup + 8, temperature=0.0, ignore_eos=True))
+        while any(r.num_output_tokens == 0 for r in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced = 0
+        for _ in range(steps):
+            produced += len(engine.step())
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        h2d = runner.last_meta_bytes
+        engine.reset()
+        return {"value": produced / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt * 1e3 / steps}
+
+    main = decode(args.batch, args.steps, args.warmup, sample_clocks=True)
+    pre = prefill()
+    b1 = decode(1, min(args.steps, 32), 3)
+    b64 = decode(64, min(args.steps, 32), 3)
+    e2e = end_to_end(args.batch, args.steps, args.warmup)
+    return {
+        "metric": "decode tok/s at batch 8, context 4096 (Qwen2.5-7B shape)",
+        "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0,0.02) seed 0",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-7B shape", "layers": layers, "layers_full": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE,
+                   "prefill_tokens": PREFILL_TOKENS, "parallelism": "1gpu",
+                   "l2": "inputs larger than L2", "cuda_graphs": bool(runner.use_graphs),
+                   "peaks": peaks["source"]},
+        "clocks": main["clocks"], "gpu_launches": main["launches"], "e2e": e2e,
+        "prefill": pre,
+        "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": main["gbs"] / peaks["hbm_gbs"]},
+        "points": {"decode_b1": b1["tok_s"], "decode_b64": b64["tok_s"],
+                   "decode_b1_hbm_frac": b1["gbs"] / peaks["hbm_gbs"],
+                   "decode_b64_hbm_frac": b64["gbs"] / peaks["hbm_gbs"]},
+        "reference_a100_fp16_b8_tok_s": A100_FP16_B8_TOK_S,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference, installed under baseline/_ref, through its own LLMEngine."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "emberserve").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no install of the reference"}
+    sys.path.insert(0, str(ref))
+    try:
+        import torch
+        from emberserve.config import EngineConfig, ModelConfig
+        from emberserve.engine import LLMEngine
+        from emberserve.model.qwen2 import Qwen2ForCausalLM
+        from emberserve.sched.request import SamplingParams
+    except Exception as e:  # pragma: no cover - depends on the machine
+        return {"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA GPU"}
+    s = SHAPE_7B
+    mcfg = ModelConfig(
+        vocab_size=s["vocab_size"], hidden_size=s["hidden_size"], intermediate_size=s["intermediate_size"],
+        num_hidden_layers=args.layers or s["num_hidden_layers"], num_attention_heads=s["num_attention_heads"],
+        num_key_value_heads=s["num_key_value_heads"], max_position_embeddings=s["max_position_embeddings"],
+        rms_norm_eps=s["rms_norm_eps"], rope_theta=s["rope_theta"],
+        tie_word_embeddings=s["tie_word_embeddings"], attention_bias=s["attention_bias"],
+        eos_token_id=s["eos_token_id"])
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device("cuda"):
+            model = Qwen2ForCausalLM(mcfg, tp_size=1)
+    finally:
+        torch.set_default_dtype(prev)
+    with torch.no_grad():
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        for name, p in model.named_parameters():
+            if "norm" in name:
+                p.fill_(1.0)
+            else:
+                p.normal_(0, 0.02, generator=gen)
+    errors = []
+    for backend, block, graphs in (("paged_triton", 16, True), ("paged_triton", 16, False),
+                                   ("paged_flash", 256, True), ("paged_flash", 256, False),
+                                   ("paged_torch", 16, False)):
+        try:
+            pages = 80 * (CONTEXT // block + 2)
+            ecfg = EngineConfig(device="cuda", dtype=torch.bfloat16, attn_backend=backend, block_size=block,
+                                num_gpu_blocks=pages, max_num_seqs=64, max_num_batched_tokens=8192,
+                                max_model_len=CONTEXT + 64, enable_cuda_graphs=graphs,
+                                enable_chunked_prefill=True)
+            engine = LLMEngine(model, mcfg, ecfg, tokenizer=None)
+            engine.keep_stats = False
+            g = torch.Generator().manual_seed(1)
+            prompt_len = CONTEXT - (args.steps + args.warmup) - 1
+            for b in range(args.batch):
+                ids = torch.randint(0, mcfg.vocab_size, (prompt_len,), generator=g).tolist()
+                engine.add_request(f"bench-{b}", ids, SamplingParams(
+                    max_tokens=args.steps + args.warmup + 8, temperature=0.0, ignore_eos=True))
+            while engine.scheduler.waiting or any(r.num_output_tokens == 0 for r in engine.scheduler.running):
+                engine.step()
+            for _ in range(args.warmup):
+                engine.step()
+            torch.cuda.synchronize()
+            with ClockSampler() as clocks:
+                t0 = time.perf_counter()
+                produced = 0
+                for _ in range(args.steps):
+                    produced += len(engine.step())
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+            return {"metric": "decode tok/s at batch 8, context 4096 (Qwen2.5-7B shape)",
+                    "value": produced / dt, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+                    "warmup": args.warmup, "ms_per_step": dt * 1e3 / args.steps, "higher_is_better": True,
+                    "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "impl": "reference",
+                    "config": {"model": "Qwen2.5-7B shape", "layers": mcfg.num_hidden_layers,
+                               "global_batch": args.batch, "seq_len": CONTEXT, "attn_backend": backend,
+                               "block_size": block, "cuda_graphs": graphs, "parallelism": "1gpu"},
+                    "clocks": clocks.summary(),
+                    "e2e": {"value": produced / dt, "unit": "tok/s"},
+                    "tried": errors}
+        except Exception as e:  # try the next stock backend of the reference
+            errors.append(f"{backend}/graphs={graphs}: {type(e).__name__}: {str(e)[:120]}")
+            torch.cuda.synchronize()
+    return {"impl": "reference", "unavailable": "no attention backend of the reference ran here: "
+            + " | ".join(errors)[:600]}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the shape has (the line then names both numbers)")
+    args = ap.parse_args()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py measures a one-GPU engine; --gpus {args.gpus} is not supported (N=1 only)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

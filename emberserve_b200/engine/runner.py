@@ -122,6 +122,8 @@ class ModelRunner:
         self._meta_events: list[torch.cuda.Event | None] = [None, None]
         self._meta_turn = 0
         self.steps_run = 0
+        self.last_meta_bytes = 0  # bytes of the last step's host-to-device copy
+        self.use_graphs = False
 
     # ---- construction ----------------------------------------------------------------------
     @classmethod
@@ -239,6 +241,7 @@ class ModelRunner:
         for off, s in zip(offsets, sections):
             hv[off:off + s.size] = s
         self._meta_dev[:total].copy_(host[:total], non_blocking=True)
+        self.last_meta_bytes = 4 * total
         if self._on_cuda:
             ev = torch.cuda.Event()
             ev.record()

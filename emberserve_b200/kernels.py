@@ -75,9 +75,25 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ems_paged_attention_scratch_bytes.restype = c_longlong
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process (eager launches; a CUDA
+    graph replay adds what its capture recorded)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'status {code}')}")
+    _launches += kernels
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -207,7 +223,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
         _i32(cu_q, "cu_q"), _i32(starts, "starts"), num_rows, num_tokens, num_heads, num_kv_heads,
         head_dim, int(window or 0), float(scale), max_q_len, splits,
         _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
-        _stream()), "paged_attention")
+        _stream()), "paged_attention", 2 if splits > 1 else 1)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

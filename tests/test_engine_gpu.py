@@ -1,0 +1,506 @@
+"""The engine on the GPU beyond the four cuts: greedy generation through the entry point,
+long decoding, the first tokens of a sequence, faults that random weights would hide
+(a far key, a window's edge, a page's edge), each part alone, and a toy architecture with
+a mixer that has state of its own, registered from here without touching the package."""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+from dataclasses import dataclass
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import replay_cases as rc
+from tiny_configs import ALL, PAGE_SIZES, SEEDS
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = {torch.float32: 3e-5, torch.bfloat16: 3e-2}
+
+
+def _runner(model_dir, dtype, page_size, pages):
+    from emberserve_b200.engine.runner import ModelRunner
+
+    return ModelRunner.from_dir(model_dir, dtype, device=DEV, page_size=page_size, num_pages=pages)
+
+
+def _llm(model_dir, name, dtype, pages=512, **cfg):
+    from emberserve_b200 import LLM
+
+    return LLM(model_dir, dtype=dtype, device=DEV, block_size=PAGE_SIZES[name], num_gpu_blocks=pages,
+               max_model_len=ALL[name].max_position_embeddings, **cfg)
+
+
+def _sharp_model(tmp_path_factory, name, std=0.1):
+    """Weights with five times the usual deviation: logits far enough apart that greedy
+    tokens vary and mean something, while the model stays well conditioned (ten times the
+    deviation makes these tiny models chaotic: bfloat16 rounding alone then moves logits by
+    several per cent)."""
+    from emberserve_b200.weights.loader import write_random_model
+
+    return write_random_model(ALL[name], tmp_path_factory.mktemp(f"sharp_{name}"), SEEDS[name], std=std,
+                              bias_std=std)
+
+
+@pytest.fixture(scope="module")
+def sharp_dirs(tmp_path_factory):
+    return {name: _sharp_model(tmp_path_factory, name) for name in ALL}
+
+
+# ---- generation through the entry point ---------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_greedy_generation_equals_plain(sharp_dirs, name):
+    from emberserve_b200 import SamplingParams
+
+    cfg, w = plain.read_model_dir(sharp_dirs[name])
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, ALL[name].vocab_size, (n,), generator=g).tolist() for n in (5, 11, 17)]
+    want = [plain.greedy_generate(cfg, w, p, 8) for p in prompts]
+    llm = _llm(sharp_dirs[name], name, "float32")
+    got = [r.output_token_ids for r in llm.generate(prompts, SamplingParams.greedy(8, ignore_eos=True))]
+    assert got == want
+    # bfloat16: a token may differ only where the plain logits of the two candidates are
+    # closer than the bfloat16 error of the engine (the reference's rule,
+    # scripts/check_golden.py:55-117)
+    got16 = [r.output_token_ids for r in
+             _llm(sharp_dirs[name], name, "bfloat16").generate(prompts, SamplingParams.greedy(8, ignore_eos=True))]
+    for p, a, b in zip(prompts, got16, want):
+        for i, (x, y) in enumerate(zip(a, b)):
+            if x != y:
+                logits = plain.forward_logits(cfg, w, p + b[:i])[-1]
+                assert abs(float(logits[x] - logits[y])) <= 2 * TOL[torch.bfloat16] * float(logits.abs().max())
+                break
+
+
+def test_chunked_mixed_and_preempted_generation_on_the_gpu(sharp_dirs):
+    from emberserve_b200 import SamplingParams
+
+    name = "tiny_b"
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, ALL[name].vocab_size, (n,), generator=g).tolist() for n in (1, 9, 23, 40)]
+    params = [SamplingParams(max_tokens=12, temperature=0.8, seed=7 + i, ignore_eos=True) for i in range(4)]
+    base = [r.output_token_ids for r in _llm(sharp_dirs[name], name, "float32",
+                                             enable_chunked_prefill=False).generate(prompts, params)]
+    llm = _llm(sharp_dirs[name], name, "float32", max_num_batched_tokens=7)
+    llm.engine.keep_stats = True
+    assert [r.output_token_ids for r in llm.generate(prompts, params)] == base
+    assert any(s.num_decode_tokens and s.num_prefill_tokens for s in llm.engine.stats)
+    tight = _llm(sharp_dirs[name], name, "float32", pages=13, max_num_batched_tokens=16)
+    tight.engine.keep_stats = True
+    assert [r.output_token_ids for r in tight.generate(prompts, params)] == base
+    assert sum(s.num_preempted for s in tight.engine.stats) >= 1
+    st = tight.engine.runner.cache.stats()
+    assert st.num_free == st.num_pages
+
+
+def test_cpu_device_is_refused(model_dirs):
+    from emberserve_b200.engine.runner import ModelRunner
+
+    with pytest.raises(RuntimeError, match="CUDA GPU only"):
+        ModelRunner.from_dir(model_dirs["tiny_a"], torch.float32, device="cpu")
+
+
+# ---- long decoding and the first tokens ---------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
+def test_long_decoding_token_by_token(sharp_dirs, name, dtype):
+    """A short prompt and then every further token alone, across many pages (and, for the
+    windowed model, far past the window, while its pages are given back)."""
+    from emberserve_b200.engine.replay import TraceReplayer
+
+    cfg = ALL[name]
+    n = cfg.max_position_embeddings - 3
+    reqs = rc.make_requests(cfg.vocab_size, [n], seed=5)
+    cfgd, w = plain.read_model_dir(sharp_dirs[name])
+    want = plain.forward_logits(cfgd, w, reqs[0][1]).numpy()
+    steps = rc.bulk_then_tail(reqs, tail=n - 3)
+    ps = PAGE_SIZES[name]
+    runner = _runner(sharp_dirs[name], dtype, ps, -(-n // ps))
+    rp = TraceReplayer(runner)
+    outs = {s["step"]: rp.run_step(s) for s in steps}
+    got = rc.collect(steps, outs)
+    err = max(float(np.abs(got[("r0", p)] - want[p]).max()) for p in range(n))
+    assert err <= TOL[dtype] * float(np.abs(want).max()), err
+    if name == "tiny_c":
+        assert runner.cache.stats().num_free[1] == runner.cache.stats().num_pages[1]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_first_tokens_of_a_sequence(sharp_dirs, dtype):
+    """Sequences of one, two and three tokens, token by token and whole, beside each other."""
+    from emberserve_b200.engine.replay import TraceReplayer
+
+    name = "tiny_b"
+    reqs = rc.make_requests(ALL[name].vocab_size, [1, 2, 3], seed=6)
+    cfgd, w = plain.read_model_dir(sharp_dirs[name])
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": toks[:1], "want": [0]} for rid, toks in reqs],
+              "end": ["r0"]},
+             {"step": 1, "entries": [{"id": rid, "tokens": toks[1:2], "want": [0]} for rid, toks in reqs[1:]],
+              "end": ["r1"]},
+             {"step": 2, "entries": [{"id": "r2", "tokens": reqs[2][1][2:], "want": [0]},
+                                     {"id": "w", "tokens": reqs[2][1], "want": [0, 1, 2]}], "end": ["r2", "w"]}]
+    runner = _runner(sharp_dirs[name], dtype, 8, 8)
+    rp = TraceReplayer(runner)
+    got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+    for rid, toks in reqs + [("w", reqs[2][1])]:
+        want = plain.forward_logits(cfgd, w, toks).numpy()
+        for p in range(len(toks)):
+            assert np.abs(got[(rid, p)] - want[p]).max() <= TOL[dtype] * np.abs(want).max()
+
+
+# ---- faults that random weights would hide ------------------------------------------------------
+
+def _with_attention_pointing_at(model_dir, out_dir, gain=5.0):
+    """A copy of a model whose q and k projections are scaled up (scores grow with the
+    square of the gain) so that attention is peaked instead of nearly uniform: the result at
+    a position then hangs on few keys, near or far, and a missed key shows."""
+    from safetensors.torch import load_file, save_file
+
+    out_dir.mkdir(parents=True, exist_ok=True)
+    (out_dir / "config.json").write_text((model_dir / "config.json").read_text())
+    t = load_file(str(model_dir / "model.safetensors"))
+    for k in t:
+        if ".q_proj." in k or ".k_proj." in k:
+            t[k] = (t[k].float() * gain).to(t[k].dtype)
+    save_file(t, str(out_dir / "model.safetensors"))
+    return out_dir
+
+
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
+def test_peaked_attention_far_keys_window_edge_page_edge(model_dirs, tmp_path, name):
+    """With peaked attention a skipped key, an off-by-one at the window's edge or a wrong
+    slot at a page's edge changes logits by far more than the tolerance.  The sequence is
+    cut so that portions start and end on and around page edges and the window's edge."""
+    from emberserve_b200.engine.replay import TraceReplayer
+
+    folder = _with_attention_pointing_at(model_dirs[name], tmp_path / "peaked")
+    cfg = ALL[name]
+    ps = PAGE_SIZES[name]
+    n = min(cfg.max_position_embeddings - 1, 230)
+    reqs = rc.make_requests(cfg.vocab_size, [n], seed=8)
+    cfgd, w = plain.read_model_dir(folder)
+    want = plain.forward_logits(cfgd, w, reqs[0][1]).numpy()
+    # the attention must really be peaked, else the test shows nothing
+    base = plain.forward_logits(*plain.read_model_dir(model_dirs[name]), reqs[0][1]).numpy()
+    assert np.abs(want - base).max() > 0.2 * np.abs(want).max()
+    win = cfg.sliding_window or 24
+    cuts = sorted({ps - 1, ps, ps + 1, 2 * ps, win - 1, win, win + 1, 3 * ps + 1, 64, 65, 96, 127, 128, 129, n})
+    toks = reqs[0][1]
+    steps, prev = [], 0
+    for c in cuts:
+        if c <= prev or c > n:
+            continue
+        steps.append({"entries": [{"id": "r0", "tokens": toks[prev:c], "want": list(range(c - prev))}], "end": []})
+        prev = c
+    for i, s in enumerate(steps):
+        s["step"] = i
+    for dtype in (torch.float32, torch.bfloat16):
+        runner = _runner(folder, dtype, ps, -(-n // ps) + 1)
+        rp = TraceReplayer(runner)
+        got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+        err = max(float(np.abs(got[("r0", p)] - want[p]).max()) for p in range(n))
+        assert err <= TOL[dtype] * float(np.abs(want).max()), (dtype, err)
+
+
+def test_stale_page_contents_do_not_leak(sharp_dirs):
+    """A pool of exactly the pages one request needs: the second request gets the first
+    one's pages, full of its keys, and must not see them."""
+    from emberserve_b200.engine.replay import TraceReplayer
+
+    name = "tiny_a"
+    reqs = rc.make_requests(ALL[name].vocab_size, [37, 35], seed=9)
+    cfgd, w = plain.read_model_dir(sharp_dirs[name])
+    steps = rc.portions(reqs)
+    runner = _runner(sharp_dirs[name], torch.float32, 4, 10)
+    rp = TraceReplayer(runner)
+    got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+    for rid, toks in reqs:
+        want = plain.forward_logits(cfgd, w, toks).numpy()
+        for p in range(len(toks)):
+            assert np.abs(got[(rid, p)] - want[p]).max() <= TOL[torch.float32] * np.abs(want).max()
+
+
+# ---- each part alone ----------------------------------------------------------------------------
+
+def _ctx(q_lens, starts, dtype):
+    from emberserve_b200.engine.runner import ScratchArena
+    from emberserve_b200.parts.base import StepContext
+
+    b, n = len(q_lens), sum(q_lens)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(s, s + q) for s, q in zip(starts, q_lens)]).to(**i32)
+    row = torch.repeat_interleave(torch.arange(b), torch.tensor(q_lens)).to(**i32)
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), **i32)
+    return StepContext(num_tokens=n, num_rows=b, dtype=dtype, device=torch.device(DEV),
+                       tokens=torch.zeros(n, **i32), positions=pos, row_of_token=row, cu_q=cu,
+                       starts=torch.tensor(starts, **i32), q_lens=q_lens, start_list=starts,
+                       max_q_len=max(q_lens), max_ctx_len=max(s + q for s, q in zip(starts, q_lens)),
+                       scratch=ScratchArena(torch.device(DEV)))
+
+
+def _bind_random(part, dtype, seed, std=0.3):
+    g = torch.Generator().manual_seed(seed)
+    params, by_source = {}, {}
+    for local, ps in part.param_specs().items():
+        t = torch.ones(ps.shape) if ps.init == "ones" else torch.randn(ps.shape, generator=g) * std
+        if ps.init == "ones":
+            t = t + 0.1 * torch.randn(ps.shape, generator=g)
+        t = t.to(dtype)
+        params[local] = t.to(DEV)
+        for src in ps.sources:
+            by_source[src.name] = (t if src.rows is None else t[src.rows[0]:src.rows[1]]).double()
+    part.bind(params)
+    return by_source
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_norm_part_alone(dtype):
+    from emberserve_b200.parts.base import build_part
+    from emberserve_b200.parts.norm import RMSNormSpec
+
+    part = build_part("norm", RMSNormSpec(200, 3e-5, "n.weight"), "n")
+    w = _bind_random(part, dtype, 0)
+    ctx = _ctx([5, 1], [0, 9], dtype)
+    g = torch.Generator().manual_seed(1)
+    delta = torch.randn(6, 200, generator=g).to(dtype)
+    res = torch.randn(6, 200, generator=g)
+    r = res.to(DEV)
+    out = part.forward(delta.to(DEV), r, ctx)
+    want_res = res.double() + delta.double()
+    want = plain.rms_norm(want_res, w["n.weight"], 3e-5)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(r.double().cpu(), want_res, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out.double().cpu(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_feed_forward_part_alone(dtype):
+    from emberserve_b200.parts.base import build_part
+    from emberserve_b200.parts.mlp import SwiGLUSpec
+
+    part = build_part("feed_forward", SwiGLUSpec(72, 200, "m.gate_proj", "m.up_proj", "m.down_proj"), "m")
+    w = _bind_random(part, dtype, 2, std=0.1)
+    ctx = _ctx([7], [0], dtype)
+    x = torch.randn(7, 72, generator=torch.Generator().manual_seed(3)).to(dtype)
+    out = part.forward(x.to(DEV), ctx)
+    want = plain.swiglu(x.double(), w, "m")
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    torch.testing.assert_close(out.double().cpu(), want, rtol=tol, atol=tol * float(want.abs().max()))
+
+
+def test_position_part_alone():
+    from emberserve_b200.parts.base import build_part
+    from emberserve_b200.parts.rope import RotarySpec
+
+    part = build_part("position", RotarySpec(48, 50000.0, 300), "p")
+    table, rot = part.rotary(torch.device(DEV))
+    assert rot == 48 and table.shape == (300, 24, 2) and part.max_positions == 300
+    ang = plain.rope_angles(torch.arange(300), 48, 50000.0)[:, :24].double()
+    torch.testing.assert_close(table[..., 0].double().cpu(), ang.cos(), rtol=0, atol=2e-6)
+    torch.testing.assert_close(table[..., 1].double().cpu(), ang.sin(), rtol=0, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_alone_in_two_steps(dtype, window):
+    """The mixer alone: a sequence in two portions through a paged cache with scattered
+    pages equals the plain attention block on the whole sequence."""
+    from emberserve_b200.parts.attention import AttentionSpec
+    from emberserve_b200.parts.base import PagedKVHandle, build_part
+    from emberserve_b200.parts.rope import RotarySpec
+
+    hidden, nh, nkv, d, ps, t = 80, 6, 2, 32, 4, 27
+    spec = AttentionSpec(hidden, nh, nkv, d, True, RotarySpec(d, 1e4, 64), "a.q_proj", "a.k_proj", "a.v_proj",
+                         "a.o_proj", window=window)
+    part = build_part("mixer", spec, "a")
+    assert part.cache_need().window == window and part.cache_need().num_kv_heads == nkv
+    w = _bind_random(part, dtype, 4, std=0.25)
+    x = torch.randn(t, hidden, generator=torch.Generator().manual_seed(5)).to(dtype)
+    g = dict(heads=nh, kv_heads=nkv, head_dim=d, theta=1e4, bias=True)
+    want = plain.attention_block(x.double(), w, "a", g, torch.arange(t), window)
+    pages = 16
+    kc = torch.full((pages, nkv, ps, d), 50.0, dtype=dtype, device=DEV)
+    vc = torch.full((pages, nkv, ps, d), 50.0, dtype=dtype, device=DEV)
+    bt = torch.tensor([[11, 3, 8, 0, 14, 6, 9]], dtype=torch.int32, device=DEV)
+    outs = []
+    for lo, hi in ((0, 10), (10, t)):
+        ctx = _ctx([hi - lo], [lo], dtype)
+        outs.append(part.forward(x[lo:hi].to(DEV), ctx, PagedKVHandle(kc, vc, bt, ps, window, True)).clone())
+    got = torch.cat(outs).double().cpu()
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    torch.testing.assert_close(got, want, rtol=tol, atol=tol * float(want.abs().max()))
+
+
+def test_block_part_alone():
+    from emberserve_b200.parts.attention import AttentionSpec
+    from emberserve_b200.parts.base import PagedKVHandle, build_part
+    from emberserve_b200.parts.block import PreNormBlockSpec
+    from emberserve_b200.parts.mlp import SwiGLUSpec
+    from emberserve_b200.parts.norm import RMSNormSpec
+    from emberserve_b200.parts.rope import RotarySpec
+
+    hidden, t, p = 48, 13, "model.layers.0"
+    spec = PreNormBlockSpec(
+        mixer=AttentionSpec(hidden, 3, 3, 16, False, RotarySpec(16, 1e4, 32), f"{p}.self_attn.q_proj",
+                            f"{p}.self_attn.k_proj", f"{p}.self_attn.v_proj", f"{p}.self_attn.o_proj"),
+        feed_forward=SwiGLUSpec(hidden, 100, f"{p}.mlp.gate_proj", f"{p}.mlp.up_proj", f"{p}.mlp.down_proj"),
+        mixer_norm=RMSNormSpec(hidden, 1e-5, f"{p}.input_layernorm.weight"),
+        ffn_norm=RMSNormSpec(hidden, 1e-5, f"{p}.post_attention_layernorm.weight"))
+    block = build_part("block", spec, "layers.0")
+    w = {}
+    for i, child in enumerate(block.children().values()):
+        w.update(_bind_random(child, torch.float32, 10 + i, std=0.2))
+    h0 = torch.randn(t, hidden, generator=torch.Generator().manual_seed(6))
+    g = dict(heads=3, kv_heads=3, head_dim=16, theta=1e4, bias=False, eps=1e-5, window=None, max_window_layers=0)
+    want = plain.decoder_layer(h0.double(), w, 0, g, torch.arange(t))
+    kc = torch.zeros(4, 3, 8, 16, device=DEV)
+    vc = torch.zeros_like(kc)
+    bt = torch.tensor([[2, 1]], dtype=torch.int32, device=DEV)
+    ctx = _ctx([t], [0], torch.float32)
+    residual = h0.to(DEV).clone()
+    delta = block.forward(None, residual, ctx, PagedKVHandle(kc, vc, bt, 8, None, True))
+    got = (residual + delta).double().cpu()  # the next norm would perform this add
+    torch.testing.assert_close(got, want, rtol=2e-5, atol=2e-5)
+
+
+# ---- a toy architecture with a mixer that keeps state of its own ----------------------------------
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A recurrent toy mixer (s_t = decay * s_{t-1} + x_t W_in ; y_t = s_t W_out) defined
+    HERE is registered as a part, used by a toy architecture registered HERE, written as a
+    random model folder, loaded, and stepped in portions, token by token and beside another
+    request; layers alternate between the toy mixer and attention.  Nothing in the package
+    is edited for it."""
+    from emberserve_b200.config.model import ModelConfig
+    from emberserve_b200.engine.replay import TraceReplayer
+    from emberserve_b200.engine.runner import ModelRunner
+    from emberserve_b200.parts.attention import AttentionSpec
+    from emberserve_b200.parts.base import FixedState, Mixer, ParamSpec, Source, register_part
+    from emberserve_b200.parts.block import PreNormBlockSpec
+    from emberserve_b200.parts.decoder import DecoderSpec, LayerCall
+    from emberserve_b200.parts.mlp import SwiGLUSpec
+    from emberserve_b200.parts.norm import RMSNormSpec
+    from emberserve_b200.parts.rope import RotarySpec
+    from emberserve_b200.registry import register_architecture
+    from emberserve_b200.weights.loader import write_random_model
+
+    @dataclass(frozen=True)
+    class ToyDecaySpec:
+        hidden: int
+        state: int
+        decay: float
+        name: str
+        kind: str = "toy_decay"
+
+    @register_part("mixer", "toy_decay")
+    class ToyDecay(Mixer):
+        def cache_need(self):
+            return FixedState((self.spec.state,), "float32")
+
+        def param_specs(self):
+            s = self.spec
+            return {"w_in": ParamSpec((s.state, s.hidden), [Source(s.name + ".in.weight")]),
+                    "w_out": ParamSpec((s.hidden, s.state), [Source(s.name + ".out.weight")])}
+
+        def forward(self, x, ctx, cache):
+            u = x.float() @ self.w_in.float().t()
+            y = torch.empty_like(u)
+            slots = cache.slots.tolist()
+            n0 = 0
+            for row, q in enumerate(ctx.q_lens):  # a request's tokens in order, from its state
+                s = cache.state[slots[row]]
+                for i in range(n0, n0 + q):
+                    s = self.spec.decay * s + u[i]
+                    y[i] = s
+                cache.state[slots[row]] = s
+                n0 += q
+            return (y @ self.w_out.float().t()).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyDecayForCausalLM"
+        vocab_size: int = 90
+        hidden_size: int = 48
+        state_size: int = 20
+        num_layers: int = 4
+        decay: float = 0.8
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{f.name: cfg[f.name] for f in dataclasses.fields(cls) if f.name in cfg})
+
+        def to_dict(self):
+            return dict(dataclasses.asdict(self), architectures=[self.architecture])
+
+    def build(cfg: ToyConfig) -> DecoderSpec:
+        layers = []
+        for i in range(cfg.num_layers):
+            p = f"toy.{i}"
+            mixer = (ToyDecaySpec(cfg.hidden_size, cfg.state_size, cfg.decay, f"{p}.rec") if i % 2 == 0 else
+                     AttentionSpec(cfg.hidden_size, 3, 1, 16, False, RotarySpec(16, 1e4, 128), f"{p}.q", f"{p}.k",
+                                   f"{p}.v", f"{p}.o"))
+            layers.append(PreNormBlockSpec(
+                mixer=mixer, feed_forward=SwiGLUSpec(cfg.hidden_size, 64, f"{p}.g", f"{p}.u", f"{p}.d"),
+                mixer_norm=RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n1"),
+                ffn_norm=RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n2")))
+        return DecoderSpec(vocab_size=cfg.vocab_size, hidden=cfg.hidden_size, embed_name="toy.embed",
+                           layers=layers, order=[LayerCall(i, i) for i in range(cfg.num_layers)],
+                           final_norm=RMSNormSpec(cfg.hidden_size, 1e-5, "toy.norm"), head_name=None,
+                           max_positions=128)
+
+    register_architecture("ToyDecayForCausalLM", ToyConfig, build)
+    cfg = ToyConfig()
+    folder = write_random_model(cfg, tmp_path / "toy", seed=3, std=0.15, store_dtype=torch.float32)
+
+    def plain_toy(tokens):
+        from safetensors.torch import load_file
+
+        w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+        h = w["toy.embed"][torch.tensor(tokens)]
+        t = len(tokens)
+        for i in range(cfg.num_layers):
+            p = f"toy.{i}"
+            x = plain.rms_norm(h, w[f"{p}.n1"], 1e-5)
+            if i % 2 == 0:
+                u = x @ w[f"{p}.rec.in.weight"].T
+                s = torch.zeros(cfg.state_size, dtype=torch.float64)
+                ys = []
+                for j in range(t):
+                    s = cfg.decay * s + u[j]
+                    ys.append(s)
+                a = torch.stack(ys) @ w[f"{p}.rec.out.weight"].T
+            else:
+                q = (x @ w[f"{p}.q.weight"].T).view(t, 3, 16)
+                k = (x @ w[f"{p}.k.weight"].T).view(t, 1, 16)
+                v = (x @ w[f"{p}.v.weight"].T).view(t, 1, 16)
+                ang = plain.rope_angles(torch.arange(t), 16, 1e4)
+                a = plain.causal_attention(plain.apply_rope(q, ang), plain.apply_rope(k, ang), v)
+                a = a.reshape(t, 48) @ w[f"{p}.o.weight"].T
+            h = h + a
+            y = plain.rms_norm(h, w[f"{p}.n2"], 1e-5)
+            gate, up = y @ w[f"{p}.g.weight"].T, y @ w[f"{p}.u.weight"].T
+            h = h + (torch.nn.functional.silu(gate) * up) @ w[f"{p}.d.weight"].T
+        return (plain.rms_norm(h, w["toy.norm"], 1e-5) @ w["toy.embed"].T).numpy()
+
+    runner = ModelRunner.from_dir(folder, torch.float32, device=DEV, page_size=8, num_pages=24,
+                                  num_state_slots=2)
+    kinds = [type(g.need).__name__ for g in runner.groups]
+    assert sorted(kinds) == ["FixedState", "PagedKV"]
+    reqs = rc.make_requests(cfg.vocab_size, [21, 30, 17], seed=2)
+    want = {rid: plain_toy(toks) for rid, toks in reqs}
+    for steps in (rc.whole(reqs), rc.portions(reqs), rc.mixed(reqs, max_live=2, seed=1, decode_tail=5)):
+        rp = TraceReplayer(runner)
+        got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+        for rid, toks in reqs:
+            for p in range(len(toks)):
+                assert np.abs(got[(rid, p)] - want[rid][p]).max() <= 3e-5 * np.abs(want[rid]).max()
+        runner.cache.check()
+        assert runner.cache.stats().free_state_slots == 2
