@@ -329,3 +329,56 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
     if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
     return EMS_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------
+// The variant that allocates nothing (see no_alloc.h for the contract and for who needs
+// it): the partial results of the splits go to a fixed array inside the library.
+#include "no_alloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) unsigned char g_static_scratch[EMS_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the current device; taken once per device.  In
+// host code the symbol's name is not that address, so it must go through the runtime.
+void* static_scratch_address() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) {
+            cudaGetLastError();  // leave no sticky error behind for the caller's next check
+            return nullptr;
+        }
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    return g_static_scratch_ptr[dev];
+}
+}  // namespace
+
+EMS_EXPORT long long ems_static_scratch_capacity(void) { return (long long)EMS_STATIC_SCRATCH_BYTES; }
+
+EMS_EXPORT int ems_paged_attention_static_scratch(
+    const void* q, long long q_stride, void* out, int dtype, const void* kcache, const void* vcache,
+    const int* block_tables, int bt_stride, int page_size, const int* cu_q, const int* starts, int B,
+    int N, int nh, int nkv, int D, int window, float scale, int max_q_len, int splits,
+    cudaStream_t stream) {
+    if (splits <= 1)
+        return ems_paged_attention(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride,
+                                   page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
+                                   1, nullptr, 0, stream);
+    if (N <= 0 || nh <= 0 || D <= 0) return B <= 0 || N <= 0 ? EMS_OK : EMS_ERR_SHAPE;
+    const long long need = ems_paged_attention_scratch_bytes(N, nh, D, splits);
+    if (need > (long long)EMS_STATIC_SCRATCH_BYTES) return EMS_ERR_SCRATCH;
+    void* scratch = static_scratch_address();
+    if (scratch == nullptr) return EMS_ERR_LAUNCH;
+    return ems_paged_attention(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride,
+                               page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
+                               splits, scratch, (long long)EMS_STATIC_SCRATCH_BYTES, stream);
+}
