@@ -139,6 +139,8 @@ def run_ours(args) -> dict:
     pages = max_b * (CONTEXT // PAGE_SIZE + 1) + PREFILL_TOKENS // PAGE_SIZE + 64
     runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0",
                                      page_size=PAGE_SIZE, num_pages=pages)
+    if not args.no_graphs:
+        runner.enable_graphs(CONTEXT + 64, max_b)
     for t in runner.storage.tensors:  # keys and values of the "earlier" tokens: random, not zero
         t.normal_(0, 1)
     m = model_bytes_and_flops(cfg, layers)
@@ -215,7 +217,8 @@ def run_ours(args) -> dict:
         """The same decode steps through LLMEngine.step(): schedule, pack, copy in, run,
         sample, copy out, stop-check."""
         ecfg = EngineConfig(dtype=torch.bfloat16, block_size=PAGE_SIZE, max_model_len=CONTEXT + 64,
-                            max_num_batched_tokens=8192, max_num_seqs=max_b)
+                            max_num_batched_tokens=8192, max_num_seqs=max_b,
+                            enable_cuda_graphs=False)  # the runner's graphs are on already
         engine = LLMEngine.from_runner(runner, ecfg)
         prompt_len = CONTEXT - (steps + warmup) - 1
         for b in range(batch):
@@ -237,6 +240,30 @@ def run_ours(args) -> dict:
         return {"value": produced / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt * 1e3 / steps}
 
+    def kernel_times(fn) -> list:
+        """Device time per kernel name over one call of `fn` (torch's profiler)."""
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows) or 1.0
+        return [{"kernel": e.key[:90], "calls": e.count, "us": round(e.device_time_total, 1),
+                 "share": round(e.device_time_total / total, 4)} for e in rows[:25]]
+
+    if args.only == "decode":
+        d = decode(args.batch, args.steps, args.warmup)
+        out = {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": d["ms"],
+               "tok_s": d["tok_s"], "hbm_frac": d["gbs"] / peaks["hbm_gbs"]}
+        if args.kernel_times:
+            out["kernels"] = kernel_times(lambda: decode(args.batch, args.steps, args.warmup))
+        return out
+    if args.only == "prefill":
+        out = dict(prefill(max(1, args.steps)), only="prefill", layers=layers)
+        if args.kernel_times:
+            out["kernels"] = kernel_times(lambda: prefill(1))
+        return out
     main = decode(args.batch, args.steps, args.warmup, sample_clocks=True)
     pre = prefill()
     b1 = decode(1, min(args.steps, 32), 3)
@@ -360,6 +387,11 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one small part only (for profiling): decode at --batch, or the prefill")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="with --only: add device time per kernel name (torch profiler)")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the shape has (the line then names both numbers)")
     args = ap.parse_args()

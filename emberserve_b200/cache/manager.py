@@ -20,6 +20,8 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from emberserve_b200.parts.base import CacheNeed, FixedState, PagedKV
 
 
@@ -99,6 +101,19 @@ class _Sequence:
     tables: list[list[int]] = field(default_factory=list)  # per paged group; -1 = given back
     released: list[int] = field(default_factory=list)  # per paged group: leading pages given back
     slot: int = -1
+    # The tables once more as int32 arrays (given-back pages as 0, a valid id that is never
+    # read), kept in step with `tables`, so that a step copies them without a Python loop.
+    arrays: list[np.ndarray] = field(default_factory=list)
+
+    def append_page(self, k: int, page: int) -> None:
+        table = self.tables[k]
+        arr = self.arrays[k]
+        if len(table) >= arr.size:
+            grown = np.zeros(max(8, 2 * arr.size), dtype=np.int32)
+            grown[:arr.size] = arr
+            self.arrays[k] = arr = grown
+        arr[len(table)] = page
+        table.append(page)
 
 
 @dataclass
@@ -150,6 +165,11 @@ class CacheManager:
         window has passed and the page was given back."""
         return self._seqs[seq_id].tables[paged_group]
 
+    def table_array(self, seq_id: int, paged_group: int) -> np.ndarray:
+        """The same table as an int32 array, with 0 where a page was given back."""
+        seq = self._seqs[seq_id]
+        return seq.arrays[paged_group][:len(seq.tables[paged_group])]
+
     def state_slot(self, seq_id: int) -> int:
         return self._seqs[seq_id].slot
 
@@ -189,9 +209,12 @@ class CacheManager:
         if self.state_groups and not self._free_slots:
             raise OutOfPages("no free state slot")
         seq = _Sequence(num_tokens=num_tokens)
-        for pool in self.pools:
-            seq.tables.append([pool.take() for _ in range(need)])
+        for k, pool in enumerate(self.pools):
+            seq.tables.append([])
+            seq.arrays.append(np.zeros(max(8, need), dtype=np.int32))
             seq.released.append(0)
+            for _ in range(need):
+                seq.append_page(k, pool.take())
         if self.state_groups:
             seq.slot = self._free_slots.popleft()
             self._fresh_slots.add(seq.slot)
@@ -207,9 +230,9 @@ class CacheManager:
         for k, (table, pool) in enumerate(zip(seq.tables, self.pools)):
             if need - len(table) > pool.num_free:
                 raise OutOfPages(f"group {k}: need {need - len(table)} pages, have {pool.num_free}")
-        for table, pool in zip(seq.tables, self.pools):
+        for k, (table, pool) in enumerate(zip(seq.tables, self.pools)):
             while len(table) < need:
-                table.append(pool.take())
+                seq.append_page(k, pool.take())
         seq.num_tokens = num_tokens
         # A page that a window passed before it was ever needed is given back at once.
         self._release_passed(seq)
@@ -233,6 +256,7 @@ class CacheManager:
             for i in range(seq.released[k], upto):
                 self.pools[k].give(table[i])
                 table[i] = -1
+                seq.arrays[k][i] = 0
             seq.released[k] = max(seq.released[k], upto)
 
     def release(self, seq_id: int) -> None:

@@ -1,0 +1,286 @@
+// Paged grouped-query attention for decode rows (one query token per request) in
+// bfloat16 on the tensor cores, split over the keys.
+//
+// A decode step reads every cached key and value once and does little arithmetic with
+// them (2 * G * D multiply-adds per key for G query heads per KV head), so the kernel is
+// built around the memory system: a block is four warps that never synchronise with each
+// other until the very end; each warp owns every fourth 16-key tile of the block's key
+// range and streams it through a private three-stage cp.async ring in shared memory
+// (16 keys x D bf16 of K and of V per stage: one 4 KB page each at page size 16, D 128),
+// so that many kilobytes per SM are always in flight.  The G query heads of the group are
+// the rows of one m16 tile: S = Q K^T and O += P V are mma.sync m16n8k16 bf16 products
+// with float32 accumulators; softmax is float32 (base-2 exponentials of scores scaled by
+// log2(e) / sqrt(D)).  At the end the four warps' partial (max, sum, O) are merged in
+// shared memory and written out, or handed to the merge kernel when the keys of a
+// request are split over several blocks.
+//
+// Formulas: emberserve/attn/paged_torch.py:87-98 (decode form of base.py:105-128);
+// the reference's own kernel of this kind is attn/paged_triton.py:100-183 (split-K
+// partials merged by :185-208).
+#include "attention_decode_mma.cuh"
+
+namespace ems {
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_TK = 16;  // keys per warp tile
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_mma_kernel(const DecodeParams p) {
+    constexpr int CH = D / 8;                  // 16-byte chunks per key row
+    constexpr int ROW_BYTES = D * 2;
+    constexpr int TILE_BYTES = DEC_TK * ROW_BYTES;           // K (or V) of one 16-key tile
+    constexpr int WARP_BYTES = DEC_STAGES * 2 * TILE_BYTES;  // the warp's ring: K and V per stage
+    constexpr int KS = D / 16;                 // k-steps of Q.K^T, and pairs of d-tiles of P.V
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok = p.cu_q[b];
+    const int ctx = p.starts[b] + 1;           // keys visible to the query: [k_begin, ctx)
+    const int k_begin = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int G = p.G;
+
+    // this block's tiles (16 keys each, aligned to absolute positions), and this warp's
+    const int tile_lo = k_begin / DEC_TK, tile_hi = (ctx - 1) / DEC_TK;  // inclusive
+    const int ntiles = tile_hi - tile_lo + 1;
+    const int per_split = (ntiles + p.splits - 1) / p.splits;
+    const int t_begin = tile_lo + split * per_split;
+    const int t_end = min(tile_hi + 1, t_begin + per_split);
+    const int my_first = t_begin + warp;
+    const int my_count = my_first < t_end ? (t_end - my_first + DEC_WARPS - 1) / DEC_WARPS : 0;
+
+    unsigned char* ring = smem_raw + warp * WARP_BYTES;
+    const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
+    const int* table = p.bt + (size_t)b * p.bt_stride;
+
+    auto issue_tile = [&](int i) {  // stream the warp's i-th tile into stage i % DEC_STAGES
+        const int tile = my_first + i * DEC_WARPS;
+        const uint32_t kdst = ring_addr + (i % DEC_STAGES) * 2 * TILE_BYTES;
+        const uint32_t vdst = kdst + TILE_BYTES;
+        constexpr int ROWS_PER_IT = 32 / CH;
+#pragma unroll
+        for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
+            const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
+            const int key = tile * DEC_TK + row;
+            const bool valid = key >= k_begin && key < ctx;
+            size_t off = 0;
+            if (valid) {
+                const int page = table[key / p.page_size];
+                off = (((size_t)page * p.nkv + hk) * p.page_size + key % p.page_size) * D + chunk * 8;
+            }
+            const uint32_t sw = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+            cp_async16(kdst + sw, p.kc + off, valid);
+            cp_async16(vdst + sw, p.vc + off, valid);
+        }
+    };
+
+    // query fragments: rows of the m16 tile are the G heads of the group (rows >= G are zero)
+    uint32_t qf[KS][4];
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+        const bf16* qrow = p.q + (size_t)tok * p.q_stride + (size_t)hk * G * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int col = ks * 16 + c;
+            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(qrow + r0 * D + col) : 0u;
+            qf[ks][1] = r1 < G ? *reinterpret_cast<const uint32_t*>(qrow + r1 * D + col) : 0u;
+            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(qrow + r0 * D + col + 8) : 0u;
+            qf[ks][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(qrow + r1 * D + col + 8) : 0u;
+        }
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows lane/4 and lane/4 + 8
+
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES; ++s) {
+        if (s < my_count) issue_tile(s);
+        cp_async_commit();
+    }
+
+    for (int i = 0; i < my_count; ++i) {
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncwarp();
+        const uint32_t kst = ring_addr + (i % DEC_STAGES) * 2 * TILE_BYTES;
+        const uint32_t vst = kst + TILE_BYTES;
+        const int key0 = (my_first + i * DEC_WARPS) * DEC_TK;
+
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        {
+            const int mat = lane >> 3, r = lane & 7;
+            const int krow = (mat >> 1) * 8 + r;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int chunk = ks * 2 + (mat & 1);
+                uint32_t bfrag[4];
+                ldmatrix_x4(kst + krow * ROW_BYTES + ((chunk ^ (krow & 7)) << 4), bfrag);
+                mma_bf16_16816(s[0], qf[ks], bfrag[0], bfrag[1]);
+                mma_bf16_16816(s[1], qf[ks], bfrag[2], bfrag[3]);
+            }
+        }
+        // softmax of the tile, rows r0 (values [n][0..1]) and r1 (values [n][2..3])
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + n * 8 + (lane & 3) * 2 + e;
+                const bool visible = key >= k_begin && key < ctx;
+                s[n][e] = visible ? s[n][e] * p.scale_log2 : -INFINITY;
+                s[n][2 + e] = visible ? s[n][2 + e] * p.scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, s[n][e]);
+                mx1 = fmaxf(mx1, s[n][2 + e]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float a0 = mn0 == -INFINITY ? 1.f : exp2f(m0 - mn0);
+        const float a1 = mn1 == -INFINITY ? 1.f : exp2f(m1 - mn1);
+        m0 = mn0; m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                s[n][e] = s[n][e] == -INFINITY ? 0.f : exp2f(s[n][e] - mn0);
+                s[n][2 + e] = s[n][2 + e] == -INFINITY ? 0.f : exp2f(s[n][2 + e] - mn1);
+                ps0 += s[n][e];
+                ps1 += s[n][2 + e];
+            }
+        l0 = l0 * a0 + ps0;  // per-thread share of the row sum; the quad is summed at the end
+        l1 = l1 * a1 + ps1;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+        {
+            const int mat = lane >> 3, r = lane & 7;
+            const int vrow = (mat & 1) * 8 + r;
+#pragma unroll
+            for (int np = 0; np < KS; ++np) {
+                const int chunk = np * 2 + (mat >> 1);
+                uint32_t bfrag[4];
+                ldmatrix_x4_trans(vst + vrow * ROW_BYTES + ((chunk ^ (vrow & 7)) << 4), bfrag);
+                mma_bf16_16816(o[2 * np], pa, bfrag[0], bfrag[1]);
+                mma_bf16_16816(o[2 * np + 1], pa, bfrag[2], bfrag[3]);
+            }
+        }
+        __syncwarp();  // every lane is done with the stage before it is refilled
+        if (i + DEC_STAGES < my_count) issue_tile(i + DEC_STAGES);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncwarp();
+
+    // the warp's partial result into its own (now idle) ring: m[16], l[16], o[16][D]
+    float* wm = reinterpret_cast<float*>(ring);
+    float* wl = wm + 16;
+    float* wo = wl + 16;
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+        if ((lane & 3) == 0) { wm[r0] = m0; wm[r1] = m1; wl[r0] = l0; wl[r1] = l1; }
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            wo[r0 * D + n * 8 + c] = o[n][0];
+            wo[r0 * D + n * 8 + c + 1] = o[n][1];
+            wo[r1 * D + n * 8 + c] = o[n][2];
+            wo[r1 * D + n * 8 + c + 1] = o[n][3];
+        }
+    }
+    __syncthreads();
+
+    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w)
+            M = fmaxf(M, reinterpret_cast<const float*>(smem_raw + w * WARP_BYTES)[g]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float* base = reinterpret_cast<const float*>(smem_raw + w * WARP_BYTES);
+            const float mw = base[g];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L += base[16 + g] * f;
+            acc += base[32 + g * D + d] * f;
+        }
+        const size_t prow = (size_t)tok * p.nh + (size_t)hk * G + g;
+        if (p.splits == 1) {
+            p.out[prow * D + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            p.part_o[(prow * p.splits + split) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[(prow * p.splits + split) * 2] = M * 0.69314718055994531f;  // to natural-log units
+                p.part_ml[(prow * p.splits + split) * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+template <int D>
+int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t stream) {
+    constexpr int smem = DEC_WARPS * DEC_STAGES * 2 * DEC_TK * D * 2;
+    auto kernel = decode_attention_mma_kernel<D>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return EMS_ERR_LAUNCH;
+    if (p.nkv > 65535 || B > 65535) return EMS_ERR_SHAPE;
+    const dim3 grid((unsigned)p.splits, (unsigned)p.nkv, (unsigned)B);
+    kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(p);
+    return launch_status();
+}
+
+// Whether the tensor-core decode kernel takes this case; otherwise the generic kernel runs.
+bool decode_mma_supported(int dtype, int D, int G, long long q_stride, const void* q, const void* kc,
+                          const void* vc) {
+    if (dtype != EMS_BF16 || (D != 64 && D != 128) || G > 16) return false;
+    if ((q_stride * 2) % 4 || ((uintptr_t)q % 4) || ((uintptr_t)kc % 16) || ((uintptr_t)vc % 16)) return false;
+    return true;
+}
+
+int run_decode_mma(const DecodeParams& p, int B, int D, cudaStream_t stream) {
+    return D == 64 ? launch_decode_mma<64>(p, B, stream) : launch_decode_mma<128>(p, B, stream);
+}
+
+}  // namespace ems

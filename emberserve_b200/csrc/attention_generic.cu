@@ -16,6 +16,7 @@
 // memory.  Keys are walked in tiles of 32 whose boundaries are multiples of 32 in
 // absolute position: the order of additions for a query does not depend on how the
 // prompt was cut or on what else is in the batch.
+#include "attention_decode_mma.cuh"
 #include "common.cuh"
 
 namespace ems {
@@ -307,7 +308,8 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
                                    int bt_stride, int page_size, const int* cu_q, const int* starts,
                                    int B, int N, int nh, int nkv, int D, int window, float scale,
                                    int max_q_len, int splits, void* scratch, long long scratch_bytes,
-                                   cudaStream_t stream) {
+                                   int impl, cudaStream_t stream) {
+    // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel.
     if (B <= 0 || N <= 0) return EMS_OK;
     if (D <= 0 || D % 16 || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1)
         return EMS_ERR_SHAPE;
@@ -324,6 +326,24 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
             return EMS_ERR_SCRATCH;
         p.part_o = reinterpret_cast<float*>(scratch);
         p.part_ml = p.part_o + (size_t)N * nh * splits * D;
+    }
+    DecodeParams d;
+    d.q = reinterpret_cast<const bf16*>(q); d.out = reinterpret_cast<bf16*>(out);
+    d.kc = reinterpret_cast<const bf16*>(kcache); d.vc = reinterpret_cast<const bf16*>(vcache);
+    d.bt = block_tables; d.cu_q = cu_q; d.starts = starts; d.part_o = p.part_o; d.part_ml = p.part_ml;
+    d.q_stride = q_stride; d.bt_stride = bt_stride; d.page_size = page_size; d.nh = nh; d.nkv = nkv;
+    d.G = p.G; d.window = window; d.splits = splits;
+    d.scale_log2 = scale * 1.4426950408889634f;
+    if (impl == 0 && splits == 1 && max_q_len > 1 &&
+        prefill_mma_supported(dtype, D, q_stride, q, out, kcache, vcache))
+        return run_prefill_mma(d, B, D, max_q_len, stream);
+    if (impl == 0 && max_q_len == 1 && N == B &&
+        decode_mma_supported(dtype, D, p.G, q_stride, q, kcache, vcache)) {
+        const int rc = run_decode_mma(d, B, D, stream);
+        if (rc != EMS_OK || splits == 1) return rc;
+        attention_merge_kernel<bf16><<<(unsigned)((size_t)N * nh), D >= 128 ? 128 : 64, 0, stream>>>(
+            p.part_o, p.part_ml, reinterpret_cast<bf16*>(out), splits, D);
+        return launch_status();
     }
     if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
     if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
@@ -372,7 +392,7 @@ EMS_EXPORT int ems_paged_attention_static_scratch(
     if (splits <= 1)
         return ems_paged_attention(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride,
                                    page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
-                                   1, nullptr, 0, stream);
+                                   1, nullptr, 0, 0, stream);
     if (N <= 0 || nh <= 0 || D <= 0) return B <= 0 || N <= 0 ? EMS_OK : EMS_ERR_SHAPE;
     const long long need = ems_paged_attention_scratch_bytes(N, nh, D, splits);
     if (need > (long long)EMS_STATIC_SCRATCH_BYTES) return EMS_ERR_SCRATCH;
@@ -380,5 +400,5 @@ EMS_EXPORT int ems_paged_attention_static_scratch(
     if (scratch == nullptr) return EMS_ERR_LAUNCH;
     return ems_paged_attention(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride,
                                page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
-                               splits, scratch, (long long)EMS_STATIC_SCRATCH_BYTES, stream);
+                               splits, scratch, (long long)EMS_STATIC_SCRATCH_BYTES, 0, stream);
 }

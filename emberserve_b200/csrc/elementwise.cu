@@ -62,6 +62,81 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* residual,
     }
 }
 
+// The same, four columns per thread held in registers between the two phases (H a multiple
+// of 4, at most 4 * VPT * blockDim).  A row of a decode step is then one round trip to
+// memory instead of four dependent ones.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<const uint32_t*>(&a);
+        t.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = t;
+    }
+};
+
+template <typename T, int VPT>
+__global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* residual,
+                                       const void* __restrict__ weight, int w_dtype,
+                                       T* __restrict__ out, const int* __restrict__ rows, int H,
+                                       float eps, int write_residual) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : r;
+    float* res = residual + src * H;
+    const T* dl = delta ? delta + src * H : nullptr;
+    const bool store = dl && write_residual;
+    float x[VPT][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int col = (v * blockDim.x + threadIdx.x) * 4;
+        if (col < H) {
+            Vec4<float>::load(res + col, x[v]);
+            if (dl) {
+                float d[4];
+                Vec4<T>::load(dl + col, d);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) x[v][i] += d[i];
+            }
+            if (store) Vec4<float>::store(res + col, x[v]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ss += x[v][i] * x[v][i];
+        }
+    }
+    const float total = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+    T* o = out + r * H;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int col = (v * blockDim.x + threadIdx.x) * 4;
+        if (col < H) {
+            float w[4], y[4];
+            if (w_dtype == EMS_F32) Vec4<float>::load(reinterpret_cast<const float*>(weight) + col, w);
+            else Vec4<bf16>::load(reinterpret_cast<const bf16*>(weight) + col, w);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y[i] = round_to<T>(x[v][i] * rstd) * w[i];
+            Vec4<T>::store(o + col, y);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]
 
@@ -102,46 +177,41 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int nh, int nkv, int D
                                      T* __restrict__ kcache, T* __restrict__ vcache,
                                      const int* __restrict__ block_tables, int bt_stride,
                                      int page_size, int write_kv) {
+    // blockIdx.y: a q head (< nh), then a k head (< nh + nkv), then a v head
     const size_t n = blockIdx.x;
+    const int head = blockIdx.y;
     const int pos = positions[n];
     const int half = rot / 2;
     T* row = qkv + n * (size_t)(nh + 2 * nkv) * D;
     const float* cs = table ? table + (size_t)pos * half * 2 : nullptr;
-
-    // q heads, in place
-    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx % half;
-        T* x = row + (size_t)h * D;
-        const float c = cs[2 * i], s = cs[2 * i + 1];
-        const float x1 = to_f32<T>(x[i]), x2 = to_f32<T>(x[i + half]);
-        x[i] = from_f32<T>(x1 * c - x2 * s);
-        x[i + half] = from_f32<T>(x2 * c + x1 * s);
+    if (head < nh) {  // rotate q in place
+        T* x = row + (size_t)head * D;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float c = cs[2 * i], s = cs[2 * i + 1];
+            const float x1 = to_f32<T>(x[i]), x2 = to_f32<T>(x[i + half]);
+            x[i] = from_f32<T>(x1 * c - x2 * s);
+            x[i + half] = from_f32<T>(x2 * c + x1 * s);
+        }
+        return;
     }
-    if (!write_kv) return;
-
     const int page = block_tables[(size_t)row_of_token[n] * bt_stride + pos / page_size];
     const int slot = pos % page_size;
-    const T* k = row + (size_t)nh * D;
-    const T* v = k + (size_t)nkv * D;
-    // rotated part of k
-    for (int idx = threadIdx.x; idx < nkv * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx % half;
-        const T* x = k + (size_t)h * D;
+    if (head < nh + nkv) {  // rotate k into its cache slot
+        const int h = head - nh;
+        const T* x = row + (size_t)head * D;
         T* dst = kcache + (((size_t)page * nkv + h) * page_size + slot) * D;
-        const float c = cs[2 * i], s = cs[2 * i + 1];
-        const float x1 = to_f32<T>(x[i]), x2 = to_f32<T>(x[i + half]);
-        dst[i] = from_f32<T>(x1 * c - x2 * s);
-        dst[i + half] = from_f32<T>(x2 * c + x1 * s);
-    }
-    // unrotated tail of k, and all of v
-    const int tail = D - rot;
-    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
-        const int h = idx / tail, i = rot + idx % tail;
-        kcache[(((size_t)page * nkv + h) * page_size + slot) * D + i] = k[(size_t)h * D + i];
-    }
-    for (int idx = threadIdx.x; idx < nkv * D; idx += blockDim.x) {
-        const int h = idx / D, i = idx % D;
-        vcache[(((size_t)page * nkv + h) * page_size + slot) * D + i] = v[idx];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float c = cs[2 * i], s = cs[2 * i + 1];
+            const float x1 = to_f32<T>(x[i]), x2 = to_f32<T>(x[i + half]);
+            dst[i] = from_f32<T>(x1 * c - x2 * s);
+            dst[i + half] = from_f32<T>(x2 * c + x1 * s);
+        }
+        for (int i = rot + threadIdx.x; i < D; i += blockDim.x) dst[i] = x[i];
+    } else {  // copy v
+        const int h = head - nh - nkv;
+        const T* x = row + (size_t)head * D;
+        T* dst = vcache + (((size_t)page * nkv + h) * page_size + slot) * D;
+        for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = x[i];
     }
 }
 
@@ -179,6 +249,27 @@ EMS_EXPORT int ems_add_rmsnorm(const void* delta, float* residual, const void* w
     if (num_out <= 0) return EMS_OK;
     if (w_dtype != EMS_F32 && w_dtype != EMS_BF16) return EMS_ERR_DTYPE;
     // The block size is a function of H alone, so a row's sum never depends on the batch.
+    if (H % 4 == 0 && H <= 16384 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0 && ((uintptr_t)delta % 16) == 0) {
+        const int vecs = H / 4;
+        const int vpt = (vecs + 1023) / 1024;                       // 1..4
+        const int threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;  // <= 1024
+#define EMS_NORM_VEC(T, V)                                                                          \
+    add_rmsnorm_vec_kernel<T, V><<<num_out, threads, 0, stream>>>((const T*)delta, residual, weight, \
+                                                                  w_dtype, (T*)out, rows, H, eps,     \
+                                                                  write_residual)
+        if (dtype == EMS_F32) {
+            if (vpt == 1) EMS_NORM_VEC(float, 1); else if (vpt == 2) EMS_NORM_VEC(float, 2);
+            else if (vpt == 3) EMS_NORM_VEC(float, 3); else EMS_NORM_VEC(float, 4);
+        } else if (dtype == EMS_BF16) {
+            if (vpt == 1) EMS_NORM_VEC(bf16, 1); else if (vpt == 2) EMS_NORM_VEC(bf16, 2);
+            else if (vpt == 3) EMS_NORM_VEC(bf16, 3); else EMS_NORM_VEC(bf16, 4);
+        } else {
+            return EMS_ERR_DTYPE;
+        }
+#undef EMS_NORM_VEC
+        return launch_status();
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (dtype == EMS_F32)
         add_rmsnorm_kernel<float><<<num_out, threads, 0, stream>>>(
@@ -221,12 +312,16 @@ EMS_EXPORT int ems_rope_kv_write(void* qkv, int dtype, int N, int nh, int nkv, i
     if (N <= 0) return EMS_OK;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1)) return EMS_ERR_SHAPE;
     if (rotary_dim > 0 && table == nullptr) return EMS_ERR_SHAPE;
+    const int heads = write_kv ? nh + 2 * nkv : nh;
+    if (heads > 65535) return EMS_ERR_SHAPE;
+    const dim3 grid(N, heads);
+    const int threads = D >= 128 ? 64 : 32;
     if (dtype == EMS_F32)
-        rope_kv_write_kernel<float><<<N, 128, 0, stream>>>(
+        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
             (float*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (float*)kcache,
             (float*)vcache, block_tables, bt_stride, page_size, write_kv);
     else if (dtype == EMS_BF16)
-        rope_kv_write_kernel<bf16><<<N, 128, 0, stream>>>(
+        rope_kv_write_kernel<bf16><<<grid, threads, 0, stream>>>(
             (bf16*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (bf16*)kcache,
             (bf16*)vcache, block_tables, bt_stride, page_size, write_kv);
     else

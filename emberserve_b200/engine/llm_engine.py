@@ -52,6 +52,8 @@ class LLMEngine:
         self._step_count = 0
         self.keep_stats = False
         self.stats: list[StepStats] = []
+        if config.enable_cuda_graphs:
+            runner.enable_graphs(config.max_model_len, config.max_num_seqs)
 
     @classmethod
     def from_pretrained(cls, model_dir: str | os.PathLike, engine_config: EngineConfig | None = None,

@@ -113,7 +113,9 @@ class ModelRunner:
         has_state = any(not g.paged for g in self.groups)
         self.cache = CacheManager(self.groups, num_pages, page_size,
                                   num_state_slots if has_state else 0)
-        self.storage = CacheStorage(self.groups, [num_pages] * len(paged), page_size,
+        # One page more than the manager hands out: rows that pad a CUDA-graph bucket write there.
+        self.scratch_page = num_pages
+        self.storage = CacheStorage(self.groups, [num_pages + 1] * len(paged), page_size,
                                     num_state_slots if has_state else 0, dtype, self.device)
         self.scratch = ScratchArena(self.device)
         self._meta_dev = torch.empty(1 << 12, dtype=torch.int32, device=self.device)
@@ -124,6 +126,20 @@ class ModelRunner:
         self.steps_run = 0
         self.last_meta_bytes = 0  # bytes of the last step's host-to-device copy
         self.use_graphs = False
+        self.graphs = None
+        self._has_state = has_state
+
+    def enable_graphs(self, max_ctx_len: int, max_rows: int) -> bool:
+        """Replay pure-decode steps of up to `max_rows` rows and contexts up to `max_ctx_len`
+        from CUDA graphs (captured per row-count bucket at first use).  Models with
+        fixed-size state per request run eagerly."""
+        from emberserve_b200.engine.graphs import DecodeGraphs
+
+        if not self._on_cuda or self._has_state:
+            return False
+        self.graphs = DecodeGraphs(self, min(max_ctx_len, self.max_positions), max_rows)
+        self.use_graphs = True
+        return True
 
     # ---- construction ----------------------------------------------------------------------
     @classmethod
@@ -208,12 +224,11 @@ class ModelRunner:
         npaged = len(self.cache.pools)
         tables = []
         for k in range(npaged):
-            per_row = [self.cache.table(r.seq_id, k) for r in rows]
-            width = max(1, max(len(t) for t in per_row))
+            per_row = [self.cache.table_array(r.seq_id, k) for r in rows]
+            width = max(1, max(t.size for t in per_row))
             arr = np.zeros((b, width), dtype=np.int32)
             for i, t in enumerate(per_row):
-                arr[i, :len(t)] = t
-            np.maximum(arr, 0, out=arr)  # pages given back (-1) are never read; keep ids valid
+                arr[i, :t.size] = t  # pages given back read 0: a valid id that is never read
             tables.append(arr)
         slots = np.asarray([max(0, self.cache.state_slot(r.seq_id)) for r in rows], dtype=np.int32)
 
@@ -267,6 +282,12 @@ class ModelRunner:
             return torch.empty(0, self.vocab_size, dtype=torch.float32, device=self.device)
         self._check_rows(rows)
         with (torch.cuda.device(self.device) if self._on_cuda else contextlib.nullcontext()):
+            if self.use_graphs and self.graphs.usable(rows):
+                logits = self.graphs.run(rows)
+                for r in rows:
+                    self.cache.commit(r.seq_id, r.start + 1)
+                self.steps_run += 1
+                return logits
             fresh = self.cache.take_fresh_slots()
             if fresh:
                 self.storage.zero_slots(fresh)

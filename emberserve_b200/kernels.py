@@ -62,7 +62,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_table": [P, P, I, I, P],
         "ems_rope_kv_write": [P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, P],
         "ems_to_f32": [P, I, P, L, P],
-        "ems_paged_attention": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I, P, L, P],
+        "ems_paged_attention": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I, P, L, I, P],
         "ems_argmax": [P, P, I, I, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
@@ -208,10 +208,11 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
                     block_tables: torch.Tensor, cu_q: torch.Tensor, starts: torch.Tensor,
                     num_rows: int, num_tokens: int, num_heads: int, num_kv_heads: int,
                     head_dim: int, scale: float, max_q_len: int, window: int | None = None,
-                    splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+                    splits: int = 1, scratch: torch.Tensor | None = None, generic: bool = False) -> None:
     """Causal grouped-query attention of every packed query over its request's pages.
     `q` is a [N, stride] tensor whose first nh*D columns are the queries (a view of the
-    qkv buffer is fine); `out` is [N, nh*D]."""
+    qkv buffer is fine); `out` is [N, nh*D].  `generic=True` forces the generic kernel where
+    a faster one would take the case (tests compare the two)."""
     assert q.stride(1) == 1 and out.is_contiguous() and q.dtype == out.dtype == kcache.dtype
     page_size = kcache.shape[2]
     assert kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
@@ -223,7 +224,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
         _i32(cu_q, "cu_q"), _i32(starts, "starts"), num_rows, num_tokens, num_heads, num_kv_heads,
         head_dim, int(window or 0), float(scale), max_q_len, splits,
         _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
-        _stream()), "paged_attention", 2 if splits > 1 else 1)
+        1 if generic else 0, _stream()), "paged_attention", 2 if splits > 1 else 1)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

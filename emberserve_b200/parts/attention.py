@@ -26,7 +26,7 @@ from emberserve_b200.parts.linear import linear
 # Blocks wanted in flight before keys are split among several blocks of a decode step:
 # two per SM of a B200.
 _TARGET_BLOCKS = 2 * 148
-_MAX_SPLITS = 16
+_MAX_SPLITS = 32
 _MIN_KEYS_PER_SPLIT = 256
 
 
@@ -106,16 +106,26 @@ class GQAttention(Mixer):
                         ctx.row_of_token, table, rot, cache.k, cache.v, cache.block_tables,
                         cache.page_size, write_kv=cache.write)
         out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
-        splits, scratch = 1, None
-        if ctx.max_q_len == 1:
-            splits = ctx.extra.get("decode_splits") or decode_splits(
-                ctx.num_rows, s.num_kv_heads, ctx.max_ctx_len)
+        # Rows that bring one token and stand first (the scheduler puts decoding requests
+        # first) go to the split-key decode kernel; the rest, prompt portions, follow.
+        b = ctx.num_rows
+        nd = 0
+        while nd < b and ctx.q_lens[nd] == 1:
+            nd += 1
+        if nd > 0:
+            splits, scratch = 1, None
+            max_ctx = ctx.max_ctx_len if nd == b else max(st + 1 for st in ctx.start_list[:nd])
+            splits = ctx.extra.get("decode_splits") or decode_splits(nd, s.num_kv_heads, max_ctx)
             if splits > 1:
-                nbytes = K.attention_scratch_bytes(n, s.num_heads, s.head_dim, splits)
+                nbytes = K.attention_scratch_bytes(nd, s.num_heads, s.head_dim, splits)
                 scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)
-        K.paged_attention(qkv, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts,
-                          ctx.num_rows, n, s.num_heads, s.num_kv_heads, s.head_dim, self.scale,
-                          ctx.max_q_len, window=cache.window, splits=splits, scratch=scratch)
+            K.paged_attention(qkv, out, cache.k, cache.v, cache.block_tables[:nd], ctx.cu_q[:nd + 1],
+                              ctx.starts[:nd], nd, nd, s.num_heads, s.num_kv_heads, s.head_dim,
+                              self.scale, 1, window=cache.window, splits=splits, scratch=scratch)
+        if nd < b:
+            K.paged_attention(qkv, out, cache.k, cache.v, cache.block_tables[nd:], ctx.cu_q[nd:],
+                              ctx.starts[nd:], b - nd, n, s.num_heads, s.num_kv_heads, s.head_dim,
+                              self.scale, max(ctx.q_lens[nd:]), window=cache.window)
         y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
         linear(out, self.wo, None, y)
         return y

@@ -55,7 +55,7 @@ def sharp_dirs(tmp_path_factory):
 
 # ---- generation through the entry point ---------------------------------------------------------
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_greedy_generation_equals_plain(sharp_dirs, name):
     from emberserve_b200 import SamplingParams
 
@@ -110,7 +110,7 @@ def test_cpu_device_is_refused(model_dirs):
 # ---- long decoding and the first tokens ---------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_c", "tiny_d"])
 def test_long_decoding_token_by_token(sharp_dirs, name, dtype):
     """A short prompt and then every further token alone, across many pages (and, for the
     windowed model, far past the window, while its pages are given back)."""
@@ -156,6 +156,33 @@ def test_first_tokens_of_a_sequence(sharp_dirs, dtype):
             assert np.abs(got[(rid, p)] - want[p]).max() <= TOL[dtype] * np.abs(want).max()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+def test_decode_steps_replayed_from_cuda_graphs(model_dirs, name, dtype):
+    """With CUDA graphs on, steps made of single tokens are replayed from a graph of their
+    row-count bucket (padded with rows that write to a scratch page); the logits still
+    equal the plain implementation's, in a trace that mixes such steps with prompt portions
+    and that hands pages from finished requests to new ones."""
+    from emberserve_b200.engine.replay import TraceReplayer
+
+    cfg = ALL[name]
+    reqs = rc.make_requests(cfg.vocab_size, [30, 41, 17, 55, 23, 38], seed=12)
+    cfgd, w = plain.read_model_dir(model_dirs[name])
+    steps = rc.mixed(reqs, max_live=3, seed=2, decode_tail=20)
+    ps = PAGE_SIZES[name]
+    runner = _runner(model_dirs[name], dtype, ps, TraceReplayer.pages_for(rc.max_live_tokens(steps), ps))
+    assert runner.enable_graphs(cfg.max_position_embeddings, 4)
+    rp = TraceReplayer(runner)
+    got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+    assert runner.graphs._graphs, "no step went through a graph"
+    assert {1, 2, 4} & set(runner.graphs._graphs), sorted(runner.graphs._graphs)
+    for rid, toks in reqs:
+        want = plain.forward_logits(cfgd, w, toks).numpy()
+        err = max(float(np.abs(got[(rid, p)] - want[p]).max()) for p in range(len(toks)))
+        assert err <= TOL[dtype] * float(np.abs(want).max()), (rid, err)
+    runner.cache.check()
+
+
 # ---- faults that random weights would hide ------------------------------------------------------
 
 def _with_attention_pointing_at(model_dir, out_dir, gain=5.0):
@@ -174,7 +201,7 @@ def _with_attention_pointing_at(model_dir, out_dir, gain=5.0):
     return out_dir
 
 
-@pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_c", "tiny_d"])
 def test_peaked_attention_far_keys_window_edge_page_edge(model_dirs, tmp_path, name):
     """With peaked attention a skipped key, an off-by-one at the window's edge or a wrong
     slot at a page's edge changes logits by far more than the tolerance.  The sequence is

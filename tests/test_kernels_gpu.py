@@ -207,28 +207,102 @@ def test_paged_attention_decode_splits(dtype, splits, window):
     torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else tol(dtype)))
 
 
+@pytest.mark.parametrize("nh,nkv,d,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (16, 1, 128, 16), (8, 8, 64, 8),
+                                         (7, 1, 128, 4), (6, 3, 64, 32), (12, 4, 128, 1), (4, 2, 64, 48)])
+@pytest.mark.parametrize("splits,window", [(1, None), (5, None), (2, 100), (16, 33), (1, 16)])
+def test_decode_tensor_core_kernel(nh, nkv, d, ps, splits, window):
+    """The bfloat16 tensor-core decode kernel (head sizes 64 and 128, up to 16 query heads per
+    KV head, any page size) against the restatement and against the generic kernel; contexts
+    of 1 key, at page and tile edges, and long ones."""
+    dtype = torch.bfloat16
+    q_lens = [1] * 9
+    starts = [0, 1, 15, 16, 17, 63, 64, 1500, 700]
+    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, splits, peaky=True)
+    torch.testing.assert_close(got, want, **tol(dtype))
+    g = torch.Generator(device="cuda").manual_seed(11)
+    # the same inputs through the generic kernel
+    b, n = len(q_lens), len(q_lens)
+    width = max(-(-(s + 1) // ps) for s in starts) + 1
+    pages = b * width
+    perm = torch.randperm(pages, device=dev(), generator=g).view(b, width).to(torch.int32)
+    kc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    vc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    qkv = (torch.randn(n, (nh + 2 * nkv) * d, device=dev(), generator=g) * 3).to(dtype)
+    cu = torch.arange(b + 1, device=dev(), dtype=torch.int32)
+    st = torch.tensor(starts, device=dev(), dtype=torch.int32)
+    scratch = torch.empty(max(1, K().attention_scratch_bytes(n, nh, d, splits) // 4), device=dev())
+    outs = []
+    for generic in (False, True):
+        out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+        K().paged_attention(qkv, out, kc, vc, perm, cu, st, b, n, nh, nkv, d, 1 / math.sqrt(d), 1,
+                            window=window, splits=splits, scratch=scratch, generic=generic)
+        outs.append(out.float())
+    torch.testing.assert_close(outs[0], outs[1], **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (20, 1, 128, 16), (3, 3, 64, 8),
+                                         (7, 1, 128, 4), (6, 3, 64, 32), (8, 4, 128, 1), (2, 1, 64, 48)])
+@pytest.mark.parametrize("window", [None, 1, 40, 64, 65, 200])
+def test_prefill_tensor_core_kernel(nh, nkv, d, ps, window):
+    """The bfloat16 tensor-core kernel for prompt portions (head sizes 64 and 128, any
+    group count and page size): fresh prompts, later portions over cached context, single
+    tokens, lengths around the 64-key tile and the 16-row warp tile; against the restatement
+    and the generic kernel."""
+    dtype = torch.bfloat16
+    q_lens = [130, 1, 64, 9, 2, 65, 1, 33]
+    starts = [0, 200, 64, 119, 0, 63, 0, 300]
+    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=21, peaky=True)
+    torch.testing.assert_close(got, want, **tol(dtype))
+
+
+def test_prefill_tensor_core_kernel_equals_generic_kernel():
+    dtype, nh, nkv, d, ps = torch.bfloat16, 28, 4, 128, 16
+    g = torch.Generator(device="cuda").manual_seed(12)
+    q_lens, starts = [257, 3, 1], [31, 500, 77]
+    b, n = len(q_lens), sum(q_lens)
+    width = max(-(-(s + q) // ps) for s, q in zip(starts, q_lens)) + 1
+    perm = torch.randperm(b * width, device=dev(), generator=g).view(b, width).to(torch.int32)
+    kc = torch.randn(b * width, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    vc = torch.randn(b * width, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    qkv = (torch.randn(n, (nh + 2 * nkv) * d, device=dev(), generator=g) * 2).to(dtype)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=dev(), dtype=torch.int32)
+    st = torch.tensor(starts, device=dev(), dtype=torch.int32)
+    outs = []
+    for generic in (False, True):
+        out = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+        K().paged_attention(qkv, out, kc, vc, perm, cu, st, b, n, nh, nkv, d, 1 / math.sqrt(d), max(q_lens),
+                            generic=generic)
+        outs.append(out.float())
+    torch.testing.assert_close(outs[0], outs[1], **tol(dtype))
+
+
 def test_paged_attention_far_key_stands_out():
     """One far key among hundreds carries the whole result: its score is made to dominate,
     so a kernel that skipped or misplaced it would be plainly wrong."""
-    dtype = torch.float32
+    _far_key_case(torch.float32)
+    _far_key_case(torch.bfloat16)  # decode rows in bfloat16 run on the tensor-core kernel
+
+
+def _far_key_case(dtype):
     nh, nkv, d, ps, ctx = 4, 1, 64, 16, 600
     for far in (0, 15, 16, 511, 512, 598):
         g = torch.Generator(device="cuda").manual_seed(far)
         pages = 64
         perm = torch.randperm(pages, device=dev(), generator=g)[None, :].to(torch.int32)
-        kc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g) * 0.1
-        vc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g)
-        q = torch.randn(1, (nh + 2) * d, device=dev(), generator=g)
+        kc = (torch.randn(pages, nkv, ps, d, device=dev(), generator=g) * 0.1).to(dtype)
+        vc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+        q = torch.randn(1, (nh + 2) * d, device=dev(), generator=g).to(dtype)
         page, slot = int(perm[0, far // ps]), far % ps
-        kc[page, 0, slot] = q[0, :d] * 50.0  # head 0 points at key `far`
+        kc[page, 0, slot] = (q[0, :d].float() * 50.0).to(dtype)  # head 0 points at key `far`
         cu = torch.tensor([0, 1], device=dev(), dtype=torch.int32)
         st = torch.tensor([ctx - 1], device=dev(), dtype=torch.int32)
-        out = torch.empty(1, nh * d, device=dev())
+        out = torch.empty(1, nh * d, device=dev(), dtype=dtype)
         for splits in (1, 4):
             scratch = torch.empty(max(1, K().attention_scratch_bytes(1, nh, d, splits) // 4), device=dev())
             K().paged_attention(q, out, kc, vc, perm, cu, st, 1, 1, nh, nkv, d, 1.0, 1, splits=splits,
                                 scratch=scratch)
-            torch.testing.assert_close(out[0, :d], vc[page, 0, slot], rtol=1e-4, atol=1e-4)
+            t = 1e-4 if dtype == torch.float32 else 2e-2
+            torch.testing.assert_close(out[0, :d].float(), vc[page, 0, slot].float(), rtol=t, atol=t)
 
 
 @pytest.mark.parametrize("r,v", [(1, 7), (5, 1000), (64, 152064), (3, 151936)])

@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"tiny_a": [5, 11, 17, 40, 23, 64, 100], "tiny_b": [1, 9, 23, 40, 70, 33, 130],
-           "tiny_c": [3, 48, 90, 61, 35, 77, 200]}
+           "tiny_c": [3, 48, 90, 61, 35, 77, 200], "tiny_d": [2, 70, 141, 64, 33, 90, 260]}
 # Largest |logit difference| allowed, as a fraction of the largest |logit| of the model.
 TOL = {torch.float32: 3e-5, torch.bfloat16: 3e-2}
 
@@ -76,7 +76,7 @@ def cases(model_dirs):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_cut_equals_plain(model_dirs, cases, name, cut, dtype):
     reqs, want, scale = cases[name]
     steps = {"whole": rc.whole, "tail": lambda r: rc.bulk_then_tail(r, 32), "portions": rc.portions,

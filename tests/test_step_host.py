@@ -17,7 +17,7 @@ from tiny_configs import ALL, PAGE_SIZES
 from emberserve_b200.engine.replay import TraceReplayer
 
 LENGTHS = {"tiny_a": [5, 11, 17, 40, 23, 64], "tiny_b": [1, 9, 23, 40, 70, 33],
-           "tiny_c": [3, 48, 90, 61, 35, 77]}
+           "tiny_c": [3, 48, 90, 61, 35, 77], "tiny_d": [2, 70, 141, 64, 33, 90]}
 
 
 @pytest.fixture(autouse=True)
@@ -46,7 +46,7 @@ def _oracle(model_dir, reqs):
     return {rid: plain.forward_logits(cfg, w, toks, torch.float64).numpy() for rid, toks in reqs}
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_all_cuts_equal_plain(model_dirs, name):
     cfg = ALL[name]
     reqs = rc.make_requests(cfg.vocab_size, LENGTHS[name], seed=7)
