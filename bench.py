@@ -294,6 +294,84 @@ def run_ours(args) -> dict:
     }
 
 
+def run_kernel(args) -> dict:
+    """One kernel alone at the geometry of the 7B shape, inputs larger than L2, timed with
+    CUDA events (median of the iterations): achieved bandwidth or arithmetic rate against
+    the measured peaks.  This is also the small case that ncu profiles are taken on."""
+    import math
+
+    import torch
+
+    from emberserve_b200 import kernels as K
+
+    peaks = measured_peaks()
+    s = SHAPE_7B
+    nh, nkv, d, ps = s["num_attention_heads"], s["num_key_value_heads"], s["head_dim"], PAGE_SIZE
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+    iters = max(3, args.steps)
+
+    def timed(fn, reps: int = 8) -> float:
+        """Median device time of one call.  `reps` calls are captured in a CUDA graph and the
+        replay is timed, so that the host's launch cost is not what is measured; every call
+        of a replay reads its inputs again from memory (they exceed L2 where it matters)."""
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        times = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / reps)
+        return statistics.median(times)
+
+    if args.kernel == "decode_attention":
+        b, ctx = args.batch, args.context
+        width = ctx // ps + 1
+        pages = b * width
+        kc = torch.randn(pages, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
+        vc = torch.randn(pages, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
+        bt = torch.randperm(pages, device=dev, generator=g).view(b, width).to(torch.int32)
+        qkv = torch.randn(b, (nh + 2 * nkv) * d, device=dev, generator=g).to(torch.bfloat16)
+        out = torch.empty(b, nh * d, device=dev, dtype=torch.bfloat16)
+        cu = torch.arange(b + 1, device=dev, dtype=torch.int32)
+        st = torch.full((b,), ctx - 1, device=dev, dtype=torch.int32)
+        from emberserve_b200.parts.attention import decode_splits
+
+        splits = args.splits or decode_splits(b, nkv, ctx)
+        scratch = torch.empty(max(1, K.attention_scratch_bytes(b, nh, d, splits) // 4), device=dev)
+        ms = timed(lambda: K.paged_attention(qkv, out, kc, vc, bt, cu, st, b, b, nh, nkv, d,
+                                             1 / math.sqrt(d), 1, splits=splits, scratch=scratch))
+        nbytes = 2 * b * ctx * nkv * d * 2
+        return {"kernel": "decode_attention", "batch": b, "context": ctx, "splits": splits, "ms": ms,
+                "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
+    if args.kernel == "prefill_attention":
+        t = args.context
+        width = t // ps + 1
+        kc = torch.randn(width, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
+        vc = torch.randn(width, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
+        bt = torch.randperm(width, device=dev, generator=g).view(1, width).to(torch.int32)
+        qkv = torch.randn(t, (nh + 2 * nkv) * d, device=dev, generator=g).to(torch.bfloat16)
+        out = torch.empty(t, nh * d, device=dev, dtype=torch.bfloat16)
+        cu = torch.tensor([0, t], device=dev, dtype=torch.int32)
+        st = torch.zeros(1, device=dev, dtype=torch.int32)
+        ms = timed(lambda: K.paged_attention(qkv, out, kc, vc, bt, cu, st, 1, t, nh, nkv, d,
+                                             1 / math.sqrt(d), t))
+        flops = 4 * nh * d * t * t / 2
+        return {"kernel": "prefill_attention", "tokens": t, "ms": ms, "tflops": flops / ms / 1e9,
+                "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+    raise SystemExit(f"unknown kernel {args.kernel!r}")
+
+
 def run_reference(args) -> dict:
     """The unmodified reference, installed under baseline/_ref, through its own LLMEngine."""
     ref = ROOT / "baseline" / "_ref"
@@ -388,8 +466,12 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
-                    help="run one small part only (for profiling): decode at --batch, or the prefill")
+    ap.add_argument("--only", choices=["decode", "prefill", "kernel"], default=None,
+                    help="run one small part only (for profiling): decode at --batch, the prefill, or "
+                         "one kernel alone (--kernel)")
+    ap.add_argument("--kernel", choices=["decode_attention", "prefill_attention"], default="decode_attention")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
+    ap.add_argument("--splits", type=int, default=0, help="with --only kernel: key splits (0 = the engine's rule)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --only: add device time per kernel name (torch profiler)")
     ap.add_argument("--layers", type=int, default=None,
@@ -400,6 +482,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.only == "kernel":
+        print(json.dumps(run_kernel(args)))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0

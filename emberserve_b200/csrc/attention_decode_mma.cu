@@ -46,12 +46,21 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x of a float32 by the special-function unit (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int D>
+// PAGE16: the page size is a multiple of 16, so the 16 keys of a tile (tiles are aligned to
+// multiples of 16 in absolute position) lie in one page, contiguously: one block-table
+// lookup per tile instead of one per key row.
+template <int D, bool PAGE16>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_mma_kernel(const DecodeParams p) {
     constexpr int CH = D / 8;                  // 16-byte chunks per key row
@@ -86,6 +95,23 @@ decode_attention_mma_kernel(const DecodeParams p) {
         const uint32_t kdst = ring_addr + (i % DEC_STAGES) * 2 * TILE_BYTES;
         const uint32_t vdst = kdst + TILE_BYTES;
         constexpr int ROWS_PER_IT = 32 / CH;
+        if (PAGE16) {
+            const int key0 = tile * DEC_TK;
+            const int page = table[key0 / p.page_size];
+            const size_t base = (((size_t)page * p.nkv + hk) * p.page_size + key0 % p.page_size) * D;
+            const bf16* ksrc = p.kc + base + lane * 8;   // the tile is 16 * D contiguous elements
+            const bf16* vsrc = p.vc + base + lane * 8;
+#pragma unroll
+            for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
+                const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
+                const int key = key0 + row;
+                const bool valid = key >= k_begin && key < ctx;
+                const uint32_t sw = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+                cp_async16(kdst + sw, valid ? ksrc + it * 256 : p.kc, valid);
+                cp_async16(vdst + sw, valid ? vsrc + it * 256 : p.vc, valid);
+            }
+            return;
+        }
 #pragma unroll
         for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
             const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
@@ -150,34 +176,35 @@ decode_attention_mma_kernel(const DecodeParams p) {
                 mma_bf16_16816(s[1], qf[ks], bfrag[2], bfrag[3]);
             }
         }
-        // softmax of the tile, rows r0 (values [n][0..1]) and r1 (values [n][2..3])
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        // softmax of the tile, rows r0 (values [n][0..1]) and r1 (values [n][2..3]), in base 2:
+        // p = 2^(s * scale_log2 - m), one FMA and one ex2 per score
+        if (key0 < k_begin || key0 + DEC_TK > ctx) {  // only the first and the last tile need a mask
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key0 + n * 8 + (lane & 3) * 2 + e;
-                const bool visible = key >= k_begin && key < ctx;
-                s[n][e] = visible ? s[n][e] * p.scale_log2 : -INFINITY;
-                s[n][2 + e] = visible ? s[n][2 + e] * p.scale_log2 : -INFINITY;
-                mx0 = fmaxf(mx0, s[n][e]);
-                mx1 = fmaxf(mx1, s[n][2 + e]);
-            }
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key0 + n * 8 + (lane & 3) * 2 + e;
+                    if (key < k_begin || key >= ctx) { s[n][e] = -INFINITY; s[n][2 + e] = -INFINITY; }
+                }
+        }
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float a0 = mn0 == -INFINITY ? 1.f : exp2f(m0 - mn0);
-        const float a1 = mn1 == -INFINITY ? 1.f : exp2f(m1 - mn1);
+        const float sl2 = p.scale_log2;
+        const float mn0 = fmaxf(m0, mx0 * sl2), mn1 = fmaxf(m1, mx1 * sl2);
+        const float mb0 = mn0 == -INFINITY ? 0.f : mn0, mb1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float a0 = ex2_approx(m0 - mb0), a1 = ex2_approx(m1 - mb1);
         m0 = mn0; m1 = mn1;
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                s[n][e] = s[n][e] == -INFINITY ? 0.f : exp2f(s[n][e] - mn0);
-                s[n][2 + e] = s[n][2 + e] == -INFINITY ? 0.f : exp2f(s[n][2 + e] - mn1);
+                s[n][e] = ex2_approx(fmaf(s[n][e], sl2, -mb0));
+                s[n][2 + e] = ex2_approx(fmaf(s[n][2 + e], sl2, -mb1));
                 ps0 += s[n][e];
                 ps1 += s[n][2 + e];
             }
@@ -258,10 +285,10 @@ decode_attention_mma_kernel(const DecodeParams p) {
     }
 }
 
-template <int D>
+template <int D, bool PAGE16>
 int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t stream) {
     constexpr int smem = DEC_WARPS * DEC_STAGES * 2 * DEC_TK * D * 2;
-    auto kernel = decode_attention_mma_kernel<D>;
+    auto kernel = decode_attention_mma_kernel<D, PAGE16>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return EMS_ERR_LAUNCH;
@@ -280,7 +307,9 @@ bool decode_mma_supported(int dtype, int D, int G, long long q_stride, const voi
 }
 
 int run_decode_mma(const DecodeParams& p, int B, int D, cudaStream_t stream) {
-    return D == 64 ? launch_decode_mma<64>(p, B, stream) : launch_decode_mma<128>(p, B, stream);
+    if (p.page_size % 16 == 0)
+        return D == 64 ? launch_decode_mma<64, true>(p, B, stream) : launch_decode_mma<128, true>(p, B, stream);
+    return D == 64 ? launch_decode_mma<64, false>(p, B, stream) : launch_decode_mma<128, false>(p, B, stream);
 }
 
 }  // namespace ems

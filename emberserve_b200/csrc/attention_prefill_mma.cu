@@ -41,12 +41,20 @@ __device__ __forceinline__ void pf_mma(float (&c)[4], const uint32_t (&a)[4], ui
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x of a float32 by the special-function unit (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float pf_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int D>
+// PAGE16: the page size is a multiple of 16, so every aligned group of 16 keys of a tile
+// lies in one page, contiguously: a warp fetches one such group with one block-table lookup.
+template <int D, bool PAGE16>
 __global__ void __launch_bounds__(PF_WARPS * 32)
 prefill_attention_mma_kernel(const DecodeParams p) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
@@ -86,6 +94,31 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     auto issue_tile = [&](int t) {
         const uint32_t kdst = kv_s + (t & 1) * 2 * KV_BYTES, vdst = kdst + KV_BYTES;
         const int kt = kt0 + t * PF_BK;
+        if (PAGE16) {
+            // warp w fetches keys [kt + 16 w', kt + 16 w' + 16) for w' = w, w + 4, ... : one page each
+            constexpr int ROWS_PER_IT = 32 / CH;
+            for (int grp = warp; grp < PF_BK / 16; grp += PF_WARPS) {
+                const int key0 = kt + grp * 16;
+                const bool any = key0 < k_end && key0 + 16 > k_begin;
+                size_t base = 0;
+                if (any) {
+                    const int page = table[key0 / p.page_size];
+                    base = (((size_t)page * p.nkv + hk) * p.page_size + key0 % p.page_size) * D;
+                }
+                const bf16* ksrc = p.kc + base + lane * 8;
+                const bf16* vsrc = p.vc + base + lane * 8;
+#pragma unroll
+                for (int it = 0; it < 16 / ROWS_PER_IT; ++it) {
+                    const int row = grp * 16 + it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
+                    const int key = kt + row;
+                    const bool valid = key >= k_begin && key < k_end;
+                    const uint32_t sw = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+                    pf_cp_async16(kdst + sw, valid ? ksrc + it * 256 : p.kc, valid);
+                    pf_cp_async16(vdst + sw, valid ? vsrc + it * 256 : p.vc, valid);
+                }
+            }
+            return;
+        }
         for (int idx = tid; idx < PF_BK * CH; idx += PF_WARPS * 32) {
             const int row = idx / CH, chunk = idx % CH;
             const int key = kt + row;
@@ -154,39 +187,44 @@ prefill_attention_mma_kernel(const DecodeParams p) {
                     }
                 }
             }
-            // mask, scale, online softmax
-            const bool full = kt + PF_BK - 1 <= wpos_lo && (p.window <= 0 || kt > wpos_hi - p.window) && kt >= k_begin;
+            // mask (only tiles that touch the diagonal or the window's edge need one), online
+            // softmax in base 2: p = 2^(s * scale_log2 - m), one FMA and one ex2 per score
+            const bool full = kt + PF_BK - 1 <= wpos_lo && (p.window <= 0 || kt > wpos_hi - p.window);
+            if (!full) {
+#pragma unroll
+                for (int n = 0; n < PF_BK / 8; ++n)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = kt + n * 8 + (lane & 3) * 2 + e;
+                        const bool v0 = key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
+                        const bool v1 = key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
+                        if (!v0) s[n][e] = -INFINITY;
+                        if (!v1) s[n][2 + e] = -INFINITY;
+                    }
+            }
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int n = 0; n < PF_BK / 8; ++n)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = kt + n * 8 + (lane & 3) * 2 + e;
-                    bool v0 = true, v1 = true;
-                    if (!full) {
-                        v0 = key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
-                        v1 = key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
-                    }
-                    s[n][e] = v0 ? s[n][e] * p.scale_log2 : -INFINITY;
-                    s[n][2 + e] = v1 ? s[n][2 + e] * p.scale_log2 : -INFINITY;
-                    mx0 = fmaxf(mx0, s[n][e]);
-                    mx1 = fmaxf(mx1, s[n][2 + e]);
-                }
+            for (int n = 0; n < PF_BK / 8; ++n) {
+                mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+            }
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            const float a0 = mn0 == -INFINITY ? 1.f : exp2f(m0 - mn0);
-            const float a1 = mn1 == -INFINITY ? 1.f : exp2f(m1 - mn1);
+            const float sl2 = p.scale_log2;
+            const float mn0 = fmaxf(m0, mx0 * sl2), mn1 = fmaxf(m1, mx1 * sl2);
+            // a row that has seen no key yet keeps max -inf; subtract 0 instead so that 2^(-inf) = 0
+            const float mb0 = mn0 == -INFINITY ? 0.f : mn0, mb1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float a0 = pf_ex2(m0 - mb0), a1 = pf_ex2(m1 - mb1);
             m0 = mn0; m1 = mn1;
             float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
             for (int n = 0; n < PF_BK / 8; ++n)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    s[n][e] = s[n][e] == -INFINITY ? 0.f : exp2f(s[n][e] - mn0);
-                    s[n][2 + e] = s[n][2 + e] == -INFINITY ? 0.f : exp2f(s[n][2 + e] - mn1);
+                    s[n][e] = pf_ex2(fmaf(s[n][e], sl2, -mb0));
+                    s[n][2 + e] = pf_ex2(fmaf(s[n][2 + e], sl2, -mb1));
                     ps0 += s[n][e];
                     ps1 += s[n][2 + e];
                 }
@@ -240,10 +278,10 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     }
 }
 
-template <int D>
+template <int D, bool PAGE16>
 int launch_prefill_mma(const DecodeParams& p, int B, int max_q_len, cudaStream_t stream) {
     constexpr int smem = PF_BQ * D * 2 + 2 * 2 * PF_BK * D * 2;
-    auto kernel = prefill_attention_mma_kernel<D>;
+    auto kernel = prefill_attention_mma_kernel<D, PAGE16>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return EMS_ERR_LAUNCH;
@@ -264,8 +302,11 @@ bool prefill_mma_supported(int dtype, int D, long long q_stride, const void* q, 
 }
 
 int run_prefill_mma(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream) {
-    return D == 64 ? launch_prefill_mma<64>(p, B, max_q_len, stream)
-                   : launch_prefill_mma<128>(p, B, max_q_len, stream);
+    if (p.page_size % 16 == 0)
+        return D == 64 ? launch_prefill_mma<64, true>(p, B, max_q_len, stream)
+                       : launch_prefill_mma<128, true>(p, B, max_q_len, stream);
+    return D == 64 ? launch_prefill_mma<64, false>(p, B, max_q_len, stream)
+                   : launch_prefill_mma<128, false>(p, B, max_q_len, stream);
 }
 
 }  // namespace ems

@@ -151,6 +151,20 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     out[n * I + i] = from_f32<T>(act * u);
 }
 
+// Four columns per thread (I a multiple of 4).
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    const size_t n = blockIdx.x;
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (i >= I) return;
+    float g[4], u[4], y[4];
+    Vec4<T>::load(gate_up + n * 2 * I + i, g);
+    Vec4<T>::load(gate_up + n * 2 * I + I + i, u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) y[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+    Vec4<T>::store(out + n * I + i, y);
+}
+
 // ---------------------------------------------------------------------------------------
 // table[pos, i, 0] = cos(pos * inv_freq[i]); table[pos, i, 1] = sin(...)
 
@@ -212,6 +226,69 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int nh, int nkv, int D
         const T* x = row + (size_t)head * D;
         T* dst = vcache + (((size_t)page * nkv + h) * page_size + slot) * D;
         for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = x[i];
+    }
+}
+
+// The same with four pairs per work item and one block per token (all sizes multiples of 4):
+// item = (head, group of 4 consecutive i), heads being q heads, then k heads, then v heads.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nh, int nkv, int D,
+                                         const int* __restrict__ positions,
+                                         const int* __restrict__ row_of_token,
+                                         const float* __restrict__ table, int rot,
+                                         T* __restrict__ kcache, T* __restrict__ vcache,
+                                         const int* __restrict__ block_tables, int bt_stride,
+                                         int page_size, int write_kv) {
+    const size_t n = blockIdx.x;
+    const int pos = positions[n];
+    const int half = rot / 2;
+    T* row = qkv + n * (size_t)(nh + 2 * nkv) * D;
+    const float* cs = table ? table + (size_t)pos * half * 2 : nullptr;
+    size_t cache_base = 0;
+    if (write_kv) {
+        const int page = block_tables[(size_t)row_of_token[n] * bt_stride + pos / page_size];
+        cache_base = ((size_t)page * nkv * page_size + pos % page_size) * D;
+    }
+    const int per_rot = half / 4;            // rotated items per head
+    const int per_tail = (D - rot) / 4;      // copied items per k head
+    const int per_head = per_rot + per_tail;
+    const int rot_heads = write_kv ? nh + nkv : nh;
+    const int total = rot_heads * per_head + (write_kv ? nkv * (D / 4) : 0);
+    for (int item = threadIdx.x; item < total; item += blockDim.x) {
+        if (item < rot_heads * per_head) {
+            const int head = item / per_head, j = item % per_head;
+            const bool is_q = head < nh;
+            T* x = row + (size_t)head * D;
+            T* dst = is_q ? x : kcache + cache_base + (size_t)(head - nh) * page_size * D;
+            if (j < per_rot) {
+                const int i = j * 4;
+                float x1[4], x2[4], c4[4], s4[4], o1[4], o2[4];
+                Vec4<T>::load(x + i, x1);
+                Vec4<T>::load(x + i + half, x2);
+                const float4 ca = *reinterpret_cast<const float4*>(cs + 2 * i);
+                const float4 cb = *reinterpret_cast<const float4*>(cs + 2 * i + 4);
+                c4[0] = ca.x; s4[0] = ca.y; c4[1] = ca.z; s4[1] = ca.w;
+                c4[2] = cb.x; s4[2] = cb.y; c4[3] = cb.z; s4[3] = cb.w;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    o1[k] = x1[k] * c4[k] - x2[k] * s4[k];
+                    o2[k] = x2[k] * c4[k] + x1[k] * s4[k];
+                }
+                Vec4<T>::store(dst + i, o1);
+                Vec4<T>::store(dst + i + half, o2);
+            } else if (!is_q) {  // unrotated tail of k; q's tail stays where it is
+                const int i = rot + (j - per_rot) * 4;
+                float t[4];
+                Vec4<T>::load(x + i, t);
+                Vec4<T>::store(dst + i, t);
+            }
+        } else {
+            const int j = item - rot_heads * per_head;
+            const int h = j / (D / 4), i = (j % (D / 4)) * 4;
+            float t[4];
+            Vec4<T>::load(row + (size_t)(nh + nkv + h) * D + i, t);
+            Vec4<T>::store(vcache + cache_base + (size_t)h * page_size * D + i, t);
+        }
     }
 }
 
@@ -286,6 +363,17 @@ EMS_EXPORT int ems_silu_mul(const void* gate_up, void* out, int dtype, int N, in
                             cudaStream_t stream) {
     if (N <= 0) return EMS_OK;
     const int threads = 256;
+    if (I % 4 == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const dim3 vgrid(N, (I / 4 + threads - 1) / threads);
+        if (vgrid.y > 65535) return EMS_ERR_SHAPE;
+        if (dtype == EMS_F32)
+            silu_mul_vec_kernel<float><<<vgrid, threads, 0, stream>>>((const float*)gate_up, (float*)out, I);
+        else if (dtype == EMS_BF16)
+            silu_mul_vec_kernel<bf16><<<vgrid, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I);
+        else
+            return EMS_ERR_DTYPE;
+        return launch_status();
+    }
     const dim3 grid(N, (I + threads - 1) / threads);
     if (grid.y > 65535) return EMS_ERR_SHAPE;
     if (dtype == EMS_F32)
@@ -312,6 +400,23 @@ EMS_EXPORT int ems_rope_kv_write(void* qkv, int dtype, int N, int nh, int nkv, i
     if (N <= 0) return EMS_OK;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1)) return EMS_ERR_SHAPE;
     if (rotary_dim > 0 && table == nullptr) return EMS_ERR_SHAPE;
+    const int esize = dtype == EMS_F32 ? 4 : 2;
+    if (D % 4 == 0 && rotary_dim % 8 == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)kcache % 16) == 0 &&
+        ((uintptr_t)vcache % 16) == 0 && ((uintptr_t)table % 16) == 0 && (D * esize) % 8 == 0) {
+        const int items = (write_kv ? nh + nkv : nh) * (D - rotary_dim / 2) / 4 + (write_kv ? nkv * D / 4 : 0);
+        const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        if (dtype == EMS_F32)
+            rope_kv_write_vec_kernel<float><<<N, threads, 0, stream>>>(
+                (float*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (float*)kcache,
+                (float*)vcache, block_tables, bt_stride, page_size, write_kv);
+        else if (dtype == EMS_BF16)
+            rope_kv_write_vec_kernel<bf16><<<N, threads, 0, stream>>>(
+                (bf16*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (bf16*)kcache,
+                (bf16*)vcache, block_tables, bt_stride, page_size, write_kv);
+        else
+            return EMS_ERR_DTYPE;
+        return launch_status();
+    }
     const int heads = write_kv ? nh + 2 * nkv : nh;
     if (heads > 65535) return EMS_ERR_SHAPE;
     const dim3 grid(N, heads);

@@ -52,7 +52,7 @@ def decode_splits(num_rows: int, num_kv_heads: int, max_ctx: int) -> int:
     """How many blocks share the keys of one (request, KV head) in a decode step.  A
     function of shapes only (``emberserve/attn/paged_triton.py:259-281`` has the same idea)."""
     blocks = max(1, num_rows * num_kv_heads)
-    want = -(-_TARGET_BLOCKS // blocks)
+    want = _TARGET_BLOCKS // blocks  # rounded down: all blocks of the step run in one wave
     cap = max(1, max_ctx // _MIN_KEYS_PER_SPLIT)
     return max(1, min(_MAX_SPLITS, want, cap))
 
