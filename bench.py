@@ -369,6 +369,38 @@ def run_kernel(args) -> dict:
         flops = 4 * nh * d * t * t / 2
         return {"kernel": "prefill_attention", "tokens": t, "ms": ms, "tflops": flops / ms / 1e9,
                 "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+    if args.kernel == "gemm":
+        h, i, v = s["hidden_size"], s["intermediate_size"], s["vocab_size"]
+        shapes = {"qkv": ((nh + 2 * nkv) * d, h), "o": (h, nh * d), "gate_up": (2 * i, h), "down": (h, i),
+                  "head": (v, h)}
+        n_out, k = shapes[args.shape]
+        m = args.batch
+        # several copies of the weight, used in turn, so that it is never found in L2
+        copies = max(2, int(300e6 // (n_out * k * 2)) + 1)
+        ws = [(torch.randn(n_out, k, device=dev, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
+        out = torch.empty(m, n_out, device=dev, dtype=torch.bfloat16)
+        from emberserve_b200.parts.linear import smallm_ksplit
+
+        ksplit = args.splits or smallm_ksplit(m, n_out, k)
+        scratch = torch.empty(max(1, K.gemm_smallm_scratch_bytes(m, n_out, ksplit) // 4), device=dev)
+        state = {"i": 0}
+
+        def ours():
+            K.gemm_smallm(x, ws[state["i"] % copies], None, out, ksplit=ksplit, scratch=scratch)
+            state["i"] += 1
+
+        def cublas():
+            torch.mm(x, ws[state["i"] % copies].t(), out=out)
+            state["i"] += 1
+
+        ms = timed(ours, reps=copies)
+        ms_lib = timed(cublas, reps=copies)
+        K.check_status()
+        nbytes = n_out * k * 2
+        return {"kernel": "gemm", "shape": args.shape, "m": m, "n": n_out, "k": k, "ksplit": ksplit, "ms": ms,
+                "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                "cublas_ms": ms_lib, "cublas_gbs": nbytes / ms_lib / 1e6}
     raise SystemExit(f"unknown kernel {args.kernel!r}")
 
 
@@ -469,7 +501,10 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill", "kernel"], default=None,
                     help="run one small part only (for profiling): decode at --batch, the prefill, or "
                          "one kernel alone (--kernel)")
-    ap.add_argument("--kernel", choices=["decode_attention", "prefill_attention"], default="decode_attention")
+    ap.add_argument("--kernel", choices=["decode_attention", "prefill_attention", "gemm"],
+                    default="decode_attention")
+    ap.add_argument("--shape", choices=["qkv", "o", "gate_up", "down", "head"], default="qkv",
+                    help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
     ap.add_argument("--splits", type=int, default=0, help="with --only kernel: key splits (0 = the engine's rule)")
     ap.add_argument("--kernel-times", action="store_true",

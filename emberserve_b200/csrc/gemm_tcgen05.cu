@@ -1,0 +1,361 @@
+// y = x W^T for few rows of x (decode steps): a weight-streaming GEMM on the fifth-generation
+// tensor cores.
+//
+// With 1..64 token rows the product is a bandwidth problem: every weight is read once and
+// used a few times.  So the WEIGHT matrix is put on the 128-row side of the MMA and the
+// tokens on its N side (8..64 columns): a block owns 128 output features and a range of
+// K, streams its weight tile through a ring of shared-memory stages with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast), and one elected thread issues
+// tcgen05.mma (kind::f16, bfloat16 inputs, float32 accumulators in tensor memory) on the
+// stages as they land; tcgen05.commit hands each stage back to the TMA producer.  When the
+// block's K range is done the four warps read their 32 accumulator lanes from tensor
+// memory (tcgen05.ld) and store them: as the result, or as a float32 partial when K is
+// split over several blocks so that all SMs stream (a small second kernel adds the
+// partials in a fixed order, adds the bias, and rounds once).
+//
+// The reference's engine calls cuBLAS for these products (emberserve/model/qwen2.py:57-58,
+// 77-79,203); this kernel replaces the library where the row count is small.
+//
+// Every wait on an mbarrier is bounded: if it runs out, the block records a code in a
+// status word that the host can read, stops issuing work, lets what it has in flight
+// land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace ems {
+
+constexpr int G5_BM = 128;      // output features per block (MMA M)
+constexpr int G5_BK = 64;       // K per stage: 64 bf16 = one 128-byte swizzle span
+constexpr int G5_STAGES = 6;
+constexpr int G5_THREADS = 128;
+constexpr uint32_t G5_SPIN_LIMIT = 1u << 18;  // tries of a wait; each try may itself block for microseconds
+
+struct Gemm5Params {
+    float* partial;      // [ksplit, M_tok, N_out] float32 (ksplit > 1) or unused
+    void* y;             // [M_tok, N_out] bf16 (ksplit == 1)
+    const bf16* bias;    // [N_out] or null (applied here only when ksplit == 1)
+    int* status;         // device-visible status word
+    int m_tok, n_out, k_tiles, ksplit;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and a code in *status) if the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    for (uint32_t i = 0; i < G5_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    volatile int* word = status;  // host-mapped memory: a plain store, the first code wins
+    if (*word == 0) *word = code;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive float32 columns of this thread's accumulator lane
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    const uint64_t lo = (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16);
+    const uint64_t hi = (uint64_t)(1024 >> 4) | ((uint64_t)1 << 14) | ((uint64_t)2 << 29);
+    return lo | (hi << 32);
+}
+
+template <int NT>  // token columns of the MMA: 16, 32 or 64
+__global__ void __launch_bounds__(G5_THREADS)
+gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           const Gemm5Params p) {
+    constexpr uint32_t A_BYTES = G5_BM * G5_BK * 2;   // 16 KB
+    constexpr uint32_t B_BYTES = NT * G5_BK * 2;      // 2..8 KB
+    constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+    // instruction descriptor: D float32, A and B bfloat16, both K-major, N = NT, M = 128
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) |
+                               ((uint32_t)(G5_BM >> 4) << 24);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // carve: [A stages][B stages][barriers][tmem pointer]; the base is rounded up to 1024 bytes
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t a_s = base, b_s = base + G5_STAGES * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + G5_STAGES * (A_BYTES + B_BYTES));
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * G5_STAGES, done_bar = empty0 + 8 * G5_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G5_STAGES + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, ks = blockIdx.y;
+    // this block's K tiles
+    const int per = (p.k_tiles + p.ksplit - 1) / p.ksplit;
+    const int kt_begin = ks * per, kt_end = min(p.k_tiles, kt_begin + per);
+    const int nk = max(0, kt_end - kt_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < G5_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory for the accumulator: TMEM_COLS columns x 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer --------------------------------------------------------------
+        int armed = 0;
+        for (int it = 0; it < nk && ok; ++it) {
+            const int s = it % G5_STAGES;
+            const uint32_t ph = (uint32_t)(it / G5_STAGES) & 1u;
+            ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1);
+            if (!ok) break;
+            mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+            const int k0 = (kt_begin + it) * G5_BK;
+            tma_load_2d(a_s + s * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * s);
+            tma_load_2d(b_s + s * B_BYTES, &map_x, k0, 0, full0 + 8 * s);
+            armed = it + 1;
+        }
+        if (!ok) {  // let the copies that were issued land before the block leaves
+            for (int it = max(0, armed - G5_STAGES); it < armed; ++it)
+                mbar_wait(full0 + 8 * (it % G5_STAGES), (uint32_t)(it / G5_STAGES) & 1u, p.status, 4);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----------------------------------------------------------------
+        for (int it = 0; it < nk && ok; ++it) {
+            const int s = it % G5_STAGES;
+            const uint32_t ph = (uint32_t)(it / G5_STAGES) & 1u;
+            ok = mbar_wait(full0 + 8 * s, ph, p.status, 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t da = smem_desc_sw128(a_s + s * A_BYTES), db = smem_desc_sw128(b_s + s * B_BYTES);
+#pragma unroll
+            for (int k = 0; k < G5_BK / 16; ++k)  // 16 K per MMA = 32 bytes = 2 descriptor units
+                tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            tc_commit(empty0 + 8 * s);  // arrives once these MMAs have read the stage
+        }
+        tc_commit(done_bar);            // arrives once every MMA issued above has completed
+    }
+    __syncwarp();
+
+    // ---- epilogue: all four warps, 32 accumulator lanes (= output features) each -------
+    bool done = true;
+    if (lane == 0) done = mbar_wait(done_bar, 0, p.status, 3);
+    done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
+    tc_fence_after();
+    if (done && nk > 0) {
+        const int row = tile * G5_BM + warp * 32 + lane;  // output feature of this thread
+        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < NT; c0 += 16) {
+            float v[16];
+            tc_ld16(taddr + c0, v);
+            if (row < p.n_out) {
+                if (p.ksplit == 1) {
+                    const float bias = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+                    bf16* y = reinterpret_cast<bf16*>(p.y);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (c0 + i < p.m_tok) y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(v[i] + bias);
+                } else {
+                    float* dst = p.partial + (size_t)ks * p.m_tok * p.n_out;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (c0 + i < p.m_tok) dst[(size_t)(c0 + i) * p.n_out + row] = v[i];
+                }
+            }
+        }
+    } else if (done && nk == 0 && p.ksplit > 1) {  // a split with no K: its partial is zero
+        const int row = tile * G5_BM + warp * 32 + lane;
+        if (row < p.n_out)
+            for (int n = 0; n < p.m_tok; ++n) p.partial[((size_t)ks * p.m_tok + n) * p.n_out + row] = 0.f;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// out[n, j] = round(sum_s partial[s, n, j] + bias[j]), splits added in index order
+__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ partial, const bf16* __restrict__ bias,
+                                          bf16* __restrict__ y, int ksplit, int m_tok, int n_out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)m_tok * n_out;
+    if (idx >= total) return;
+    float acc = 0.f;
+    for (int s = 0; s < ksplit; ++s) acc += partial[(size_t)s * total + idx];
+    if (bias) acc += __bfloat162float(bias[idx % n_out]);
+    y[idx] = __float2bfloat16_rn(acc);
+}
+
+// ---- host side: tensor maps and launch ---------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^
+               (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows;
+    }
+};
+
+// Tensor map of a row-major bf16 matrix [rows, cols], box [box_rows, 64 columns], 128-byte
+// swizzle, zeros outside the matrix.  Maps are cached: the same weight is mapped once.
+static bool tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)G5_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap map;
+    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return true;
+}
+
+static int* status_word() {  // host-mapped, so the host reads it without a CUDA call
+    static int* host = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped) == cudaSuccess) *host = 0;
+        else host = nullptr;
+    });
+    return host;
+}
+
+template <int NT>
+static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
+                        cudaStream_t stream) {
+    constexpr int smem = G5_STAGES * (G5_BM * G5_BK * 2 + NT * G5_BK * 2) + (2 * G5_STAGES + 1) * 8 + 16 + 1024;
+    auto kernel = gemm_smallm_tcgen05_kernel<NT>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return EMS_ERR_LAUNCH;
+    kernel<<<dim3(tiles, p.ksplit), G5_THREADS, smem, stream>>>(mw, mx, p);
+    return launch_status();
+}
+
+}  // namespace ems
+
+using namespace ems;
+
+// Bytes of float32 scratch for `ksplit` > 1.
+EMS_EXPORT long long ems_gemm_smallm_scratch_bytes(int m_tok, int n_out, int ksplit) {
+    return ksplit > 1 ? (long long)ksplit * m_tok * n_out * 4 : 0;
+}
+
+// 0 while no kernel of this file has recorded a failed wait; else the code of the first one
+// (1 producer, 2 MMA issuer, 3 epilogue, 4 drain).
+EMS_EXPORT int ems_gemm_smallm_status(void) {
+    int* s = status_word();
+    return s ? *s : -1;
+}
+
+// y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias).
+// m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit >= 1 blocks share K.
+EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
+                               int k, int ksplit, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+    if (m_tok <= 0 || n_out <= 0) return EMS_OK;
+    if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 64) return EMS_ERR_SHAPE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2)) return EMS_ERR_ALIGN;
+    if (ksplit > 1 && (scratch == nullptr || scratch_bytes < ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit)))
+        return EMS_ERR_SCRATCH;
+    int* status = status_word();
+    if (!status) return EMS_ERR_LAUNCH;
+    int* status_dev = nullptr;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
+    const int nt = m_tok <= 16 ? 16 : (m_tok <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    if (!tensor_map_2d(w, n_out, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, nt, &mx)) return EMS_ERR_LAUNCH;
+    Gemm5Params p;
+    p.partial = reinterpret_cast<float*>(scratch); p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
+    p.status = status_dev; p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = ksplit;
+    const int tiles = (n_out + G5_BM - 1) / G5_BM;
+    int rc;
+    if (nt == 16) rc = launch_gemm5<16>(mw, mx, p, tiles, stream);
+    else if (nt == 32) rc = launch_gemm5<32>(mw, mx, p, tiles, stream);
+    else rc = launch_gemm5<64>(mw, mx, p, tiles, stream);
+    if (rc != EMS_OK || ksplit == 1) return rc;
+    const size_t total = (size_t)m_tok * n_out;
+    gemm_splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        p.partial, p.bias, reinterpret_cast<bf16*>(y), ksplit, m_tok, n_out);
+    return launch_status();
+}

@@ -79,6 +79,34 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
     if (threadIdx.x == 0) out[r] = idx;
 }
 
+// The same in two stages for few rows of a large vocabulary: blockIdx.y takes a slice of
+// the row and leaves (ordered value, ~index) packed in 64 bits, largest first on ties of
+// the value means smallest index; the second stage takes the maximum of the slices.
+constexpr int ARGMAX_SLICE = 4096;
+
+__global__ void argmax_slice_kernel(const float* __restrict__ logits, unsigned long long* __restrict__ tmp,
+                                    int V, int slices) {
+    __shared__ float red_v[33];
+    __shared__ int red_i[33];
+    const int r = blockIdx.x, sl = blockIdx.y;
+    const int lo = sl * ARGMAX_SLICE, n = min(ARGMAX_SLICE, V - lo);
+    const float* x = logits + (size_t)r * V + lo;
+    const int idx = block_argmax(x, n, red_v, red_i);
+    if (threadIdx.x == 0)
+        tmp[(size_t)r * slices + sl] =
+            ((unsigned long long)ordered_key(x[idx]) << 32) | (unsigned)(0x7fffffff - (lo + idx));
+}
+
+__global__ void argmax_merge_kernel(const unsigned long long* __restrict__ tmp, int* __restrict__ out,
+                                    int slices) {
+    const int r = blockIdx.x;
+    unsigned long long best = 0;
+    for (int i = threadIdx.x; i < slices; i += 32) best = max(best, tmp[(size_t)r * slices + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (threadIdx.x == 0) out[r] = 0x7fffffff - (int)(best & 0xffffffffull);
+}
+
 // logits[row, tok] = s > 0 ? s / penalty : s * penalty for every distinct tok of the row
 __global__ void penalty_kernel(float* __restrict__ logits, int V, const int* __restrict__ row_ptr,
                                const int* __restrict__ token_ids, const float* __restrict__ penalty) {
@@ -268,9 +296,22 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 
 using namespace ems;
 
-EMS_EXPORT int ems_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
+// Slices per row of the two-stage form; tmp must hold R * slices 64-bit words (0 = one stage).
+EMS_EXPORT int ems_argmax_slices(int R, int V) {
+    const int slices = (V + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+    return (slices >= 4 && R * slices <= 65535 && R <= 256) ? slices : 0;
+}
+
+EMS_EXPORT int ems_argmax(const float* logits, int* out, int R, int V, unsigned long long* tmp,
+                          cudaStream_t stream) {
     if (R <= 0) return EMS_OK;
     if (V <= 0) return EMS_ERR_SHAPE;
+    const int slices = ems_argmax_slices(R, V);
+    if (slices > 0 && tmp != nullptr) {
+        argmax_slice_kernel<<<dim3(R, slices), 256, 0, stream>>>(logits, tmp, V, slices);
+        argmax_merge_kernel<<<R, 32, 0, stream>>>(tmp, out, slices);
+        return launch_status();
+    }
     argmax_kernel<<<R, 1024, 0, stream>>>(logits, out, V);
     return launch_status();
 }

@@ -63,14 +63,21 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_kv_write": [P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, P],
         "ems_to_f32": [P, I, P, L, P],
         "ems_paged_attention": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I, P, L, I, P],
-        "ems_argmax": [P, P, I, I, P],
+        "ems_argmax": [P, P, I, I, P, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
+        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, L, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int
+    lib.ems_gemm_smallm_status.argtypes = []
+    lib.ems_gemm_smallm_status.restype = c_int
+    lib.ems_gemm_smallm_scratch_bytes.argtypes = [I, I, I]
+    lib.ems_gemm_smallm_scratch_bytes.restype = c_longlong
+    lib.ems_argmax_slices.argtypes = [I, I]
+    lib.ems_argmax_slices.restype = c_int
     lib.ems_paged_attention_scratch_bytes.argtypes = [I, I, I, I]
     lib.ems_paged_attention_scratch_bytes.restype = c_longlong
 
@@ -228,9 +235,13 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = first index of the maximum of logits[r]."""
     r, v = logits.shape
     assert logits.dtype == torch.float32
-    _check(library().ems_argmax(_ptr(logits, "logits"), _i32(out, "out"), r, v, _stream()), "argmax")
+    slices = library().ems_argmax_slices(r, v)
+    tmp = torch.empty(r * slices, dtype=torch.int64, device=logits.device) if slices else None
+    _check(library().ems_argmax(_ptr(logits, "logits"), _i32(out, "out"), r, v, _ptr(tmp, "tmp"), _stream()),
+           "argmax", 2 if slices else 1)
 
 
 def repetition_penalty(logits: torch.Tensor, row_ptr: torch.Tensor, token_ids: torch.Tensor,
@@ -252,3 +263,38 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _check(library().ems_sample(_ptr(logits, "logits"), r, v, _ptr(temperature, "temperature"),
                                 _i32(top_k, "top_k"), _ptr(top_p, "top_p"), _ptr(seeds, "seeds"),
                                 _ptr(counters, "counters"), _i32(out, "out"), _stream()), "sample")
+
+
+GEMM_SMALLM_MAX_ROWS = 64
+
+
+def gemm_smallm_scratch_bytes(m_tok: int, n_out: int, ksplit: int) -> int:
+    return int(library().ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit))
+
+
+def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
+                ksplit: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """out[m, n] = x[m, :] . weight[n, :] (+ bias[n]) in bfloat16 with float32 accumulation, for
+    m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks share K and leave
+    float32 partials in `scratch` that a second kernel adds in a fixed order."""
+    m, k = x.shape
+    n = weight.shape[0]
+    assert weight.shape[1] == k and out.shape == (m, n)
+    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    assert bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == n)
+    _check(library().ems_gemm_smallm(
+        _ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
+        _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
+        _stream()), "gemm_smallm", 2 if ksplit > 1 else 1)
+
+
+def gemm_smallm_status() -> int:
+    """0, or the code of the first bounded wait that ran out in the tcgen05 kernel (after a
+    synchronisation point): 1 producer, 2 MMA issuer, 3 epilogue, 4 drain."""
+    return int(library().ems_gemm_smallm_status())
+
+
+def check_status() -> None:
+    code = gemm_smallm_status()
+    if code != 0:
+        raise KernelError(f"a wait inside the tcgen05 GEMM kernel ran out (code {code}); its results are invalid")

@@ -96,7 +96,7 @@ class GQAttention(Mixer):
         s: AttentionSpec = self.spec
         n = ctx.num_tokens
         qkv = ctx.scratch("qkv", (n, self.q_size + 2 * self.kv_size), ctx.dtype)
-        linear(x, self.wqkv, self.bqkv, qkv)
+        linear(x, self.wqkv, self.bqkv, qkv, ctx.scratch)
         table, rot = (None, 0)
         if self.position is not None:
             r = self.position.rotary(ctx.device)
@@ -127,5 +127,5 @@ class GQAttention(Mixer):
                               ctx.starts[nd:], b - nd, n, s.num_heads, s.num_kv_heads, s.head_dim,
                               self.scale, max(ctx.q_lens[nd:]), window=cache.window)
         y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
-        linear(out, self.wo, None, y)
+        linear(out, self.wo, None, y, ctx.scratch)
         return y

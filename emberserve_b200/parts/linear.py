@@ -16,6 +16,8 @@ from __future__ import annotations
 
 import torch
 
+from emberserve_b200 import kernels as K
+
 
 def strict_matmul_precision() -> None:
     """Process-wide matmul settings of the engine: no TF32, no split-K in bfloat16."""
@@ -26,9 +28,47 @@ def strict_matmul_precision() -> None:
     torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 
+# Blocks of the small-row kernel that a B200 runs at once: 148 SMs, two blocks each while the
+# token tile is narrow (their shared-memory rings then fit twice), else one.
+_SMS = 148
+_MIN_K_TILES_PER_SPLIT = 8
+# Up to this many rows the hand-written kernel is used; with more, cuBLAS is as fast or faster
+# (measured at the projection shapes of a 7B model).
+_SMALLM_ROWS = 32
+
+
+def smallm_ksplit(m_tok: int, n_out: int, k: int) -> int:
+    """Over how many blocks the small-row kernel splits K: enough that every SM streams
+    weights, a function of the shape alone (so a result never depends on the batch)."""
+    tiles = -(-n_out // 128)
+    k_tiles = -(-k // 64)
+    slots = _SMS * (2 if m_tok <= 32 else 1)
+    if tiles >= slots:
+        return 1
+    return max(1, min(slots // tiles, k_tiles // _MIN_K_TILES_PER_SPLIT, 64))
+
+
+def _use_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and out.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
+            and x.shape[0] <= _SMALLM_ROWS and x.shape[1] % 8 == 0
+            and x.is_contiguous() and weight.is_contiguous() and out.is_contiguous())
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
-           out: torch.Tensor) -> torch.Tensor:
-    """out = x @ weight.T (+ bias).  x: [N, K], weight: [M, K], out: [N, M]."""
+           out: torch.Tensor, scratch=None) -> torch.Tensor:
+    """out = x @ weight.T (+ bias).  x: [N, K], weight: [M, K], out: [N, M].  With few rows
+    in bfloat16 the product runs on the hand-written tcgen05 kernel (`scratch` is the step's
+    scratch allocator, for its split-K partials); otherwise in cuBLAS."""
+    if scratch is not None and _use_smallm(x, weight, bias, out):
+        m, k = x.shape
+        n = weight.shape[0]
+        ksplit = smallm_ksplit(m, n, k)
+        buf = None
+        if ksplit > 1:
+            buf = scratch("gemm_partials", (K.gemm_smallm_scratch_bytes(m, n, ksplit) // 4,), torch.float32)
+        K.gemm_smallm(x, weight, bias, out, ksplit=ksplit, scratch=buf)
+        return out
     same = weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
     if same and out.dtype == x.dtype:
         if bias is None:

@@ -45,9 +45,9 @@ class SwiGLU(FeedForward):
         s: SwiGLUSpec = self.spec
         n = x.shape[0]
         gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
-        linear(x, self.wgu, None, gu)
+        linear(x, self.wgu, None, gu, ctx.scratch)
         act = ctx.scratch("ffn_act", (n, s.intermediate), ctx.dtype)
         K.silu_mul(gu, act)
         y = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
-        linear(act, self.wdown, None, y)
+        linear(act, self.wdown, None, y, ctx.scratch)
         return y

@@ -193,7 +193,25 @@ def sample(logits, temperature, top_k, top_p, seeds, counters, out):
         out[r] = idx
 
 
-ALL = ["embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write", "to_f32",
+GEMM_SMALLM_MAX_ROWS = 64
+
+
+def gemm_smallm_scratch_bytes(m_tok, n_out, ksplit):
+    return ksplit * m_tok * n_out * 4 if ksplit > 1 else 0
+
+
+def gemm_smallm(x, weight, bias, out, ksplit=1, scratch=None):
+    y = x.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    out.copy_(y.to(out.dtype))
+
+
+def check_status():
+    return None
+
+
+ALL = ["gemm_smallm_scratch_bytes", "gemm_smallm", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write", "to_f32",
        "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample"]
 
 

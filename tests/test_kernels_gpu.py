@@ -390,3 +390,27 @@ def test_sample_distribution_and_seeds():
         u = ref.uniform_of(i, 0)
         want = int(torch.searchsorted(torch.cumsum(probs, 0), torch.tensor(u, dtype=torch.float64), right=True))
         assert abs(out[i].item() - want) <= 0 or abs(float(torch.cumsum(probs, 0)[min(want, v - 1)]) - u) < 1e-5
+
+
+@pytest.mark.parametrize("m,n,k,ksplit", [(1, 256, 128, 1), (8, 4608, 3584, 4), (8, 3584, 3584, 5), (16, 1000, 3584, 1),
+                                          (17, 384, 18944, 5), (33, 640, 1024, 2), (64, 3584, 18944, 5), (5, 130, 72, 1),
+                                          (8, 37888, 3584, 1), (3, 152064, 896, 1), (64, 256, 64, 1), (2, 128, 4096, 64)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_smallm_tcgen05(m, n, k, ksplit, with_bias):
+    """The weight-streaming tcgen05 GEMM for few rows against a float32 product of the same
+    bfloat16 inputs: row counts around the MMA's column tiles (16, 32, 64), output widths that
+    are no multiple of 128, K that is no multiple of 64, K split over blocks."""
+    g = torch.Generator(device="cuda").manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16) if with_bias else None
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev())
+    scratch = torch.empty(max(1, K().gemm_smallm_scratch_bytes(m, n, ksplit) // 4), device=dev())
+    K().gemm_smallm(x, w, bias, out, ksplit=ksplit, scratch=scratch)
+    torch.cuda.synchronize()
+    K().check_status()
+    want = x.float() @ w.float().t()
+    if with_bias:
+        want = want + bias.float()
+    scale = float(want.abs().max())
+    assert float((out.float() - want).abs().max()) <= 8e-3 * scale + 1e-3, (m, n, k, ksplit)
