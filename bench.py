@@ -383,11 +383,16 @@ def run_kernel(args) -> dict:
         from emberserve_b200.parts.linear import smallm_ksplit
 
         ksplit = args.splits or smallm_ksplit(m, n_out, k)
-        scratch = torch.empty(max(1, K.gemm_smallm_scratch_bytes(m, n_out, ksplit) // 4), device=dev)
+        on_chip = ksplit in (1, 2, 4, 8)  # the blocks of a split reduce as a cluster
+        scratch = None if on_chip else torch.empty(K.gemm_smallm_scratch_bytes(m, n_out, ksplit) // 4, device=dev)
+        act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
         state = {"i": 0}
 
         def ours():
-            K.gemm_smallm(x, ws[state["i"] % copies], None, out, ksplit=ksplit, scratch=scratch)
+            if args.shape == "gate_up":  # as the engine runs it: both halves and SiLU in one kernel
+                K.gemm_smallm_gated(x, ws[state["i"] % copies], act)
+            else:
+                K.gemm_smallm(x, ws[state["i"] % copies], None, out, ksplit=ksplit, scratch=scratch)
             state["i"] += 1
 
         def cublas():

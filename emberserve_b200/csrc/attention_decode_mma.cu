@@ -63,6 +63,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D, bool PAGE16>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_mma_kernel(const DecodeParams p) {
+    allow_dependent_launch();
     constexpr int CH = D / 8;                  // 16-byte chunks per key row
     constexpr int ROW_BYTES = D * 2;
     constexpr int TILE_BYTES = DEC_TK * ROW_BYTES;           // K (or V) of one 16-key tile

@@ -228,6 +228,7 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
                                        int splits, int D) {
+    allow_dependent_launch();
     const size_t prow = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(prow * splits + s) * 2]);

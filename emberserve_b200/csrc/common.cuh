@@ -88,6 +88,12 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// Lets a kernel that was launched as a programmatic dependent of this one (the tcgen05 GEMM
+// that follows a norm, an attention or an activation kernel) start its prologue and its
+// weight loads while this kernel still runs; that kernel waits before it reads our output.
+// A no-op when nothing of the kind follows.
+__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? EMS_OK : EMS_ERR_LAUNCH; }
 
 }  // namespace ems

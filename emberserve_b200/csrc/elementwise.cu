@@ -96,6 +96,7 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* resid
                                        const void* __restrict__ weight, int w_dtype,
                                        T* __restrict__ out, const int* __restrict__ rows, int H,
                                        float eps, int write_residual) {
+    allow_dependent_launch();
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : r;
@@ -154,6 +155,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // Four columns per thread (I a multiple of 4).
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    allow_dependent_launch();
     const size_t n = blockIdx.x;
     const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (i >= I) return;

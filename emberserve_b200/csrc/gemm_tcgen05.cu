@@ -40,6 +40,8 @@ struct Gemm5Params {
     const bf16* bias;    // [N_out] or null (applied here only when ksplit == 1)
     int* status;         // device-visible status word
     int m_tok, n_out, k_tiles, ksplit;
+    int cluster_reduce;  // 1: the ksplit blocks of a row tile are a cluster and reduce on chip
+    int dual_offset;     // DUAL kernels: row distance between the two weight tiles
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -72,6 +74,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// Programmatic dependent launch: this kernel may be started while the kernel before it in the
+// stream is still running; everything that reads that kernel's output comes after this wait
+// (which returns once the earlier kernel has completed and its writes are visible).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -106,13 +112,40 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return lo | (hi << 32);
 }
 
-template <int NT>  // token columns of the MMA: 16, 32 or 64
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// float at shared-memory address `addr` of the block with rank `rank` in this cluster
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// NT: token columns of the MMA (16, 32 or 64).
+// DUAL: the block owns TWO weight tiles, rows [tile*128, +128) and the same rows `dual_offset`
+// further down (gate and up projections of a gated feed-forward), accumulates both, and
+// stores silu(first) * second: the activation never goes to memory unfused.
+// Split K (ksplit > 1) in one of two ways: the ksplit blocks of a row tile form a thread-block
+// cluster and add their accumulators through distributed shared memory, in rank order
+// (p.cluster_reduce); or each block writes a float32 partial for a second kernel to add.
+template <int NT, bool DUAL>
 __global__ void __launch_bounds__(G5_THREADS)
 gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            const Gemm5Params p) {
-    constexpr uint32_t A_BYTES = G5_BM * G5_BK * 2;   // 16 KB
-    constexpr uint32_t B_BYTES = NT * G5_BK * 2;      // 2..8 KB
-    constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+    constexpr int STAGES = DUAL ? 5 : G5_STAGES;
+    constexpr uint32_t W_BYTES = G5_BM * G5_BK * 2;               // 16 KB per weight tile
+    constexpr uint32_t A_BYTES = (DUAL ? 2 : 1) * W_BYTES;
+    constexpr uint32_t B_BYTES = NT * G5_BK * 2;                  // 2..8 KB
+    constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * NT;
+    constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
     // instruction descriptor: D float32, A and B bfloat16, both K-major, N = NT, M = 128
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) |
                                ((uint32_t)(G5_BM >> 4) << 24);
@@ -120,10 +153,10 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     // carve: [A stages][B stages][barriers][tmem pointer]; the base is rounded up to 1024 bytes
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t a_s = base, b_s = base + G5_STAGES * A_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + G5_STAGES * (A_BYTES + B_BYTES));
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * G5_STAGES, done_bar = empty0 + 8 * G5_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * G5_STAGES + 1);
+    const uint32_t a_s = base, b_s = base + STAGES * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * (A_BYTES + B_BYTES));
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, done_bar = empty0 + 8 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, ks = blockIdx.y;
@@ -133,11 +166,11 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int nk = max(0, kt_end - kt_begin);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < G5_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor memory for the accumulator: TMEM_COLS columns x 128 lanes
+    if (warp == 1) {  // tensor memory for the accumulators: TMEM_COLS columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -150,34 +183,50 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer --------------------------------------------------------------
-        int armed = 0;
-        for (int it = 0; it < nk && ok; ++it) {
-            const int s = it % G5_STAGES;
-            const uint32_t ph = (uint32_t)(it / G5_STAGES) & 1u;
+        // The weights do not depend on the kernel before this one: the first ring of weight
+        // tiles is requested at once, the activations only after the dependency wait.
+        const int pre = min(nk, STAGES);
+        for (int it = 0; it < pre; ++it) {
+            mbar_expect_tx(full0 + 8 * it, A_BYTES + B_BYTES);
+            const int k0 = (kt_begin + it) * G5_BK;
+            tma_load_2d(a_s + it * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * it);
+            if (DUAL) tma_load_2d(a_s + it * A_BYTES + W_BYTES, &map_w, k0, p.dual_offset + tile * G5_BM, full0 + 8 * it);
+        }
+        grid_dependency_wait();
+        for (int it = 0; it < pre; ++it)
+            tma_load_2d(b_s + it * B_BYTES, &map_x, (kt_begin + it) * G5_BK, 0, full0 + 8 * it);
+        int armed = pre;
+        for (int it = pre; it < nk && ok; ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
             ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 1);
             if (!ok) break;
             mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
             const int k0 = (kt_begin + it) * G5_BK;
             tma_load_2d(a_s + s * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * s);
+            if (DUAL) tma_load_2d(a_s + s * A_BYTES + W_BYTES, &map_w, k0, p.dual_offset + tile * G5_BM, full0 + 8 * s);
             tma_load_2d(b_s + s * B_BYTES, &map_x, k0, 0, full0 + 8 * s);
             armed = it + 1;
         }
         if (!ok) {  // let the copies that were issued land before the block leaves
-            for (int it = max(0, armed - G5_STAGES); it < armed; ++it)
-                mbar_wait(full0 + 8 * (it % G5_STAGES), (uint32_t)(it / G5_STAGES) & 1u, p.status, 4);
+            for (int it = max(0, armed - STAGES); it < armed; ++it)
+                mbar_wait(full0 + 8 * (it % STAGES), (uint32_t)(it / STAGES) & 1u, p.status, 4);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----------------------------------------------------------------
         for (int it = 0; it < nk && ok; ++it) {
-            const int s = it % G5_STAGES;
-            const uint32_t ph = (uint32_t)(it / G5_STAGES) & 1u;
+            const int s = it % STAGES;
+            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
             ok = mbar_wait(full0 + 8 * s, ph, p.status, 2);
             if (!ok) break;
             tc_fence_after();
             const uint64_t da = smem_desc_sw128(a_s + s * A_BYTES), db = smem_desc_sw128(b_s + s * B_BYTES);
 #pragma unroll
-            for (int k = 0; k < G5_BK / 16; ++k)  // 16 K per MMA = 32 bytes = 2 descriptor units
-                tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < G5_BK / 16; ++k) {  // 16 K per MMA = 32 bytes = 2 descriptor units
+                const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, acc);
+                if (DUAL) tc_mma_bf16(tmem_d + NT, da + (W_BYTES >> 4) + 2 * k, db + 2 * k, IDESC, acc);
+            }
             tc_commit(empty0 + 8 * s);  // arrives once these MMAs have read the stage
         }
         tc_commit(done_bar);            // arrives once every MMA issued above has completed
@@ -185,13 +234,65 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     __syncwarp();
 
     // ---- epilogue: all four warps, 32 accumulator lanes (= output features) each -------
+    grid_dependency_wait();  // (the producer has passed it already; this orders the stores below)
+    allow_dependent_launch();  // a GEMM that follows may set up and fetch weights as blocks retire
     bool done = true;
     if (lane == 0) done = mbar_wait(done_bar, 0, p.status, 3);
     done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
     tc_fence_after();
-    if (done && nk > 0) {
-        const int row = tile * G5_BM + warp * 32 + lane;  // output feature of this thread
-        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
+    const int row_local = warp * 32 + lane;
+    const int row = tile * G5_BM + row_local;  // output feature of this thread
+    const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
+    const bool have = done && nk > 0;
+    if (DUAL) {
+        if (have) {
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                float g[16], u[16];
+                tc_ld16(taddr + c0, g);
+                tc_ld16(taddr + NT + c0, u);
+                if (row < p.n_out) {
+                    bf16* y = reinterpret_cast<bf16*>(p.y);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (c0 + i < p.m_tok)
+                            y[(size_t)(c0 + i) * p.n_out + row] =
+                                __float2bfloat16_rn(g[i] / (1.0f + expf(-g[i])) * u[i]);
+                }
+            }
+        }
+    } else if (p.cluster_reduce) {
+        // every block of the cluster leaves its accumulator in its own shared memory (the
+        // stage ring is idle now); the block whose rank is row % ksplit adds the row up
+        // layout red[column][row]: neighbouring threads write neighbouring words
+        float* red = reinterpret_cast<float*>(base_ptr);
+#pragma unroll
+        for (int c0 = 0; c0 < NT; c0 += 16) {
+            float v[16];
+            if (have) tc_ld16(taddr + c0, v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) red[(c0 + i) * G5_BM + row_local] = have ? v[i] : 0.f;
+        }
+        cluster_sync_all();
+        const int me = (int)cluster_rank();
+        const int owned = G5_BM / p.ksplit;  // ksplit is 2, 4 or 8: rows me, me + ksplit, ...
+        bf16* y = reinterpret_cast<bf16*>(p.y);
+        for (int idx = threadIdx.x; idx < owned * p.m_tok; idx += G5_THREADS) {
+            const int n = idx / owned, rl = (idx % owned) * p.ksplit + me;
+            const int orow = tile * G5_BM + rl;
+            if (orow >= p.n_out) continue;
+            const uint32_t addr = a_s + (uint32_t)(n * G5_BM + rl) * 4u;
+            float part[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) part[r] = r < p.ksplit ? ld_cluster_f32(addr, (uint32_t)r) : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) acc += part[r];  // rank order, the same for every batch
+            if (p.bias) acc += __bfloat162float(p.bias[orow]);
+            y[(size_t)n * p.n_out + orow] = __float2bfloat16_rn(acc);
+        }
+        cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+    } else if (have) {
 #pragma unroll
         for (int c0 = 0; c0 < NT; c0 += 16) {
             float v[16];
@@ -211,8 +312,7 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 }
             }
         }
-    } else if (done && nk == 0 && p.ksplit > 1) {  // a split with no K: its partial is zero
-        const int row = tile * G5_BM + warp * 32 + lane;
+    } else if (done && p.ksplit > 1) {  // a split with no K: its partial is zero
         if (row < p.n_out)
             for (int n = 0; n < p.m_tok; ++n) p.partial[((size_t)ks * p.m_tok + n) * p.n_out + row] = 0.f;
     }
@@ -302,14 +402,39 @@ static int* status_word() {  // host-mapped, so the host reads it without a CUDA
     return host;
 }
 
-template <int NT>
+template <int NT, bool DUAL>
 static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
                         cudaStream_t stream) {
-    constexpr int smem = G5_STAGES * (G5_BM * G5_BK * 2 + NT * G5_BK * 2) + (2 * G5_STAGES + 1) * 8 + 16 + 1024;
-    auto kernel = gemm_smallm_tcgen05_kernel<NT>;
+    constexpr int stages = DUAL ? 5 : G5_STAGES;
+    constexpr int smem = stages * ((DUAL ? 2 : 1) * G5_BM * G5_BK * 2 + NT * G5_BK * 2) + (2 * stages + 1) * 8 +
+                         16 + 1024;
+    auto kernel = gemm_smallm_tcgen05_kernel<NT, DUAL>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return EMS_ERR_LAUNCH;
-    kernel<<<dim3(tiles, p.ksplit), G5_THREADS, smem, stream>>>(mw, mx, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, p.ksplit);
+    cfg.blockDim = dim3(G5_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    // may start while the kernel before it still runs (see grid_dependency_wait)
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+    if (p.cluster_reduce) {
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = 1;
+        attr[nattr].val.clusterDim.y = p.ksplit;
+        attr[nattr].val.clusterDim.z = 1;
+        ++nattr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = nattr;
+    if (cudaLaunchKernelEx(&cfg, kernel, mw, mx, p) != cudaSuccess) {
+        cudaGetLastError();
+        return EMS_ERR_LAUNCH;
+    }
     return launch_status();
 }
 
@@ -330,13 +455,17 @@ EMS_EXPORT int ems_gemm_smallm_status(void) {
 }
 
 // y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias).
-// m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit >= 1 blocks share K.
+// m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit >= 1 blocks share K: with
+// scratch == null and ksplit in {2, 4, 8} they form a cluster and reduce on chip; with a
+// scratch buffer they leave float32 partials for a second kernel.
 EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
                                int k, int ksplit, void* scratch, long long scratch_bytes, cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;
     if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 64) return EMS_ERR_SHAPE;
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2)) return EMS_ERR_ALIGN;
-    if (ksplit > 1 && (scratch == nullptr || scratch_bytes < ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit)))
+    const bool cluster = ksplit > 1 && scratch == nullptr;
+    if (cluster && ksplit != 2 && ksplit != 4 && ksplit != 8) return EMS_ERR_SHAPE;
+    if (ksplit > 1 && !cluster && scratch_bytes < ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit))
         return EMS_ERR_SCRATCH;
     int* status = status_word();
     if (!status) return EMS_ERR_LAUNCH;
@@ -348,14 +477,38 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
     Gemm5Params p;
     p.partial = reinterpret_cast<float*>(scratch); p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
     p.status = status_dev; p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = ksplit;
+    p.cluster_reduce = cluster ? 1 : 0; p.dual_offset = 0;
     const int tiles = (n_out + G5_BM - 1) / G5_BM;
     int rc;
-    if (nt == 16) rc = launch_gemm5<16>(mw, mx, p, tiles, stream);
-    else if (nt == 32) rc = launch_gemm5<32>(mw, mx, p, tiles, stream);
-    else rc = launch_gemm5<64>(mw, mx, p, tiles, stream);
-    if (rc != EMS_OK || ksplit == 1) return rc;
+    if (nt == 16) rc = launch_gemm5<16, false>(mw, mx, p, tiles, stream);
+    else if (nt == 32) rc = launch_gemm5<32, false>(mw, mx, p, tiles, stream);
+    else rc = launch_gemm5<64, false>(mw, mx, p, tiles, stream);
+    if (rc != EMS_OK || ksplit == 1 || cluster) return rc;
     const size_t total = (size_t)m_tok * n_out;
     gemm_splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
         p.partial, p.bias, reinterpret_cast<bf16*>(y), ksplit, m_tok, n_out);
     return launch_status();
+}
+
+// act[m_tok, inter] (bf16) = silu(x . w[0:inter]^T) * (x . w[inter:2*inter]^T): the gated
+// feed-forward's first two projections and its activation in one kernel.  w: [2*inter, k].
+EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, int m_tok, int inter, int k,
+                                     cudaStream_t stream) {
+    if (m_tok <= 0 || inter <= 0) return EMS_OK;
+    if (m_tok > 64 || k <= 0 || k % 8) return EMS_ERR_SHAPE;
+    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)act % 2)) return EMS_ERR_ALIGN;
+    int* status = status_word();
+    if (!status) return EMS_ERR_LAUNCH;
+    int* status_dev = nullptr;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
+    const int nt = m_tok <= 16 ? 16 : (m_tok <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    if (!tensor_map_2d(w, 2LL * inter, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, nt, &mx)) return EMS_ERR_LAUNCH;
+    Gemm5Params p;
+    p.partial = nullptr; p.y = act; p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
+    p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = 1; p.cluster_reduce = 0; p.dual_offset = inter;
+    const int tiles = (inter + G5_BM - 1) / G5_BM;
+    if (nt == 16) return launch_gemm5<16, true>(mw, mx, p, tiles, stream);
+    if (nt == 32) return launch_gemm5<32, true>(mw, mx, p, tiles, stream);
+    return launch_gemm5<64, true>(mw, mx, p, tiles, stream);
 }

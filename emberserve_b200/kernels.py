@@ -67,6 +67,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
         "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, L, P],
+        "ems_gemm_smallm_gated": [P, P, P, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -275,8 +276,10 @@ def gemm_smallm_scratch_bytes(m_tok: int, n_out: int, ksplit: int) -> int:
 def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
                 ksplit: int = 1, scratch: torch.Tensor | None = None) -> None:
     """out[m, n] = x[m, :] . weight[n, :] (+ bias[n]) in bfloat16 with float32 accumulation, for
-    m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks share K and leave
-    float32 partials in `scratch` that a second kernel adds in a fixed order."""
+    m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks share K: without
+    `scratch` (ksplit 2, 4 or 8) they form a thread-block cluster and add their accumulators
+    on chip, in rank order; with `scratch` they leave float32 partials there that a second
+    kernel adds in a fixed order."""
     m, k = x.shape
     n = weight.shape[0]
     assert weight.shape[1] == k and out.shape == (m, n)
@@ -285,7 +288,18 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     _check(library().ems_gemm_smallm(
         _ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
         _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
-        _stream()), "gemm_smallm", 2 if ksplit > 1 else 1)
+        _stream()), "gemm_smallm", 2 if (ksplit > 1 and scratch is not None) else 1)
+
+
+def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, i] = silu(x . weight[i]) * (x . weight[I + i]) for weight [2 I, K]: gate and up
+    projections of a gated feed-forward and its activation in one tcgen05 kernel, m <= 64."""
+    m, k = x.shape
+    inter = out.shape[1]
+    assert weight.shape == (2 * inter, k) and out.shape[0] == m
+    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    _check(library().ems_gemm_smallm_gated(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(out, "out"), m, inter, k,
+                                           _stream()), "gemm_smallm_gated")
 
 
 def gemm_smallm_status() -> int:

@@ -34,7 +34,7 @@ _SMS = 148
 _MIN_K_TILES_PER_SPLIT = 8
 # Up to this many rows the hand-written kernel is used; with more, cuBLAS is as fast or faster
 # (measured at the projection shapes of a 7B model).
-_SMALLM_ROWS = 32
+_SMALLM_ROWS = 16
 
 
 def smallm_ksplit(m_tok: int, n_out: int, k: int) -> int:
@@ -43,9 +43,11 @@ def smallm_ksplit(m_tok: int, n_out: int, k: int) -> int:
     tiles = -(-n_out // 128)
     k_tiles = -(-k // 64)
     slots = _SMS * (2 if m_tok <= 32 else 1)
-    if tiles >= slots:
-        return 1
-    return max(1, min(slots // tiles, k_tiles // _MIN_K_TILES_PER_SPLIT, 64))
+    want = min(slots // max(1, tiles), k_tiles // _MIN_K_TILES_PER_SPLIT)
+    for split in (4, 2):  # the blocks of a split form a cluster (8 gained nothing over 4)
+        if want >= split:
+            return split
+    return 1
 
 
 def _use_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> bool:
@@ -53,6 +55,15 @@ def _use_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
             and out.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
             and x.shape[0] <= _SMALLM_ROWS and x.shape[1] % 8 == 0
             and x.is_contiguous() and weight.is_contiguous() and out.is_contiguous())
+
+
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    """out = silu(x Wg^T) * (x Wu^T) with weight = [Wg; Wu], in one kernel, where the
+    hand-written small-row kernel takes the case; False if the caller has to do it in steps."""
+    if not _use_smallm(x, weight, None, out):
+        return False
+    K.gemm_smallm_gated(x, weight, out)
+    return True
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
@@ -63,11 +74,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
     if scratch is not None and _use_smallm(x, weight, bias, out):
         m, k = x.shape
         n = weight.shape[0]
-        ksplit = smallm_ksplit(m, n, k)
-        buf = None
-        if ksplit > 1:
-            buf = scratch("gemm_partials", (K.gemm_smallm_scratch_bytes(m, n, ksplit) // 4,), torch.float32)
-        K.gemm_smallm(x, weight, bias, out, ksplit=ksplit, scratch=buf)
+        K.gemm_smallm(x, weight, bias, out, ksplit=smallm_ksplit(m, n, k))
         return out
     same = weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
     if same and out.dtype == x.dtype:

@@ -13,7 +13,7 @@ import torch
 
 from emberserve_b200 import kernels as K
 from emberserve_b200.parts.base import FeedForward, ParamSpec, Source, StepContext, register_part
-from emberserve_b200.parts.linear import linear
+from emberserve_b200.parts.linear import gated_linear, linear
 
 
 @dataclass(frozen=True)
@@ -44,10 +44,11 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s: SwiGLUSpec = self.spec
         n = x.shape[0]
-        gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
-        linear(x, self.wgu, None, gu, ctx.scratch)
         act = ctx.scratch("ffn_act", (n, s.intermediate), ctx.dtype)
-        K.silu_mul(gu, act)
+        if not gated_linear(x, self.wgu, act):  # few rows: both projections and SiLU in one kernel
+            gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
+            linear(x, self.wgu, None, gu, ctx.scratch)
+            K.silu_mul(gu, act)
         y = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
         linear(act, self.wdown, None, y, ctx.scratch)
         return y

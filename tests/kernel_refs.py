@@ -207,11 +207,18 @@ def gemm_smallm(x, weight, bias, out, ksplit=1, scratch=None):
     out.copy_(y.to(out.dtype))
 
 
+def gemm_smallm_gated(x, weight, out):
+    i = out.shape[1]
+    y = x.float() @ weight.float().t()
+    g, u = y[:, :i], y[:, i:]
+    out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+
+
 def check_status():
     return None
 
 
-ALL = ["gemm_smallm_scratch_bytes", "gemm_smallm", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write", "to_f32",
+ALL = ["gemm_smallm_scratch_bytes", "gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write", "to_f32",
        "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample"]
 
 

@@ -406,7 +406,7 @@ def test_gemm_smallm_tcgen05(m, n, k, ksplit, with_bias):
     bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16) if with_bias else None
     out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev())
     scratch = torch.empty(max(1, K().gemm_smallm_scratch_bytes(m, n, ksplit) // 4), device=dev())
-    K().gemm_smallm(x, w, bias, out, ksplit=ksplit, scratch=scratch)
+    K().gemm_smallm(x, w, bias, out, ksplit=ksplit, scratch=scratch if ksplit > 1 else None)
     torch.cuda.synchronize()
     K().check_status()
     want = x.float() @ w.float().t()
@@ -414,3 +414,42 @@ def test_gemm_smallm_tcgen05(m, n, k, ksplit, with_bias):
         want = want + bias.float()
     scale = float(want.abs().max())
     assert float((out.float() - want).abs().max()) <= 8e-3 * scale + 1e-3, (m, n, k, ksplit)
+
+
+@pytest.mark.parametrize("m,n,k,ksplit", [(1, 256, 512, 2), (8, 4608, 3584, 8), (8, 3584, 3584, 4), (16, 1000, 3584, 8),
+                                          (17, 384, 18944, 8), (32, 3584, 18944, 8), (5, 130, 200, 2), (64, 256, 1024, 4)])
+def test_gemm_smallm_cluster_split(m, n, k, ksplit):
+    """K split over the blocks of a thread-block cluster that add their accumulators through
+    distributed shared memory (no scratch, one launch)."""
+    g = torch.Generator(device="cuda").manual_seed(m * 77 + n)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev())
+    before = K().launch_count()
+    K().gemm_smallm(x, w, bias, out, ksplit=ksplit)
+    assert K().launch_count() - before == 1
+    torch.cuda.synchronize()
+    K().check_status()
+    want = x.float() @ w.float().t() + bias.float()
+    assert float((out.float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
+    again = torch.empty_like(out)
+    K().gemm_smallm(x, w, bias, again, ksplit=ksplit)
+    assert torch.equal(out, again)  # fixed order of additions
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 256, 128), (8, 18944, 3584), (16, 1000, 3584), (17, 4864, 896),
+                                       (33, 640, 1024), (64, 2048, 512), (5, 130, 72)])
+def test_gemm_smallm_gated(m, inter, k):
+    """Gate and up projections and silu(gate) * up in one kernel (two accumulators in tensor
+    memory), against the float32 computation of the same bfloat16 inputs."""
+    g = torch.Generator(device="cuda").manual_seed(m * 31 + inter)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=dev())
+    K().gemm_smallm_gated(x, w, out)
+    torch.cuda.synchronize()
+    K().check_status()
+    y = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    assert float((out.float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
