@@ -63,7 +63,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D, bool PAGE16>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_mma_kernel(const DecodeParams p) {
-    allow_dependent_launch();
+    pdl_prologue();
     constexpr int CH = D / 8;                  // 16-byte chunks per key row
     constexpr int ROW_BYTES = D * 2;
     constexpr int TILE_BYTES = DEC_TK * ROW_BYTES;           // K (or V) of one 16-key tile
@@ -295,8 +295,7 @@ int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t stream) {
         return EMS_ERR_LAUNCH;
     if (p.nkv > 65535 || B > 65535) return EMS_ERR_SHAPE;
     const dim3 grid((unsigned)p.splits, (unsigned)p.nkv, (unsigned)B);
-    kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(p);
-    return launch_status();
+    return launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, p);
 }
 
 // Whether the tensor-core decode kernel takes this case; otherwise the generic kernel runs.

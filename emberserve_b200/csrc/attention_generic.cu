@@ -228,7 +228,7 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
                                        int splits, int D) {
-    allow_dependent_launch();
+    pdl_prologue();
     const size_t prow = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(prow * splits + s) * 2]);
@@ -342,9 +342,9 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
         decode_mma_supported(dtype, D, p.G, q_stride, q, kcache, vcache)) {
         const int rc = run_decode_mma(d, B, D, stream);
         if (rc != EMS_OK || splits == 1) return rc;
-        attention_merge_kernel<bf16><<<(unsigned)((size_t)N * nh), D >= 128 ? 128 : 64, 0, stream>>>(
-            p.part_o, p.part_ml, reinterpret_cast<bf16*>(out), splits, D);
-        return launch_status();
+        return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)N * nh)), dim3(D >= 128 ? 128 : 64),
+                          0, stream, (const float*)p.part_o, (const float*)p.part_ml, reinterpret_cast<bf16*>(out),
+                          splits, D);
     }
     if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
     if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);

@@ -94,6 +94,37 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // A no-op when nothing of the kind follows.
 __device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::); }
 
+// First statement of a kernel that is launched with launch_pdl(): let the kernel after this
+// one be scheduled early, then wait until the kernel before this one has completed (and its
+// writes are visible).  Every kernel of a chain waits, so completion is transitive.
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? EMS_OK : EMS_ERR_LAUNCH; }
+
+// Launch as a programmatic dependent of the kernel before it in the stream: the blocks may be
+// scheduled while that kernel drains, which hides launch latency in chains of short kernels.
+// The kernel must begin with pdl_prologue().
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) != cudaSuccess) {
+        cudaGetLastError();
+        return EMS_ERR_LAUNCH;
+    }
+    return launch_status();
+}
 
 }  // namespace ems

@@ -23,6 +23,7 @@ namespace ems {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                  float* __restrict__ residual, int H) {
+    pdl_prologue();
     const size_t n = blockIdx.x;
     const T* src = table + (size_t)tokens[n] * H;
     float* dst = residual + n * H;
@@ -96,7 +97,7 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* resid
                                        const void* __restrict__ weight, int w_dtype,
                                        T* __restrict__ out, const int* __restrict__ rows, int H,
                                        float eps, int write_residual) {
-    allow_dependent_launch();
+    pdl_prologue();
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : r;
@@ -241,6 +242,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nh, int nkv, i
                                          T* __restrict__ kcache, T* __restrict__ vcache,
                                          const int* __restrict__ block_tables, int bt_stride,
                                          int page_size, int write_kv) {
+    pdl_prologue();
     const size_t n = blockIdx.x;
     const int pos = positions[n];
     const int half = rot / 2;
@@ -312,12 +314,12 @@ EMS_EXPORT int ems_embedding(const void* table, int dtype, const int* tokens, fl
     if (N <= 0) return EMS_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == EMS_F32)
-        embedding_kernel<float><<<N, threads, 0, stream>>>((const float*)table, tokens, residual, H);
-    else if (dtype == EMS_BF16)
-        embedding_kernel<bf16><<<N, threads, 0, stream>>>((const bf16*)table, tokens, residual, H);
-    else
-        return EMS_ERR_DTYPE;
-    return launch_status();
+        return launch_pdl(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float*)table, tokens,
+                          residual, H);
+    if (dtype == EMS_BF16)
+        return launch_pdl(embedding_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, tokens,
+                          residual, H);
+    return EMS_ERR_DTYPE;
 }
 
 // delta may be null (first layer: the embedding is the residual).  rows may be null (all
@@ -333,10 +335,10 @@ EMS_EXPORT int ems_add_rmsnorm(const void* delta, float* residual, const void* w
         const int vecs = H / 4;
         const int vpt = (vecs + 1023) / 1024;                       // 1..4
         const int threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;  // <= 1024
-#define EMS_NORM_VEC(T, V)                                                                          \
-    add_rmsnorm_vec_kernel<T, V><<<num_out, threads, 0, stream>>>((const T*)delta, residual, weight, \
-                                                                  w_dtype, (T*)out, rows, H, eps,     \
-                                                                  write_residual)
+        int rc = EMS_OK;
+#define EMS_NORM_VEC(T, V)                                                                         \
+    rc = launch_pdl(add_rmsnorm_vec_kernel<T, V>, dim3(num_out), dim3(threads), 0, stream, (const T*)delta, \
+                    residual, weight, w_dtype, (T*)out, rows, H, eps, write_residual)
         if (dtype == EMS_F32) {
             if (vpt == 1) EMS_NORM_VEC(float, 1); else if (vpt == 2) EMS_NORM_VEC(float, 2);
             else if (vpt == 3) EMS_NORM_VEC(float, 3); else EMS_NORM_VEC(float, 4);
@@ -347,7 +349,7 @@ EMS_EXPORT int ems_add_rmsnorm(const void* delta, float* residual, const void* w
             return EMS_ERR_DTYPE;
         }
 #undef EMS_NORM_VEC
-        return launch_status();
+        return rc;
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (dtype == EMS_F32)
@@ -408,16 +410,14 @@ EMS_EXPORT int ems_rope_kv_write(void* qkv, int dtype, int N, int nh, int nkv, i
         const int items = (write_kv ? nh + nkv : nh) * (D - rotary_dim / 2) / 4 + (write_kv ? nkv * D / 4 : 0);
         const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
         if (dtype == EMS_F32)
-            rope_kv_write_vec_kernel<float><<<N, threads, 0, stream>>>(
-                (float*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (float*)kcache,
-                (float*)vcache, block_tables, bt_stride, page_size, write_kv);
-        else if (dtype == EMS_BF16)
-            rope_kv_write_vec_kernel<bf16><<<N, threads, 0, stream>>>(
-                (bf16*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (bf16*)kcache,
-                (bf16*)vcache, block_tables, bt_stride, page_size, write_kv);
-        else
-            return EMS_ERR_DTYPE;
-        return launch_status();
+            return launch_pdl(rope_kv_write_vec_kernel<float>, dim3(N), dim3(threads), 0, stream, (float*)qkv, nh,
+                              nkv, D, positions, row_of_token, table, rotary_dim, (float*)kcache, (float*)vcache,
+                              block_tables, bt_stride, page_size, write_kv);
+        if (dtype == EMS_BF16)
+            return launch_pdl(rope_kv_write_vec_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (bf16*)qkv, nh,
+                              nkv, D, positions, row_of_token, table, rotary_dim, (bf16*)kcache, (bf16*)vcache,
+                              block_tables, bt_stride, page_size, write_kv);
+        return EMS_ERR_DTYPE;
     }
     const int heads = write_kv ? nh + 2 * nkv : nh;
     if (heads > 65535) return EMS_ERR_SHAPE;
