@@ -70,7 +70,9 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     const int G = p.G;
     const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0, start = p.starts[b];
     const int nrows = qlen * G;
-    const int r0 = blockIdx.x * PF_BQ;
+    // Row tiles are handed out last first: under the causal mask the last tile of a prompt has
+    // the most keys, and the longest blocks should not be the ones that start last.
+    const int r0 = (int)(gridDim.x - 1 - blockIdx.x) * PF_BQ;
     if (r0 >= nrows) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 

@@ -275,12 +275,12 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
         cluster_sync_all();
         const int me = (int)cluster_rank();
-        const int owned = G5_BM / p.ksplit;  // ksplit is 2, 4 or 8: rows me, me + ksplit, ...
+        const int owned = (G5_BM + p.ksplit - 1) / p.ksplit;  // this block adds rows me, me + ksplit, ...
         bf16* y = reinterpret_cast<bf16*>(p.y);
         for (int idx = threadIdx.x; idx < owned * p.m_tok; idx += G5_THREADS) {
             const int n = idx / owned, rl = (idx % owned) * p.ksplit + me;
             const int orow = tile * G5_BM + rl;
-            if (orow >= p.n_out) continue;
+            if (rl >= G5_BM || orow >= p.n_out) continue;
             const uint32_t addr = a_s + (uint32_t)(n * G5_BM + rl) * 4u;
             float part[8];
 #pragma unroll
@@ -456,7 +456,7 @@ EMS_EXPORT int ems_gemm_smallm_status(void) {
 
 // y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias).
 // m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit >= 1 blocks share K: with
-// scratch == null and ksplit in {2, 4, 8} they form a cluster and reduce on chip; with a
+// scratch == null and ksplit <= 8 they form a cluster and reduce on chip; with a
 // scratch buffer they leave float32 partials for a second kernel.
 EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
                                int k, int ksplit, void* scratch, long long scratch_bytes, cudaStream_t stream) {
@@ -464,7 +464,7 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
     if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 64) return EMS_ERR_SHAPE;
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2)) return EMS_ERR_ALIGN;
     const bool cluster = ksplit > 1 && scratch == nullptr;
-    if (cluster && ksplit != 2 && ksplit != 4 && ksplit != 8) return EMS_ERR_SHAPE;
+    if (cluster && ksplit > 8) return EMS_ERR_SHAPE;  // the portable cluster size
     if (ksplit > 1 && !cluster && scratch_bytes < ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit))
         return EMS_ERR_SCRATCH;
     int* status = status_word();

@@ -277,7 +277,7 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
                 ksplit: int = 1, scratch: torch.Tensor | None = None) -> None:
     """out[m, n] = x[m, :] . weight[n, :] (+ bias[n]) in bfloat16 with float32 accumulation, for
     m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks share K: without
-    `scratch` (ksplit 2, 4 or 8) they form a thread-block cluster and add their accumulators
+    `scratch` (ksplit up to 8) they form a thread-block cluster and add their accumulators
     on chip, in rank order; with `scratch` they leave float32 partials there that a second
     kernel adds in a fixed order."""
     m, k = x.shape

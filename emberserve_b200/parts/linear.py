@@ -38,16 +38,23 @@ _SMALLM_ROWS = 16
 
 
 def smallm_ksplit(m_tok: int, n_out: int, k: int) -> int:
-    """Over how many blocks the small-row kernel splits K: enough that every SM streams
-    weights, a function of the shape alone (so a result never depends on the batch)."""
+    """Over how many blocks (one thread-block cluster, at most 8) the small-row kernel splits
+    K so that the blocks of the product fill the SMs: the smallest split that keeps at least
+    nine tenths of them busy, a function of the shape alone (a result never depends on the
+    batch)."""
     tiles = -(-n_out // 128)
     k_tiles = -(-k // 64)
-    slots = _SMS * (2 if m_tok <= 32 else 1)
-    want = min(slots // max(1, tiles), k_tiles // _MIN_K_TILES_PER_SPLIT)
-    for split in (4, 2):  # the blocks of a split form a cluster (8 gained nothing over 4)
-        if want >= split:
-            return split
-    return 1
+    best, best_fill = 1, 0.0
+    for split in range(1, 9):
+        if split > 1 and k_tiles // split < _MIN_K_TILES_PER_SPLIT:
+            break
+        blocks = tiles * split
+        fill = blocks / (-(-blocks // _SMS) * _SMS)
+        if fill > best_fill + 1e-9:
+            best, best_fill = split, fill
+        if fill >= 0.9:
+            break
+    return best
 
 
 def _use_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> bool:

@@ -416,8 +416,8 @@ def test_gemm_smallm_tcgen05(m, n, k, ksplit, with_bias):
     assert float((out.float() - want).abs().max()) <= 8e-3 * scale + 1e-3, (m, n, k, ksplit)
 
 
-@pytest.mark.parametrize("m,n,k,ksplit", [(1, 256, 512, 2), (8, 4608, 3584, 8), (8, 3584, 3584, 4), (16, 1000, 3584, 8),
-                                          (17, 384, 18944, 8), (32, 3584, 18944, 8), (5, 130, 200, 2), (64, 256, 1024, 4)])
+@pytest.mark.parametrize("m,n,k,ksplit", [(1, 256, 512, 2), (8, 4608, 3584, 8), (8, 3584, 3584, 5), (16, 1000, 3584, 7),
+                                          (17, 384, 18944, 3), (32, 3584, 18944, 5), (5, 130, 200, 2), (64, 256, 1024, 6)])
 def test_gemm_smallm_cluster_split(m, n, k, ksplit):
     """K split over the blocks of a thread-block cluster that add their accumulators through
     distributed shared memory (no scratch, one launch)."""
