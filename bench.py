@@ -409,6 +409,65 @@ def run_kernel(args) -> dict:
     raise SystemExit(f"unknown kernel {args.kernel!r}")
 
 
+SHAPE_05B = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
+                 num_attention_heads=14, num_key_value_heads=2, head_dim=64, max_position_embeddings=32768,
+                 rms_norm_eps=1e-6, rope_theta=1_000_000.0, tie_word_embeddings=True, attention_bias=True,
+                 eos_token_id=151645)
+
+
+def run_serving(args) -> dict:
+    """Continuous batching of many requests through LLM.generate(): 256 requests with
+    uniform-random prompts of 64..1024 tokens and 128..512 output tokens each, Qwen2.5-0.5B
+    shape, bfloat16, random weights.  Wall clock around the whole generate() call."""
+    import random
+
+    import torch
+
+    from emberserve_b200 import kernels as K
+    from emberserve_b200.config.engine import EngineConfig
+    from emberserve_b200.config.model import Qwen2Config
+    from emberserve_b200.engine.llm_engine import LLMEngine
+    from emberserve_b200.engine.runner import ModelRunner
+    from emberserve_b200.llm import LLM
+    from emberserve_b200.sampling.params import SamplingParams
+
+    cfg = Qwen2Config.from_dict(dict(SHAPE_05B, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    K.library()
+    n_req = args.requests
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(64, 1024))] for _ in range(n_req)]
+    params = [SamplingParams(max_tokens=rng.randint(128, 512), temperature=0.0, ignore_eos=True) for _ in range(n_req)]
+    max_len = 2048
+    pages = n_req * (max_len // PAGE_SIZE) + 64
+    runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0", page_size=PAGE_SIZE,
+                                     num_pages=pages)
+    ecfg = EngineConfig(dtype=torch.bfloat16, block_size=PAGE_SIZE, max_model_len=max_len, max_num_seqs=256,
+                        max_num_batched_tokens=2048, enable_chunked_prefill=True)
+    engine = LLMEngine.from_runner(runner, ecfg)
+    engine.keep_stats = True
+    llm = LLM.from_engine(engine)
+    llm.generate(prompts[:8], [SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)] * 8)  # warm-up
+    engine.stats.clear()
+    torch.cuda.synchronize()
+    with ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        results = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    out_tokens = sum(len(r.output_token_ids) for r in results)
+    in_tokens = sum(len(p) for p in prompts)
+    fwd = sorted(s.forward_ms + s.sample_ms for s in engine.stats)
+    return {"metric": "output tok/s, continuous batching of 256 requests (Qwen2.5-0.5B shape)",
+            "value": out_tokens / dt, "unit": "tok/s", "n_gpus": 1, "seconds": dt, "requests": n_req,
+            "output_tokens": out_tokens, "prompt_tokens": in_tokens, "steps": len(engine.stats),
+            "step_ms_p50": fwd[len(fwd) // 2], "step_ms_p99": fwd[int(len(fwd) * 0.99)],
+            "ms_per_step_wall": dt * 1e3 / max(1, len(engine.stats)),
+            "preemptions": sum(s.num_preempted for s in engine.stats), "dtype": "bf16",
+            "data": "synthetic: uniform random token ids and lengths (seed 0), random weights",
+            "config": {"model": "Qwen2.5-0.5B shape", "layers": cfg.num_hidden_layers, "max_num_seqs": 256,
+                       "max_num_batched_tokens": 2048, "page_size": PAGE_SIZE}, "clocks": clocks.summary()}
+
+
 def run_reference(args) -> dict:
     """The unmodified reference, installed under baseline/_ref, through its own LLMEngine."""
     ref = ROOT / "baseline" / "_ref"
@@ -502,6 +561,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b"], default="decode-7b",
+                    help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests")
+    ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
     ap.add_argument("--only", choices=["decode", "prefill", "kernel"], default=None,
                     help="run one small part only (for profiling): decode at --batch, the prefill, or "
@@ -524,6 +586,9 @@ def main() -> int:
         args.warmup = 3
     if args.only == "kernel":
         print(json.dumps(run_kernel(args)))
+        return 0
+    if args.workload == "serve-0.5b":
+        print(json.dumps(run_serving(args)))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
