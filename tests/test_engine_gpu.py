@@ -100,6 +100,31 @@ def test_chunked_mixed_and_preempted_generation_on_the_gpu(sharp_dirs):
     assert st.num_free == st.num_pages
 
 
+def test_command_line_generates_what_the_entry_point_generates(sharp_dirs):
+    """`python -m emberserve_b200 generate --prompt-ids ...` prints the tokens that
+    LLM.generate() returns, and the throughput line on standard error."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from emberserve_b200 import SamplingParams
+
+    name = "tiny_b"
+    prompt = [7, 100, 33, 250, 9]
+    want = _llm(sharp_dirs[name], name, "float32").generate([prompt], SamplingParams.greedy(6, ignore_eos=True))
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run(
+        [sys.executable, "-m", "emberserve_b200", "generate", "--model", str(sharp_dirs[name]), "--dtype",
+         "float32", "--block-size", "8", "--num-blocks", "64", "--max-model-len", "200", "--prompt-ids",
+         ",".join(map(str, prompt)), "--max-tokens", "6"],
+        capture_output=True, text=True, cwd=root, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    got = [int(t) for t in proc.stdout.split()]
+    # the command line stops at an end-of-sequence token, the call above ignored it
+    assert got == want[0].output_token_ids[:len(got)] and 1 <= len(got) <= 6
+    assert "tokens in" in proc.stderr and "finish=" in proc.stderr
+
+
 def test_cpu_device_is_refused(model_dirs):
     from emberserve_b200.engine.runner import ModelRunner
 
