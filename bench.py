@@ -365,9 +365,9 @@ def run_kernel(args) -> dict:
         cu = torch.tensor([0, t], device=dev, dtype=torch.int32)
         st = torch.zeros(1, device=dev, dtype=torch.int32)
         ms = timed(lambda: K.paged_attention(qkv, out, kc, vc, bt, cu, st, 1, t, nh, nkv, d,
-                                             1 / math.sqrt(d), t))
+                                             1 / math.sqrt(d), t, kernel=args.attn_kernel))
         flops = 4 * nh * d * t * t / 2
-        return {"kernel": "prefill_attention", "tokens": t, "ms": ms, "tflops": flops / ms / 1e9,
+        return {"kernel": "prefill_attention", "impl": args.attn_kernel, "tokens": t, "ms": ms, "tflops": flops / ms / 1e9,
                 "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
     if args.kernel == "gemm":
         h, i, v = s["hidden_size"], s["intermediate_size"], s["vocab_size"]
@@ -574,6 +574,8 @@ def main() -> int:
                     help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
     ap.add_argument("--splits", type=int, default=0, help="with --only kernel: key splits (0 = the engine's rule)")
+    ap.add_argument("--attn-kernel", choices=["auto", "mma", "tcgen05", "generic"], default="auto",
+                    help="with --kernel prefill_attention: which of the attention kernels")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --only: add device time per kernel name (torch profiler)")
     ap.add_argument("--layers", type=int, default=None,

@@ -31,4 +31,10 @@ bool prefill_mma_supported(int dtype, int D, long long q_stride, const void* q, 
                            const void* kc, const void* vc);
 int run_prefill_mma(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream);
 
+// The tcgen05 kernel for prompt portions (attention_prefill_tc05.cu): long prompts at head
+// sizes 64 and 128 with pages of a multiple of 16 keys; same parameter block.
+bool prefill_tc05_supported(int dtype, int D, int page_size, long long q_stride, const void* q, const void* out,
+                            const void* kc, const void* vc);
+int run_prefill_tc05(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream);
+
 }  // namespace ems

@@ -310,7 +310,8 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
                                    int B, int N, int nh, int nkv, int D, int window, float scale,
                                    int max_q_len, int splits, void* scratch, long long scratch_bytes,
                                    int impl, cudaStream_t stream) {
-    // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel.
+    // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel, 2 = the
+    // tcgen05 prompt kernel or an error, 3 = the mma.sync kernels where they take the case.
     if (B <= 0 || N <= 0) return EMS_OK;
     if (D <= 0 || D % 16 || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1)
         return EMS_ERR_SHAPE;
@@ -335,10 +336,16 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
     d.q_stride = q_stride; d.bt_stride = bt_stride; d.page_size = page_size; d.nh = nh; d.nkv = nkv;
     d.G = p.G; d.window = window; d.splits = splits;
     d.scale_log2 = scale * 1.4426950408889634f;
-    if (impl == 0 && splits == 1 && max_q_len > 1 &&
+    // impl 2 asks for the tcgen05 prompt kernel whatever the length (tests); by default it
+    // takes the portions that fill its 128-row tiles.
+    if ((impl == 2 || (impl == 0 && (long long)max_q_len * p.G >= 256)) && splits == 1 && max_q_len > 1 &&
+        prefill_tc05_supported(dtype, D, page_size, q_stride, q, out, kcache, vcache))
+        return run_prefill_tc05(d, B, D, max_q_len, stream);
+    if (impl == 2) return EMS_ERR_SHAPE;
+    if ((impl == 0 || impl == 3) && splits == 1 && max_q_len > 1 &&
         prefill_mma_supported(dtype, D, q_stride, q, out, kcache, vcache))
         return run_prefill_mma(d, B, D, max_q_len, stream);
-    if (impl == 0 && max_q_len == 1 && N == B &&
+    if ((impl == 0 || impl == 3) && max_q_len == 1 && N == B &&
         decode_mma_supported(dtype, D, p.G, q_stride, q, kcache, vcache)) {
         const int rc = run_decode_mma(d, B, D, stream);
         if (rc != EMS_OK || splits == 1) return rc;

@@ -402,6 +402,12 @@ static int* status_word() {  // host-mapped, so the host reads it without a CUDA
     return host;
 }
 
+// The same word serves the other tcgen05 kernels of the library (the prompt attention).
+int* tc_status_device_ptr() { return status_word(); }
+bool tc_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+    return tensor_map_2d(ptr, rows, cols, box_rows, out);
+}
+
 template <int NT, bool DUAL>
 static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
                         cudaStream_t stream) {

@@ -214,15 +214,22 @@ def attention_scratch_bytes(num_tokens: int, num_heads: int, head_dim: int, spli
     return int(library().ems_paged_attention_scratch_bytes(num_tokens, num_heads, head_dim, splits))
 
 
+_ATTENTION_IMPL = {"auto": 0, "generic": 1, "tcgen05": 2, "mma": 3}
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                     block_tables: torch.Tensor, cu_q: torch.Tensor, starts: torch.Tensor,
                     num_rows: int, num_tokens: int, num_heads: int, num_kv_heads: int,
                     head_dim: int, scale: float, max_q_len: int, window: int | None = None,
-                    splits: int = 1, scratch: torch.Tensor | None = None, generic: bool = False) -> None:
+                    splits: int = 1, scratch: torch.Tensor | None = None, generic: bool = False,
+                    tcgen05: bool = False, kernel: str = "auto") -> None:
     """Causal grouped-query attention of every packed query over its request's pages.
     `q` is a [N, stride] tensor whose first nh*D columns are the queries (a view of the
     qkv buffer is fine); `out` is [N, nh*D].  `generic=True` forces the generic kernel where
-    a faster one would take the case (tests compare the two)."""
+    a faster one would take the case (tests compare the two); `tcgen05=True` asks for the
+    tcgen05 prompt kernel at any length (by default it takes the long portions) and raises if
+    that kernel does not take the case.  `kernel` says the same by name: "auto", "generic",
+    "tcgen05", or "mma" (the mma.sync kernels where they take the case)."""
     assert q.stride(1) == 1 and out.is_contiguous() and q.dtype == out.dtype == kcache.dtype
     page_size = kcache.shape[2]
     assert kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
@@ -234,7 +241,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
         _i32(cu_q, "cu_q"), _i32(starts, "starts"), num_rows, num_tokens, num_heads, num_kv_heads,
         head_dim, int(window or 0), float(scale), max_q_len, splits,
         _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
-        1 if generic else 0, _stream()), "paged_attention", 2 if splits > 1 else 1)
+        _ATTENTION_IMPL["generic" if generic else ("tcgen05" if tcgen05 else kernel)], _stream()),
+        "paged_attention", 2 if splits > 1 else 1)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

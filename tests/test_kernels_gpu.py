@@ -146,7 +146,7 @@ def test_rope_kv_write(dtype, nh, nkv, d, rot, ps):
     assert torch.equal(qc[:, nh * d:], qkv[:, nh * d:])
 
 
-def _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, splits, seed=4, peaky=False):
+def _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, splits, seed=4, peaky=False, **how):
     g = torch.Generator(device="cuda").manual_seed(seed)
     b = len(q_lens)
     n = sum(q_lens)
@@ -170,7 +170,7 @@ def _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, splits, seed=
     if splits > 1:
         scratch = torch.empty(K().attention_scratch_bytes(n, nh, d, splits) // 4, device=dev())
     K().paged_attention(qkv, got, kc, vc, perm, cu, st, b, n, nh, nkv, d, scale, max(q_lens),
-                        window=window, splits=splits, scratch=scratch)
+                        window=window, splits=splits, scratch=scratch, **how)
     ref.paged_attention(qkv, want, kc, vc, perm, cu, st, b, n, nh, nkv, d, scale, max(q_lens),
                         window=window, compute_dtype=torch.float64)
     return got.float(), want.float()
@@ -253,6 +253,74 @@ def test_prefill_tensor_core_kernel(nh, nkv, d, ps, window):
     starts = [0, 200, 64, 119, 0, 63, 0, 300]
     got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=21, peaky=True)
     torch.testing.assert_close(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (16, 1, 128, 16), (8, 8, 64, 32),
+                                         (7, 1, 128, 48), (6, 3, 64, 32), (8, 4, 128, 16), (2, 1, 64, 48)])
+@pytest.mark.parametrize("window", [None, 1, 40, 64, 65, 200])
+def test_prefill_tcgen05_kernel(nh, nkv, d, ps, window):
+    """The tcgen05 kernel for prompt portions (head sizes 64 and 128, pages of a multiple of 16
+    keys), forced at every length: rows that end inside a 128-row tile, tiles that span tokens
+    of several heads, contexts around the 64-key tile."""
+    dtype = torch.bfloat16
+    q_lens = [130, 1, 64, 9, 2, 65, 1, 33]
+    starts = [0, 200, 64, 119, 0, 63, 0, 300]
+    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=21, peaky=True,
+                                tcgen05=True)
+    torch.testing.assert_close(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(28, 4, 128, 16, None), (14, 2, 64, 16, 300), (5, 5, 128, 16, None),
+                                                (12, 2, 128, 48, 1000), (3, 1, 64, 2, None)])
+def test_prefill_tcgen05_kernel_long(nh, nkv, d, ps, window):
+    """Long portions (many key tiles, both stages of the K/V ring used many times) on the
+    default dispatch, which sends them to the tcgen05 kernel."""
+    dtype = torch.bfloat16
+    q_lens = [700, 1, 391]
+    starts = [0, 900, 1234]
+    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=22, peaky=True)
+    torch.testing.assert_close(got, want, **tol(dtype))
+    got2, _ = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=22, peaky=True, generic=True)
+    torch.testing.assert_close(got, got2, **tol(dtype))
+
+
+def test_prefill_tcgen05_kernel_refuses_other_pages():
+    with pytest.raises(Exception, match="paged_attention"):
+        _attention_case(torch.bfloat16, 4, 2, 64, 8, [40], [0], None, 1, tcgen05=True)
+
+
+@pytest.mark.parametrize("kernel", ["auto", "generic", "mma", "tcgen05"])
+@pytest.mark.parametrize("window", [None, 90])
+def test_attention_ignores_slots_without_a_key(kernel, window):
+    """Cache slots behind the end of a context (and pages nobody owns) hold non-numbers: a
+    kernel that let them touch a product, even with a zero weight, would return them."""
+    dtype, nh, nkv, d, ps = torch.bfloat16, 8, 2, 128, 16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q_lens, starts = [300, 70, 1], [0, 201, 333]
+    b, n = len(q_lens), sum(q_lens)
+    ctx = [s + q for s, q in zip(starts, q_lens)]
+    width = max(-(-c // ps) for c in ctx) + 1
+    pages = b * width + 3
+    perm = torch.randperm(pages, device=dev(), generator=g)[: b * width].view(b, width).to(torch.int32)
+    kc = torch.full((pages, nkv, ps, d), float("nan"), dtype=dtype, device=dev())
+    vc = torch.full_like(kc, float("nan"))
+    for r in range(b):
+        first = max(0, starts[r] - window + 1) if window else 0  # older keys: behind every window
+        for pos in range(first, ctx[r]):
+            page = int(perm[r, pos // ps])
+            kc[page, :, pos % ps] = torch.randn(nkv, d, device=dev(), generator=g).to(dtype)
+            vc[page, :, pos % ps] = torch.randn(nkv, d, device=dev(), generator=g).to(dtype)
+    qkv = torch.randn(n, (nh + 2 * nkv) * d, device=dev(), generator=g).to(dtype)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=dev(), dtype=torch.int32)
+    st = torch.tensor(starts, device=dev(), dtype=torch.int32)
+    got = torch.full((n, nh * d), float("nan"), dtype=dtype, device=dev())
+    want = torch.empty_like(got)
+    K().paged_attention(qkv, got, kc, vc, perm, cu, st, b, n, nh, nkv, d, 1 / math.sqrt(d), max(q_lens),
+                        window=window, kernel=kernel)
+    ref.paged_attention(qkv, want, kc, vc, perm, cu, st, b, n, nh, nkv, d, 1 / math.sqrt(d), max(q_lens),
+                        window=window, compute_dtype=torch.float64)
+    assert torch.isfinite(want.float()).all()
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
 def test_prefill_tensor_core_kernel_equals_generic_kernel():
