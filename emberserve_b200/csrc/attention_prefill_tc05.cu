@@ -5,21 +5,24 @@
 //
 // A block owns 256 "rows" of one request and one KV head, as two tiles A and B of 128 (a row
 // is a (query token, query head of the group) pair, so the heads that share a KV head share
-// every K/V tile), and walks the keys in tiles of 64 aligned to absolute positions.  Its warps
+// every K/V tile), and walks the keys in tiles of 128 aligned to absolute positions.  Its warps
 // have fixed roles that meet only through mbarriers:
 //   loader (1 warp)     K and V tiles by TMA: pages are multiples of 16 keys, so 16 keys of one KV
 //                       head are one box of a tensor map over the cache seen as a matrix
-//                       [pages * kv heads * page size, D], found through the block table; four
+//                       [pages * kv heads * page size, D], found through the block table; eight
 //                       boxes (per 64-column span) make a tile in the 128-byte-swizzled layout of
-//                       the tensor cores, in a ring of three stages.  Rows of V that hold no key
+//                       the tensor cores; K and V have rings of two stages each, freed
+//                       separately (K as soon as both S products have read it).  Rows of V that hold no key
 //                       of this block (the end of the last tile, the start of a window) are
 //                       zeroed after they land, since a zero probability times a stale
 //                       non-number would still poison the row;
-//   MMA (1 thread)      S_X = Q_X K^T (128 x 64 x D, K-major operands from shared memory, S in
-//                       tensor memory), and O_X += P_X V (128 x D x 64) with P read from tensor
+//   MMA (1 warp)        S_X = Q_X K^T (128 x 128 x D, K-major operands from shared memory, S in
+//                       tensor memory), and O_X += P_X V (128 x D x 128) with P read from tensor
 //                       memory and V consumed as it lies in the cache, keys by rows (an MN-major
 //                       operand); X alternates between A and B, so the tensor pipe works on one
-//                       tile while the other tile's softmax runs;
+//                       tile while the other tile's softmax runs.  The warp runs its loop as a
+//                       whole (addresses and descriptors are the same in every lane) and one
+//                       elected lane issues the instructions;
 //   softmax (2 x 4 warps) thread r of a group owns row r: it reads its lane of S (tcgen05.ld),
 //                       masks, keeps the running maximum and sum in float32 (base-2
 //                       exponentials), and writes P = 2^(s - m) as bfloat16 over S
@@ -44,8 +47,8 @@ int* tc_status_device_ptr();
 bool tc_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out);
 
 constexpr int T5_BQ = 128;       // rows per tile = MMA M
-constexpr int T5_BK = 64;        // keys per tile
-constexpr int T5_STAGES = 3;     // K/V ring
+constexpr int T5_BK = 128;       // keys per tile
+constexpr int T5_STAGES = 2;     // stages of the K ring and of the V ring
 constexpr int T5_THREADS = 320;  // warps 0-3: softmax A, 4-7: softmax B, 8: MMA + tensor memory, 9: loader
 constexpr uint32_t T5_SPIN_LIMIT = 1u << 18;
 constexpr float T5_RESCALE_LOG2 = 8.0f;
@@ -140,6 +143,22 @@ __device__ __forceinline__ void t5_st32(uint32_t taddr, const uint32_t (&r)[32])
         "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
         ::T5_IN32(r), "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void t5_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr) : "memory");
+}
+__device__ __forceinline__ bool t5_elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void t5_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float t5_ex2(float x) {
     float y;
@@ -165,11 +184,11 @@ template <int D> struct T5Layout {
     static constexpr int KV_SPAN = T5_BK * 128;       // bytes of one span of a K or V tile
     static constexpr int Q_BYTES = SPANS * Q_SPAN;    // one Q tile
     static constexpr int KV_BYTES = SPANS * KV_SPAN;  // one K or V tile
-    static constexpr int NUM_BARS = 3 * T5_STAGES + 7;
+    static constexpr int NUM_BARS = 4 * T5_STAGES + 7;
     static constexpr int SMEM = 2 * Q_BYTES + 2 * T5_STAGES * KV_BYTES + NUM_BARS * 8 + 16 + T5_ALIGN_SLACK;
-    // tensor memory columns: S_A, S_B (64 each; P overlays the first 32), O_A, O_B (D each)
-    static constexpr uint32_t S_COL = 0, O_COL = 128;
-    static constexpr uint32_t TMEM_COLS = D == 128 ? 512 : 256;
+    // tensor memory columns: S_A, S_B (128 each; P overlays the first 64), O_A, O_B (D each)
+    static constexpr uint32_t S_COL = 0, O_COL = 2 * T5_BK;
+    static constexpr uint32_t TMEM_COLS = 512;
 };
 
 template <int D>
@@ -177,23 +196,24 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
 prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v) {
     using L = T5Layout<D>;
-    // D float32, A and B bfloat16; S: both K-major, N = 64; PV: B MN-major, N = D
+    // D float32, A and B bfloat16; S: both K-major, N = 128 keys; PV: B MN-major, N = D
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(T5_BK >> 3) << 17) | (8u << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | (8u << 24);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = (t5_smem(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - t5_smem(smem_raw));
-    const uint32_t q_s = base, kv_s = q_s + 2 * L::Q_BYTES;  // stage st: K tile, then V tile
+    const uint32_t q_s = base, k_s = q_s + 2 * L::Q_BYTES, v_s = k_s + T5_STAGES * L::KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + 2 * L::Q_BYTES + 2 * T5_STAGES * L::KV_BYTES);
     const uint32_t bar0 = t5_smem(bars);
-    // barriers: kfull[st], vfull[st], kvempty[st], then sfull[X], pfull[X], ofull[X], vland
+    // barriers: kfull, vfull, kempty, vempty (per stage), then sfull[X], pfull[X], ofull[X], vland
     auto kfull = [&](int st) { return bar0 + 8u * st; };
     auto vfull = [&](int st) { return bar0 + 8u * (T5_STAGES + st); };
-    auto kvempty = [&](int st) { return bar0 + 8u * (2 * T5_STAGES + st); };
-    auto sfull = [&](int x) { return bar0 + 8u * (3 * T5_STAGES + x); };
-    auto pfull = [&](int x) { return bar0 + 8u * (3 * T5_STAGES + 2 + x); };
-    auto ofull = [&](int x) { return bar0 + 8u * (3 * T5_STAGES + 4 + x); };
-    const uint32_t vland = bar0 + 8u * (3 * T5_STAGES + 6);
+    auto kempty = [&](int st) { return bar0 + 8u * (2 * T5_STAGES + st); };
+    auto vempty = [&](int st) { return bar0 + 8u * (3 * T5_STAGES + st); };
+    auto sfull = [&](int x) { return bar0 + 8u * (4 * T5_STAGES + x); };
+    auto pfull = [&](int x) { return bar0 + 8u * (4 * T5_STAGES + 2 + x); };
+    auto ofull = [&](int x) { return bar0 + 8u * (4 * T5_STAGES + 4 + x); };
+    const uint32_t vland = bar0 + 8u * (4 * T5_STAGES + 6);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
 
     const int b = blockIdx.z, hk = blockIdx.y;
@@ -216,11 +236,7 @@ prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_co
     const int* table = p.bt + (size_t)b * p.bt_stride;
 
     if (tid == 0) {
-        for (int st = 0; st < T5_STAGES; ++st) {
-            t5_mbar_init(kfull(st), 1);
-            t5_mbar_init(vfull(st), 1);
-            t5_mbar_init(kvempty(st), 1);
-        }
+        for (int i = 0; i < 4 * T5_STAGES; ++i) t5_mbar_init(bar0 + 8u * i, 1);
         t5_mbar_init(vland, 1);
         for (int x = 0; x < 2; ++x) {
             t5_mbar_init(sfull(x), 1);
@@ -255,55 +271,54 @@ prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_co
     t5_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
+    // every lane of a warp polls, so a wait that runs out ends the role for the whole warp
+    auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
+        if (ok) ok = t5_wait(bar, parity, status, code);
+        ok = __all_sync(0xffffffffu, ok);
+        return ok;
+    };
 
     if (warp == 9) {
         // ---- loader ------------------------------------------------------------------------
         constexpr uint32_t GROUP_BYTES = 16 * D * 2;  // 16 keys of one KV head
+        constexpr int GROUPS = T5_BK / 16;
         uint32_t edges = 0;
         int issued = 0;
         for (int j = 0; j < n_all; ++j) {
             const int st = j % T5_STAGES;
-            if (j >= T5_STAGES && ok) ok = t5_wait(kvempty(st), (uint32_t)(j / T5_STAGES - 1) & 1u, status, 11);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            const uint32_t free_ph = (uint32_t)(j / T5_STAGES - 1) & 1u;
             const int kt = kt0 + j * T5_BK;
-            // lane g < 4 finds the rows of key group g in the cache matrix (-1: no key of ours)
-            const int key0 = kt + (lane & 3) * 16;
+            // lane g < 8 finds the rows of key group g in the cache matrix (-1: no key of ours)
+            const int key0 = kt + (lane & (GROUPS - 1)) * 16;
             int row = -1;
             if (key0 < k_end && key0 + 16 > k_begin)
                 row = (table[key0 / p.page_size] * p.nkv + hk) * p.page_size + key0 % p.page_size;
-            int rows[4];
-#pragma unroll
-            for (int g16 = 0; g16 < 4; ++g16) rows[g16] = __shfl_sync(0xffffffffu, row, g16);
+            const uint32_t have = __ballot_sync(0xffffffffu, row >= 0) & ((1u << GROUPS) - 1);
+            const uint32_t bytes = GROUP_BYTES * __popc(have);
             const bool edge = kt < k_begin || kt + T5_BK > k_end;  // some rows of the tile hold no key of ours
-            if (lane == 0) {
-                const uint32_t bytes =
-                    GROUP_BYTES * ((rows[0] >= 0) + (rows[1] >= 0) + (rows[2] >= 0) + (rows[3] >= 0));
-                const uint32_t kdst = kv_s + st * 2 * L::KV_BYTES, vdst = kdst + L::KV_BYTES;
-                const uint32_t vbar = edge ? vland : vfull(st);
-                t5_expect_tx(kfull(st), bytes);
+            if (j >= T5_STAGES && !wait_warp(kempty(st), free_ph, 11)) break;
+            if (lane == 0) t5_expect_tx(kfull(st), bytes);
+            __syncwarp();
+            if (lane < GROUPS && row >= 0) {  // one lane per group issues its boxes
 #pragma unroll
-                for (int g16 = 0; g16 < 4; ++g16)
-                    if (rows[g16] >= 0)
+                for (int sp = 0; sp < L::SPANS; ++sp)
+                    t5_tma_2d(k_s + st * L::KV_BYTES + sp * L::KV_SPAN + lane * 2048, &map_k, sp * 64, row, kfull(st));
+            }
+            if (j >= T5_STAGES && !wait_warp(vempty(st), free_ph, 12)) break;
+            const uint32_t vbar = edge ? vland : vfull(st);
+            if (lane == 0) t5_expect_tx(vbar, bytes);
+            __syncwarp();
+            if (lane < GROUPS && row >= 0) {
 #pragma unroll
-                        for (int sp = 0; sp < L::SPANS; ++sp)
-                            t5_tma_2d(kdst + sp * L::KV_SPAN + g16 * 2048, &map_k, sp * 64, rows[g16], kfull(st));
-                t5_expect_tx(vbar, bytes);
-#pragma unroll
-                for (int g16 = 0; g16 < 4; ++g16)
-                    if (rows[g16] >= 0)
-#pragma unroll
-                        for (int sp = 0; sp < L::SPANS; ++sp)
-                            t5_tma_2d(vdst + sp * L::KV_SPAN + g16 * 2048, &map_v, sp * 64, rows[g16], vbar);
+                for (int sp = 0; sp < L::SPANS; ++sp)
+                    t5_tma_2d(v_s + st * L::KV_BYTES + sp * L::KV_SPAN + lane * 2048, &map_v, sp * 64, row, vbar);
             }
             issued = j + 1;
             if (edge) {
                 // wait until V has landed, zero the rows without a key, then hand the tile over
-                if (ok) ok = t5_wait(vland, edges & 1u, status, 19);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!wait_warp(vland, edges & 1u, 13)) break;
                 ++edges;
-                const uint32_t vdst = kv_s + st * 2 * L::KV_BYTES + L::KV_BYTES;
+                const uint32_t vdst = v_s + st * L::KV_BYTES;
                 for (int idx = lane; idx < T5_BK * (D / 8); idx += 32) {
                     const int r = idx / (D / 8), c = idx % (D / 8);
                     const int key = kt + r;
@@ -323,52 +338,53 @@ prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_co
             }
         }
     } else if (warp == 8) {
-        // ---- MMA issue (one thread) ----------------------------------------------------------
-        if (lane == 0) {
-            auto issue_s = [&](int x, int j) {
-                const uint32_t kst = kv_s + (j % T5_STAGES) * 2 * L::KV_BYTES;
+        // ---- MMA issue: the warp runs the loop, one elected lane issues --------------------------
+        const bool leader = t5_elect_one();
+        const int n_of[2] = {n_a, n_b};
+        auto issue_s = [&](int x, int j) {  // S_X(j) = Q_X K(j)^T
+            const int st = j % T5_STAGES;
+            const uint64_t dq = t5_desc(q_s + x * L::Q_BYTES, 16, 1024);
+            const uint64_t dk = t5_desc(k_s + st * L::KV_BYTES, 16, 1024);
+            if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t da = t5_desc(q_s + x * L::Q_BYTES + (ks / 4) * L::Q_SPAN, 16, 1024) + 2 * (ks % 4);
-                    const uint64_t db = t5_desc(kst + (ks / 4) * L::KV_SPAN, 16, 1024) + 2 * (ks % 4);
-                    t5_mma_ss(tmem + L::S_COL + x * T5_BK, da, db, IDESC_S, ks > 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < D / 16; ++ks)  // 16 elements of D: 32 bytes in a span, spans apart
+                    t5_mma_ss(tmem + L::S_COL + x * T5_BK, dq + (uint64_t)((ks / 4) * (L::Q_SPAN >> 4) + 2 * (ks % 4)),
+                              dk + (uint64_t)((ks / 4) * (L::KV_SPAN >> 4) + 2 * (ks % 4)), IDESC_S, ks > 0 ? 1u : 0u);
                 t5_commit(sfull(x));
-            };
-            const int n_of[2] = {n_a, n_b};
-            if (ok) ok = t5_wait(kfull(0), 0, status, 12);
-            t5_fence_after();
-            if (ok) {
-                issue_s(0, 0);
-                if (n_b > 0) issue_s(1, 0);
+                if (x == 1 || j >= n_b) t5_commit(kempty(st));  // the last reader of this K tile
             }
-            for (int j = 0; j < n_all && ok; ++j) {
-                const int st = j % T5_STAGES;
-                const uint32_t ring_ph = (uint32_t)(j / T5_STAGES) & 1u;
-                const uint32_t vst = kv_s + st * 2 * L::KV_BYTES + L::KV_BYTES;
+            __syncwarp();
+        };
+        if (wait_warp(kfull(0), 0, 14)) {
+            t5_fence_after();
+            issue_s(0, 0);
+            if (n_b > 0) issue_s(1, 0);
+        }
+        for (int j = 0; j < n_all && ok; ++j) {
+            const int st = j % T5_STAGES;
+            const uint32_t ring_ph = (uint32_t)(j / T5_STAGES) & 1u;
 #pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    if (j >= n_of[x] || !ok) continue;
-                    ok = t5_wait(pfull(x), (uint32_t)j & 1u, status, 13);  // P_X(j) is written, O_X rescaled
-                    if (ok) ok = t5_wait(vfull(st), ring_ph, status, 14);
-                    if (!ok) break;
-                    t5_fence_after();
+            for (int x = 0; x < 2; ++x) {
+                if (j >= n_of[x] || !ok) continue;
+                if (!wait_warp(pfull(x), (uint32_t)j & 1u, 15)) break;  // P_X(j) is written, O_X rescaled
+                if (!wait_warp(vfull(st), ring_ph, 16)) break;
+                t5_fence_after();
+                // P: 16 keys = 8 columns of packed pairs.  V, MN-major: 16 keys = two 8-row groups
+                // 1024 bytes apart (2048 bytes per step), D/64 spans KV_SPAN apart.
+                const uint64_t dv = t5_desc(v_s + st * L::KV_BYTES, L::KV_SPAN, 1024);
+                if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < T5_BK / 16; ++kk) {
-                        // P: 16 keys = 8 columns of packed pairs.  V, MN-major: 16 keys = two 8-row
-                        // groups 1024 bytes apart, D/64 spans KV_SPAN apart.
-                        const uint64_t db = t5_desc(vst + kk * 16 * 128, L::KV_SPAN, 1024);
-                        t5_mma_ts(tmem + L::O_COL + x * D, tmem + L::S_COL + x * T5_BK + kk * 8, db, IDESC_PV,
-                                  (j > 0 || kk > 0) ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < T5_BK / 16; ++kk)
+                        t5_mma_ts(tmem + L::O_COL + x * D, tmem + L::S_COL + x * T5_BK + kk * 8,
+                                  dv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
                     t5_commit(ofull(x));
-                    if (x == 1 || j >= n_b) t5_commit(kvempty(st));  // the last reader of the stage
-                    if (j + 1 < n_of[x]) {
-                        ok = t5_wait(kfull((j + 1) % T5_STAGES), (uint32_t)((j + 1) / T5_STAGES) & 1u, status, 15);
-                        if (!ok) break;
-                        t5_fence_after();
-                        issue_s(x, j + 1);  // overwrites P_X(j) behind the MMAs above (in issue order)
-                    }
+                    if (x == 1 || j >= n_b) t5_commit(vempty(st));  // the last reader of this V tile
+                }
+                __syncwarp();
+                if (j + 1 < n_of[x]) {
+                    if (!wait_warp(kfull((j + 1) % T5_STAGES), (uint32_t)((j + 1) / T5_STAGES) & 1u, 17)) break;
+                    t5_fence_after();
+                    issue_s(x, j + 1);  // overwrites P_X(j) behind the products above (in issue order)
                 }
             }
         }
@@ -386,36 +402,40 @@ prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_co
         float m_ref = -INFINITY, l_run = 0.f;  // reference point of the exponentials, running sum
         for (int j = 0; j < n_mine; ++j) {
             const int kt = kt0 + j * T5_BK;
-            if (ok) ok = t5_wait(sfull(x), (uint32_t)j & 1u, status, 16);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!wait_warp(sfull(x), (uint32_t)j & 1u, 18)) break;
             t5_fence_after();
-            uint32_t sr[2][32];
-            t5_ld32(s_addr, sr[0]);
-            t5_ld32(s_addr + 32, sr[1]);
-            t5_ld_wait();
-            // visible keys of this row in the tile: lo <= i <= hi
+            // visible keys of this row in the tile: lo <= i <= hi; only tiles on an edge pay for the mask
             const int hi = qpos - kt, lo = p.window > 0 ? qpos - p.window + 1 - kt : -(1 << 30);
-            if (!__all_sync(0xffffffffu, hi >= T5_BK - 1 && lo <= 0)) {  // only tiles on an edge pay for the mask
+            const bool masked = !__all_sync(0xffffffffu, hi >= T5_BK - 1 && lo <= 0);
+            auto mask = [&](uint32_t (&v)[32], int c0) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (h * 32 + i > hi || h * 32 + i < lo) sr[h][i] = 0xff800000u;  // -inf
-            }
+                for (int i = 0; i < 32; ++i)
+                    if (c0 + i > hi || c0 + i < lo) v[i] = 0xff800000u;  // -inf
+            };
+            // first pass over the row of S: its maximum
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int c0 = 0; c0 < T5_BK; c0 += 64) {
+                uint32_t va[32], vb[32];
+                t5_ld32(s_addr + c0, va);
+                t5_ld32(s_addr + c0 + 32, vb);
+                t5_ld_wait();
+                if (masked) {
+                    mask(va, c0);
+                    mask(vb, c0 + 32);
+                }
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[h][i]));
+                for (int i = 0; i < 32; ++i) {
+                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(va[i]));
+                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(vb[i]));
+                }
+            }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = mx * sl2;  // -inf where the row sees nothing here
             const bool grow = m_new > m_ref + T5_RESCALE_LOG2 || (m_ref == -INFINITY && m_new > -INFINITY);
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
                 // O_X holds the tiles before this one once their last product has completed
-                if (ok) ok = t5_wait(ofull(x), (uint32_t)(j - 1) & 1u, status, 17);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!wait_warp(ofull(x), (uint32_t)(j - 1) & 1u, 19)) break;
                 t5_fence_after();
                 const float f = grow ? t5_ex2(m_ref - m_new) : 1.0f;  // 0 from -inf: O and l are 0 there
                 l_run *= f;
@@ -431,45 +451,57 @@ prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_co
             }
             if (grow) m_ref = m_new;
             const float mb = m_ref == -INFINITY ? 0.f : m_ref;
+            // second pass: P = 2^(s * scale - m) as bfloat16 pairs over the first half of S (the pairs
+            // of columns [c0, c0 + 32) land in columns [c0 / 2, c0 / 2 + 16), which were read before)
             float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pr[32];
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int c0 = 0; c0 < T5_BK; c0 += 64) {
+                uint32_t va[32], vb[32];
+                t5_ld32(s_addr + c0, va);
+                t5_ld32(s_addr + c0 + 32, vb);
+                t5_ld_wait();
+                if (masked) {
+                    mask(va, c0);
+                    mask(vb, c0 + 32);
+                }
+                uint32_t pa[16], pb[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float e0 = t5_ex2(fmaf(__uint_as_float(sr[h][i]), sl2, -mb));
-                    const float e1 = t5_ex2(fmaf(__uint_as_float(sr[h][i + 1]), sl2, -mb));
-                    ps4[(i >> 1) & 3] += e0 + e1;
-                    pr[h * 16 + i / 2] = t5_pack(e0, e1);
+                    const float e0 = t5_ex2(fmaf(__uint_as_float(va[i]), sl2, -mb));
+                    const float e1 = t5_ex2(fmaf(__uint_as_float(va[i + 1]), sl2, -mb));
+                    const float e2 = t5_ex2(fmaf(__uint_as_float(vb[i]), sl2, -mb));
+                    const float e3 = t5_ex2(fmaf(__uint_as_float(vb[i + 1]), sl2, -mb));
+                    ps4[(i >> 1) & 1] += e0 + e1;
+                    ps4[2 + ((i >> 1) & 1)] += e2 + e3;
+                    pa[i / 2] = t5_pack(e0, e1);
+                    pb[i / 2] = t5_pack(e2, e3);
                 }
+                t5_st16(s_addr + c0 / 2, pa);
+                t5_st16(s_addr + c0 / 2 + 16, pb);
+            }
             l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-            t5_st32(s_addr, pr);  // P over the first half of S: key pairs in 32-bit columns
             t5_st_wait();
             t5_fence_before();
             t5_arrive(pfull(x));
         }
-        if (n_mine > 0) {
-            if (ok) ok = t5_wait(ofull(x), (uint32_t)(n_mine - 1) & 1u, status, 18);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                t5_fence_after();
-                const float inv = 1.0f / l_run;
-                bf16* dst = p.out + ((size_t)(q0 + my_row / G) * p.nh + hk * G + my_row % G) * D;
+        if (n_mine > 0 && wait_warp(ofull(x), (uint32_t)(n_mine - 1) & 1u, 21)) {
+            t5_fence_after();
+            const float inv = 1.0f / l_run;
+            bf16* dst = p.out + ((size_t)(q0 + my_row / G) * p.nh + hk * G + my_row % G) * D;
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t orr[32];
-                    t5_ld32(o_addr + c0, orr);
-                    t5_ld_wait();
-                    if (live) {
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t orr[32];
+                t5_ld32(o_addr + c0, orr);
+                t5_ld_wait();
+                if (live) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 w;
-                            w.x = t5_pack(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv);
-                            w.y = t5_pack(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv);
-                            w.z = t5_pack(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv);
-                            w.w = t5_pack(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv);
-                            *reinterpret_cast<uint4*>(dst + c0 + i) = w;
-                        }
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = t5_pack(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv);
+                        w.y = t5_pack(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv);
+                        w.z = t5_pack(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv);
+                        w.w = t5_pack(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + i) = w;
                     }
                 }
             }
