@@ -355,20 +355,21 @@ def run_kernel(args) -> dict:
         return {"kernel": "decode_attention", "batch": b, "context": ctx, "splits": splits, "ms": ms,
                 "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
     if args.kernel == "prefill_attention":
-        t = args.context
-        width = t // ps + 1
+        t, s0 = args.context, args.start  # a portion of t tokens behind s0 cached keys
+        width = (s0 + t) // ps + 1
         kc = torch.randn(width, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
         vc = torch.randn(width, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
         bt = torch.randperm(width, device=dev, generator=g).view(1, width).to(torch.int32)
         qkv = torch.randn(t, (nh + 2 * nkv) * d, device=dev, generator=g).to(torch.bfloat16)
         out = torch.empty(t, nh * d, device=dev, dtype=torch.bfloat16)
         cu = torch.tensor([0, t], device=dev, dtype=torch.int32)
-        st = torch.zeros(1, device=dev, dtype=torch.int32)
+        st = torch.full((1,), s0, device=dev, dtype=torch.int32)
         ms = timed(lambda: K.paged_attention(qkv, out, kc, vc, bt, cu, st, 1, t, nh, nkv, d,
                                              1 / math.sqrt(d), t, kernel=args.attn_kernel))
-        flops = 4 * nh * d * t * t / 2
-        return {"kernel": "prefill_attention", "impl": args.attn_kernel, "tokens": t, "ms": ms, "tflops": flops / ms / 1e9,
-                "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
+        K.check_status()
+        flops = 4 * nh * d * (t * s0 + t * t / 2)
+        return {"kernel": "prefill_attention", "impl": args.attn_kernel, "tokens": t, "start": s0, "ms": ms,
+                "tflops": flops / ms / 1e9, "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"]}
     if args.kernel == "gemm":
         h, i, v = s["hidden_size"], s["intermediate_size"], s["vocab_size"]
         shapes = {"qkv": ((nh + 2 * nkv) * d, h), "o": (h, nh * d), "gate_up": (2 * i, h), "down": (h, i),
@@ -573,6 +574,8 @@ def main() -> int:
     ap.add_argument("--shape", choices=["qkv", "o", "gate_up", "down", "head"], default="qkv",
                     help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
+    ap.add_argument("--start", type=int, default=0,
+                    help="with --kernel prefill_attention: keys cached before the portion")
     ap.add_argument("--splits", type=int, default=0, help="with --only kernel: key splits (0 = the engine's rule)")
     ap.add_argument("--attn-kernel", choices=["auto", "mma", "tcgen05", "generic"], default="auto",
                     help="with --kernel prefill_attention: which of the attention kernels")

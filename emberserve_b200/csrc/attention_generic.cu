@@ -336,9 +336,10 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
     d.q_stride = q_stride; d.bt_stride = bt_stride; d.page_size = page_size; d.nh = nh; d.nkv = nkv;
     d.G = p.G; d.window = window; d.splits = splits;
     d.scale_log2 = scale * 1.4426950408889634f;
-    // impl 2 asks for the tcgen05 prompt kernel whatever the length (tests); by default it
-    // takes the portions that fill its 128-row tiles.
-    if ((impl == 2 || (impl == 0 && (long long)max_q_len * p.G >= 256)) && splits == 1 && max_q_len > 1 &&
+    // impl 2 asks for the tcgen05 prompt kernel whatever the length (tests); by default it takes
+    // the portions whose longest request fills eight of its 256-row blocks per KV head, below
+    // which the mma.sync kernel with its smaller tiles was measured to be as fast or faster.
+    if ((impl == 2 || (impl == 0 && (long long)max_q_len * p.G >= 2048)) && splits == 1 && max_q_len > 1 &&
         prefill_tc05_supported(dtype, D, page_size, q_stride, q, out, kcache, vcache))
         return run_prefill_tc05(d, B, D, max_q_len, stream);
     if (impl == 2) return EMS_ERR_SHAPE;

@@ -273,15 +273,19 @@ def test_prefill_tcgen05_kernel(nh, nkv, d, ps, window):
 @pytest.mark.parametrize("nh,nkv,d,ps,window", [(28, 4, 128, 16, None), (14, 2, 64, 16, 300), (5, 5, 128, 16, None),
                                                 (12, 2, 128, 48, 1000), (3, 1, 64, 2, None)])
 def test_prefill_tcgen05_kernel_long(nh, nkv, d, ps, window):
-    """Long portions (many key tiles, both stages of the K/V ring used many times) on the
-    default dispatch, which sends them to the tcgen05 kernel."""
+    """Long portions (many key tiles, every stage of the K and V rings used many times): the
+    tcgen05 kernel where it takes the page size, against the restatement and the generic kernel;
+    the default dispatch must agree whichever kernel it picks."""
     dtype = torch.bfloat16
     q_lens = [700, 1, 391]
     starts = [0, 900, 1234]
-    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=22, peaky=True)
+    how = dict(tcgen05=True) if ps % 16 == 0 else {}
+    got, want = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=22, peaky=True, **how)
     torch.testing.assert_close(got, want, **tol(dtype))
     got2, _ = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=22, peaky=True, generic=True)
     torch.testing.assert_close(got, got2, **tol(dtype))
+    got3, _ = _attention_case(dtype, nh, nkv, d, ps, q_lens, starts, window, 1, seed=22, peaky=True)
+    torch.testing.assert_close(got3, want, **tol(dtype))
 
 
 def test_prefill_tcgen05_kernel_refuses_other_pages():
@@ -342,6 +346,33 @@ def test_prefill_tensor_core_kernel_equals_generic_kernel():
                             generic=generic)
         outs.append(out.float())
     torch.testing.assert_close(outs[0], outs[1], **tol(dtype))
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_prefill_far_key_stands_out(kernel):
+    """A late query of a long prompt whose score for one far key dominates: at the edges of the
+    128-key tiles, of the stages of the K/V rings and of the pages."""
+    dtype, nh, nkv, d, ps, t = torch.bfloat16, 4, 2, 128, 16, 1500
+    qtok = 1400
+    for far in (0, 127, 128, 255, 256, 1279, 1280, 1399, 1400):
+        g = torch.Generator(device="cuda").manual_seed(far)
+        pages = t // ps + 2
+        perm = torch.randperm(pages, device=dev(), generator=g)[None, :].to(torch.int32)
+        kc = (torch.randn(pages, nkv, ps, d, device=dev(), generator=g) * 0.1).to(dtype)
+        vc = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+        qkv = torch.randn(t, (nh + 2 * nkv) * d, device=dev(), generator=g).to(dtype)
+        page, slot = int(perm[0, far // ps]), far % ps
+        kc[page, 0, slot] = (qkv[qtok, :d].float() * 50.0).to(dtype)  # head 0 of that token points at `far`
+        cu = torch.tensor([0, t], device=dev(), dtype=torch.int32)
+        st = torch.zeros(1, device=dev(), dtype=torch.int32)
+        got = torch.empty(t, nh * d, device=dev(), dtype=dtype)
+        want = torch.empty_like(got)
+        K().paged_attention(qkv, got, kc, vc, perm, cu, st, 1, t, nh, nkv, d, 1 / math.sqrt(d), t, kernel=kernel)
+        ref.paged_attention(qkv, want, kc, vc, perm, cu, st, 1, t, nh, nkv, d, 1 / math.sqrt(d), t,
+                            compute_dtype=torch.float64)
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+        # the row really is that one value vector
+        torch.testing.assert_close(got[qtok, :d].float(), vc[page, 0, slot].float(), **tol(dtype))
 
 
 def test_paged_attention_far_key_stands_out():
