@@ -41,6 +41,11 @@ class EngineConfig:
     enable_chunked_prefill: bool = True
     # Replay pure-decode steps from CUDA graphs (one per batch-size bucket).
     enable_cuda_graphs: bool = True
+    # Launch a step before the tokens of the step before it have been read on the host: the
+    # sampled tokens stay on the device and feed the next step there, and step() returns the
+    # outputs of the step before the one it launched.  Requests whose sampling needs their
+    # token history on the host (a repetition penalty) switch the engine to plain stepping.
+    async_scheduling: bool = True
     seed: int = 0
     extra: dict = field(default_factory=dict)
 

@@ -18,14 +18,18 @@
 namespace ems {
 
 // ---------------------------------------------------------------------------------------
-// embedding: residual[n, :] = float(table[tokens[n], :])
+// embedding: residual[n, :] = float(table[tokens[n], :]).  A negative entry -(k + 1) stands for
+// deferred[k]: a token that an earlier kernel of the stream has sampled and the host has not
+// seen yet (the engine launches a step before it has read the step before it).
 
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                                 float* __restrict__ residual, int H) {
+                                 const int* __restrict__ deferred, float* __restrict__ residual, int H) {
     pdl_prologue();
     const size_t n = blockIdx.x;
-    const T* src = table + (size_t)tokens[n] * H;
+    int tok = tokens[n];
+    if (tok < 0) tok = deferred ? deferred[-(tok + 1)] : 0;
+    const T* src = table + (size_t)tok * H;
     float* dst = residual + n * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
 }
@@ -309,16 +313,16 @@ __global__ void to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst
 
 using namespace ems;
 
-EMS_EXPORT int ems_embedding(const void* table, int dtype, const int* tokens, float* residual,
-                             int N, int H, cudaStream_t stream) {
+EMS_EXPORT int ems_embedding(const void* table, int dtype, const int* tokens, const int* deferred,
+                             float* residual, int N, int H, cudaStream_t stream) {
     if (N <= 0) return EMS_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == EMS_F32)
         return launch_pdl(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float*)table, tokens,
-                          residual, H);
+                          deferred, residual, H);
     if (dtype == EMS_BF16)
         return launch_pdl(embedding_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, tokens,
-                          residual, H);
+                          deferred, residual, H);
     return EMS_ERR_DTYPE;
 }
 

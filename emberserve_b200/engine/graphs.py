@@ -51,6 +51,12 @@ class _Graph:
     turn: int = 0
 
 
+def _forget_cublas_workspaces() -> None:
+    clear = getattr(torch._C, "_cuda_clearCublasWorkspaces", None)
+    if clear is not None:
+        clear()
+
+
 class DecodeGraphs:
     def __init__(self, runner, max_ctx_len: int, max_rows: int) -> None:
         from emberserve_b200.engine.runner import ScratchArena
@@ -115,7 +121,8 @@ class DecodeGraphs:
             tokens=view("tokens", bucket), positions=view("positions", bucket),
             row_of_token=view("row_of", bucket), cu_q=view("cu", bucket + 1), starts=view("starts", bucket),
             q_lens=[1] * bucket, start_list=[0] * bucket, max_q_len=1, max_ctx_len=self.max_ctx_len,
-            scratch=arena, extra={"decode_splits": decode_splits(bucket, kv_heads, self.max_ctx_len)})
+            scratch=arena, extra={"decode_splits": decode_splits(bucket, kv_heads, self.max_ctx_len)},
+            deferred=r.token_feedback)
         bts = [view(f"bt{k}", bucket * self.width).view(bucket, self.width) for k in range(self.npaged)]
         handles = [None if call.cache is None else r.storage.handle(call.cache, call.write, bts, None)
                    for call in r.decoder.spec.order]
@@ -129,8 +136,14 @@ class DecodeGraphs:
         torch.cuda.synchronize(dev)
         graph = torch.cuda.CUDAGraph()
         before = K.launch_count()
+        # cuBLAS keeps one workspace per stream for as long as the process lives.  One that was
+        # allocated inside an earlier capture lies in that graph's memory pool and dangles once
+        # the graph is gone (an engine that was dropped): forget the workspaces, so that this
+        # capture allocates its own into its own pool, and again afterwards.
+        _forget_cublas_workspaces()
         with torch.cuda.graph(graph, pool=self._pool):
             logits = r.decoder.forward(ctx, handles, want, bucket)
+        _forget_cublas_workspaces()
         if self._pool is None:
             self._pool = graph.pool()
         return _Graph(bucket, graph, meta, host, [None, None], offsets, logits, K.launch_count() - before,

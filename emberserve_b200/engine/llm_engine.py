@@ -2,7 +2,18 @@
 
 ``LLMEngine`` owns the model runner (weights, cache, kernels), the scheduler and the
 sampler.  A step: schedule -> build the rows -> ``ModelRunner.step`` -> sample the rows
-whose prompt is complete -> advance, stop-check, finish and free.  Names and meanings
+whose prompt is complete -> advance, stop-check, finish and free.
+
+With ``EngineConfig.async_scheduling`` (the default) the last part trails by one step: a
+call of ``step()`` schedules and launches step n and only then reads the tokens of step
+n - 1, so the host's share of a step (scheduling, packing, bookkeeping) runs while the
+device computes.  The sampled tokens stay on the device (``ModelRunner.token_feedback``)
+and the rows of step n name them by index; on the host a placeholder stands in the
+request's output until the token arrives.  A request that turns out to have ended with the
+token of step n - 1 (an end-of-sequence token) has then already been given a row in step n:
+that row's token is dropped and the pages go back when the end is seen.  The reference has
+no such mode (``emberserve/engine.py:643-706`` reads every step's tokens before it plans
+the next).  Names and meanings
 follow ``emberserve/engine.py``: ``from_pretrained`` (``:383-426``), ``add_request``
 (``:600-619``), ``step`` (``:643-706``), ``abort_request``, ``has_unfinished_requests``,
 ``reset``; ``StepStats`` (``:46-61``) and the per-request metrics (``:1089-1099``).
@@ -12,7 +23,7 @@ from __future__ import annotations
 
 import os
 import time
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -39,6 +50,18 @@ class StepStats:
     num_decode_tokens: int
 
 
+@dataclass
+class _InFlight:
+    """A launched step whose tokens the host has not read yet."""
+
+    requests: list[Request]  # the rows that sample, in order
+    places: list[int]  # where in each request's output its placeholder stands
+    length_stop: list[bool]  # the token ends the request by count, whatever it is
+    host: torch.Tensor | None  # pinned int32 copy of the tokens, valid after `event`
+    event: "torch.cuda.Event | None"
+    tokens: list[int] = field(default_factory=list)  # off the GPU: already on the host
+
+
 class LLMEngine:
     def __init__(self, runner: ModelRunner, config: EngineConfig, tokenizer=None) -> None:
         self.runner = runner
@@ -52,6 +75,10 @@ class LLMEngine:
         self._step_count = 0
         self.keep_stats = False
         self.stats: list[StepStats] = []
+        self._inflight: _InFlight | None = None
+        self._penalties_seen = False
+        self._token_host: list[torch.Tensor | None] = [None, None]
+        self._token_turn = 0
         if config.enable_cuda_graphs:
             runner.enable_graphs(config.max_model_len, config.max_num_seqs)
 
@@ -95,6 +122,8 @@ class LLMEngine:
                       seq_id=self._next_seq_id, metadata=dict(metadata or {}))
         if arrival_time is not None:
             req.arrival_time = arrival_time
+        if req.sampling_params.repetition_penalty != 1.0:
+            self._penalties_seen = True
         self._next_seq_id += 1
         self.scheduler.add_request(req)
         return req
@@ -103,9 +132,12 @@ class LLMEngine:
         self.scheduler.abort_request(request_id)
 
     def has_unfinished_requests(self) -> bool:
+        # (a launched step whose tokens are still to be read belongs to requests that are
+        # running or waiting, unless they were aborted since)
         return self.scheduler.has_unfinished_requests()
 
     def reset(self) -> None:
+        self._inflight = None
         for req in list(self.scheduler.running) + list(self.scheduler.waiting):
             self.scheduler.abort_request(req.request_id)
         self.runner.cache.reset()
@@ -129,9 +161,51 @@ class LLMEngine:
         return logits
 
     def step(self) -> list[RequestOutput]:
+        """One step.  With async scheduling the outputs are those of the step launched by the
+        call before this one; a last call with nothing left to launch returns the rest."""
+        if not self.config.async_scheduling or self._history_needed():
+            outputs = self._finalize(self._take_inflight())
+            return outputs + self._step_sync()
         so = self.scheduler.schedule()
         if so.is_empty:
+            if self._inflight is None:
+                return self._drop_stuck()
+            return self._finalize(self._take_inflight())
+        before = self._take_inflight()
+        self._inflight = self._launch(so)
+        return self._finalize(before)
+
+    def _history_needed(self) -> bool:
+        """Whether some live request samples with its token history (kept on the host)."""
+        if not self._penalties_seen:
+            return False
+        live = list(self.scheduler.running) + list(self.scheduler.waiting)
+        if any(r.sampling_params.repetition_penalty != 1.0 for r in live):
+            return True
+        self._penalties_seen = False
+        return False
+
+    def _take_inflight(self) -> "_InFlight | None":
+        inflight, self._inflight = self._inflight, None
+        return inflight
+
+    def _drop_stuck(self) -> list[RequestOutput]:
+        """Nothing could be scheduled, nothing runs and nothing is on its way, yet a request
+        waits: with the whole cache free it still does not fit (a request that outgrew the pool
+        and preempted itself), so it never will.  It ends with ABORT and what it has produced
+        (the reference's server loop does the same, ``emberserve/server/engine_core.py:246-254``)."""
+        if self.scheduler.running or not self.scheduler.waiting:
             return []
+        req = self.scheduler.waiting[0]
+        self.scheduler.finish_request(req, FinishReason.ABORT)
+        return [RequestOutput(request_id=req.request_id, new_token_ids=[],
+                              output_token_ids=list(req.output_token_ids), finished=True,
+                              finish_reason=FinishReason.ABORT, metrics=self._metrics(req))]
+
+    def _step_sync(self) -> list[RequestOutput]:
+        so = self.scheduler.schedule()
+        if so.is_empty:
+            return self._drop_stuck()
         self._step_count += 1
         t0 = time.perf_counter()
         logits = self.runner.step(self.build_rows(so))
@@ -142,13 +216,90 @@ class LLMEngine:
         for req, qlen in zip(so.scheduled, so.query_lens):
             req.num_computed_tokens += qlen
         outputs = self._postprocess(sampling, tokens)
+        self._record(so, (t1 - t0) * 1e3, (t2 - t1) * 1e3)
+        return outputs
+
+    def _record(self, so: SchedulerOutput, forward_ms: float, sample_ms: float) -> None:
         if self.keep_stats:
             self.stats.append(StepStats(
                 step=self._step_count, is_prefill=so.is_prefill, num_seqs=len(so.scheduled),
                 num_tokens=so.num_tokens, num_preempted=len(so.preempted),
-                forward_ms=(t1 - t0) * 1e3, sample_ms=(t2 - t1) * 1e3,
+                forward_ms=forward_ms, sample_ms=sample_ms,
                 num_free_pages=self.runner.cache.num_free_pages(0) if self.runner.cache.pools else 0,
                 num_prefill_tokens=so.num_prefill_tokens, num_decode_tokens=so.num_decode_tokens))
+
+    def _launch(self, so: SchedulerOutput) -> _InFlight:
+        """Run the step and sample on the device; nothing here waits for the device.  The
+        times in the step's StepStats are therefore those of the launches."""
+        self._step_count += 1
+        t0 = time.perf_counter()
+        logits = self.runner.step(self.build_rows(so))
+        t1 = time.perf_counter()
+        sampling = [r for r, done in zip(so.scheduled, so.prefill_complete) if done]
+        host = event = None
+        tokens: list[int] = []
+        if sampling:
+            n = len(sampling)
+            dev_tokens = self.sampler.sample_tensor(logits, sampling, out=self.runner.token_feedback[:n])
+            if dev_tokens.is_cuda:
+                turn = self._token_turn
+                self._token_turn ^= 1
+                if self._token_host[turn] is None or self._token_host[turn].numel() < n:
+                    self._token_host[turn] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+                host = self._token_host[turn]
+                host[:n].copy_(dev_tokens, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
+            else:
+                tokens = dev_tokens.tolist()
+        t2 = time.perf_counter()
+        for req, qlen in zip(so.scheduled, so.query_lens):
+            req.num_computed_tokens += qlen
+        places, length_stop = [], []
+        for k, req in enumerate(sampling):
+            req.append_output(-(k + 1))  # stands for token_feedback[k] until the token is read
+            places.append(req.num_output_tokens - 1)
+            by_count = (req.num_output_tokens >= req.sampling_params.max_tokens
+                        or req.num_tokens >= self.config.max_model_len)
+            length_stop.append(by_count)
+            req.hold = by_count
+        self._record(so, (t1 - t0) * 1e3, (t2 - t1) * 1e3)
+        return _InFlight(sampling, places, length_stop, host, event, tokens)
+
+    def _finalize(self, inflight: "_InFlight | None") -> list[RequestOutput]:
+        """Read the tokens of a launched step and do what follows from them."""
+        if inflight is None or not inflight.requests:
+            return []
+        if inflight.event is not None:
+            inflight.event.synchronize()
+            tokens = inflight.host[:len(inflight.requests)].tolist()
+        else:
+            tokens = inflight.tokens
+        now = time.perf_counter()
+        outputs = []
+        for req, place, by_count, tok in zip(inflight.requests, inflight.places, inflight.length_stop,
+                                             tokens, strict=True):
+            if req.is_finished:  # aborted, or ended by an earlier token while this one was on its way
+                continue
+            req.output_token_ids[place] = int(tok)
+            if req.first_token_time is None:
+                req.first_token_time = now
+            params = req.sampling_params
+            reason = None
+            if (tok in self.eos_token_ids and not params.ignore_eos) or tok in params.stop_token_ids:
+                reason = FinishReason.STOP
+            elif by_count:
+                reason = FinishReason.LENGTH
+            text = self.tokenizer.decode([int(tok)]) if self.tokenizer is not None else ""
+            if reason is not None:
+                del req.output_token_ids[place + 1:]  # a placeholder of the step launched since
+                req.hold = False
+                self.scheduler.finish_request(req, reason)
+            outputs.append(RequestOutput(
+                request_id=req.request_id, new_token_ids=[int(tok)],
+                output_token_ids=req.output_token_ids[:place + 1], finished=reason is not None,
+                finish_reason=reason, text_delta=text,
+                metrics=self._metrics(req) if reason is not None else {}))
         return outputs
 
     def _postprocess(self, requests: list[Request], tokens: list[int]) -> list[RequestOutput]:

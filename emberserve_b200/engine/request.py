@@ -42,6 +42,9 @@ class Request:
     first_token_time: float | None = None
     finished_time: float | None = None
     metadata: dict = field(default_factory=dict)
+    # Set while the request's last token is still on its way from the device and is known to end
+    # it (max_tokens or the model length): the scheduler gives it no further token.
+    hold: bool = False
 
     @property
     def num_prompt_tokens(self) -> int:

@@ -38,6 +38,8 @@ from emberserve_b200.weights.loader import init_random_on_device, load_weights
 # free memory (``emberserve/engine.py:117-138``: workspace, activations, logits).
 _WORKSPACE_BYTES = 1 << 30
 _MIN_PAGES = 64
+# How many tokens of one step may wait on the device for the step after it.
+MAX_DEFERRED_TOKENS = 8192
 
 
 @dataclass
@@ -123,6 +125,9 @@ class ModelRunner:
                            for _ in range(2)]
         self._meta_events: list[torch.cuda.Event | None] = [None, None]
         self._meta_turn = 0
+        # Tokens sampled on the device, for steps that are launched before the host has read
+        # them: a token id -(k + 1) in a row stands for token_feedback[k].
+        self.token_feedback = torch.zeros(MAX_DEFERRED_TOKENS, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.last_meta_bytes = 0  # bytes of the last step's host-to-device copy
         self.use_graphs = False
@@ -200,7 +205,7 @@ class ModelRunner:
             if end > self.max_positions:
                 raise ValueError(f"request {r.seq_id}: position {end - 1} exceeds "
                                  f"max_position_embeddings={self.max_positions}")
-            if min(r.tokens) < 0 or max(r.tokens) >= self.vocab_size:
+            if min(r.tokens) < -MAX_DEFERRED_TOKENS or max(r.tokens) >= self.vocab_size:
                 raise ValueError(f"request {r.seq_id}: token id out of vocabulary "
                                  f"(vocab_size {self.vocab_size})")
             for w in r.want:
@@ -269,7 +274,8 @@ class ModelRunner:
             num_tokens=n, num_rows=b, dtype=self.dtype, device=self.device,
             tokens=dev(0), positions=dev(1), row_of_token=dev(2), cu_q=dev(3), starts=dev(4),
             q_lens=q_lens, start_list=starts, max_q_len=max(q_lens),
-            max_ctx_len=max(s + q for s, q in zip(starts, q_lens)), scratch=self.scratch)
+            max_ctx_len=max(s + q for s, q in zip(starts, q_lens)), scratch=self.scratch,
+            deferred=self.token_feedback)
         bt = [dev(7 + k).view(b, tables[k].shape[1]) for k in range(npaged)]
         return ctx, bt, dev(6), dev(5), num_want
 

@@ -157,7 +157,7 @@ class Scheduler:
         i = 0
         while i < len(self.running):
             req = self.running[i]
-            if skip_mid_prompt and self._outstanding(req) > 0:
+            if req.hold or (skip_mid_prompt and self._outstanding(req) > 0):
                 i += 1
                 continue
             try:

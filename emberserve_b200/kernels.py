@@ -56,7 +56,7 @@ def library_path() -> str:
 def _declare(lib: ctypes.CDLL) -> None:
     P, I, L, F = c_void_p, c_int, c_longlong, c_float
     sigs = {
-        "ems_embedding": [P, I, P, P, I, I, P],
+        "ems_embedding": [P, I, P, P, P, I, I, P],
         "ems_add_rmsnorm": [P, P, P, I, P, I, P, I, I, F, I, P],
         "ems_silu_mul": [P, P, I, I, I, P],
         "ems_rope_table": [P, P, I, I, P],
@@ -137,11 +137,14 @@ def _stream() -> int:
 # ---------------------------------------------------------------------------------------
 
 
-def embedding(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[n, :] = float32(table[tokens[n], :])"""
+def embedding(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor,
+              deferred: torch.Tensor | None = None) -> None:
+    """residual[n, :] = float32(table[tokens[n], :]); a token -(k + 1) reads deferred[k] (a token
+    sampled on the device by an earlier kernel of the stream)."""
     n, h = residual.shape
     assert table.shape[1] == h and residual.dtype == torch.float32 and tokens.numel() >= n
     _check(library().ems_embedding(_ptr(table, "table"), _dt(table), _i32(tokens, "tokens"),
+                                   None if deferred is None else _i32(deferred, "deferred"),
                                    _ptr(residual, "residual"), n, h, _stream()), "embedding")
 
 

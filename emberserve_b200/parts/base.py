@@ -121,6 +121,10 @@ class StepContext:
     # scratch buffers that live across steps: scratch(name, shape, dtype) -> tensor
     scratch: Callable[..., torch.Tensor] | None = None
     extra: dict[str, Any] = field(default_factory=dict)
+    # int32 device tokens that earlier kernels of the stream have sampled; a token id -(k + 1)
+    # in `tokens` stands for deferred[k] (the engine launches a step before it has read the
+    # tokens of the step before)
+    deferred: torch.Tensor | None = None
 
     @property
     def all_decode(self) -> bool:

@@ -147,7 +147,7 @@ class Decoder:
         s = self.spec
         n = ctx.num_tokens
         residual = ctx.scratch("residual", (n, s.hidden), torch.float32)
-        K.embedding(self.embed, ctx.tokens, residual)
+        K.embedding(self.embed, ctx.tokens, residual, deferred=ctx.deferred)
         if self.embed_position is not None:
             self.embed_position.on_embedding(residual, ctx)
         delta = None

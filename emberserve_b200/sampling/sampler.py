@@ -41,12 +41,16 @@ class Sampler:
     def __init__(self, device: torch.device | str) -> None:
         self.device = torch.device(device)
 
-    def sample_tensor(self, logits: torch.Tensor, requests: list[Request]) -> torch.Tensor:
-        """int32 tokens ``[rows]`` on the device; `logits` may be modified in place."""
+    def sample_tensor(self, logits: torch.Tensor, requests: list[Request],
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+        """int32 tokens ``[rows]`` on the device (in `out` if given); `logits` may be modified
+        in place."""
         r = logits.shape[0]
         assert logits.dim() == 2 and r == len(requests), (tuple(logits.shape), len(requests))
         params = [q.sampling_params for q in requests]
-        out = torch.empty(r, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(r, dtype=torch.int32, device=self.device)
+        assert out.dtype == torch.int32 and out.numel() == r and out.is_contiguous()
         if any(p.repetition_penalty != 1.0 for p in params):
             ptr, flat = [0], []
             for q, p in zip(requests, params):

@@ -15,9 +15,12 @@ import numpy as np
 import torch
 
 
-def embedding(table, tokens, residual):
+def embedding(table, tokens, residual, deferred=None):
     n = residual.shape[0]
-    residual.copy_(table[tokens[:n].long()].float())
+    tok = tokens[:n].long()
+    if deferred is not None and bool((tok < 0).any()):
+        tok = torch.where(tok < 0, deferred.long()[(-(tok + 1)).clamp(min=0)], tok)
+    residual.copy_(table[tok].float())
 
 
 def add_rmsnorm(delta, residual, weight, out, eps, rows=None, num_rows=None):
@@ -118,6 +121,7 @@ def argmax(logits, out):
     out[: logits.shape[0]].copy_(torch.argmax(logits, dim=-1).to(torch.int32))
 
 
+@torch.inference_mode()  # the logits of a step are inference tensors
 def repetition_penalty(logits, row_ptr, token_ids, penalty):
     ptr = row_ptr.tolist()
     for r in range(logits.shape[0]):

@@ -100,6 +100,47 @@ def test_chunked_mixed_and_preempted_generation_on_the_gpu(sharp_dirs):
     assert st.num_free == st.num_pages
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("how", [dict(), dict(max_num_batched_tokens=8), dict(pages=6, max_num_batched_tokens=64)])
+def test_async_scheduling_changes_no_token_on_the_gpu(sharp_dirs, dtype, how):
+    """Steps launched before the tokens of the step before them are read (the sampled tokens
+    feed the next step on the device, decode steps replay CUDA graphs) give the tokens and
+    finish reasons of plain stepping: requests ending by an end-of-sequence token, a stop
+    token, max_tokens and the model length, sampled and greedy, chunked and preempted."""
+    from emberserve_b200 import SamplingParams
+    from emberserve_b200.engine.request import FinishReason
+
+    name = "tiny_b"
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, ALL[name].vocab_size, (n,), generator=g).tolist() for n in (7, 19, 3, 26, 11, 15)]
+    probe = _llm(sharp_dirs[name], name, dtype, async_scheduling=False)
+    free = probe.generate(prompts[:2], SamplingParams.greedy(10, ignore_eos=True))
+    params = [
+        SamplingParams.greedy(10, stop_token_ids=[free[0].output_token_ids[3]], ignore_eos=True),
+        SamplingParams.greedy(10),
+        SamplingParams(max_tokens=9, temperature=0.9, seed=5, ignore_eos=True),
+        SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
+        SamplingParams(max_tokens=14, temperature=0.6, top_k=7, seed=6, ignore_eos=True),
+        SamplingParams(max_tokens=60, temperature=0.0, ignore_eos=True),
+    ]
+    eos = frozenset({free[1].output_token_ids[5]})
+    results = []
+    for async_on in (False, True):
+        llm = _llm(sharp_dirs[name], name, dtype, async_scheduling=async_on, **how)
+        llm.engine.config.max_model_len = 40
+        llm.engine.eos_token_ids = eos
+        llm.engine.keep_stats = True
+        res = llm.generate(prompts, params)
+        results.append([(r.output_token_ids, r.finish_reason) for r in res])
+        st = llm.engine.runner.cache.stats()
+        assert st.num_free == st.num_pages and st.num_sequences == 0
+        assert all(0 <= t < ALL[name].vocab_size for r in res for t in r.output_token_ids)
+        if "pages" in how:
+            assert sum(s.num_preempted for s in llm.engine.stats) >= 1, "the pool was not tight enough"
+    assert results[0] == results[1]
+    assert [r for _, r in results[0]][:2] == [FinishReason.STOP, FinishReason.STOP]
+
+
 def test_command_line_generates_what_the_entry_point_generates(sharp_dirs):
     """`python -m emberserve_b200 generate --prompt-ids ...` prints the tokens that
     LLM.generate() returns, and the throughput line on standard error."""

@@ -108,6 +108,95 @@ def test_stop_ids_eos_length_and_abort(model_dirs):
         eng.add_request("z", "text")
 
 
+def _mixed_workload(name, model_dir):
+    """Requests that end by an end-of-sequence token at different times, by a stop token, by
+    max_tokens and by the model length, with sampling and greedy rows."""
+    cfg, w = plain.read_model_dir(model_dir)
+    prompts = prompts_for(name, [7, 19, 3, 26, 11, 15], seed=9)
+    runs = [plain.greedy_generate(cfg, w, p, 10) for p in prompts[:2]]
+    params = [
+        SamplingParams.greedy(10, stop_token_ids=[runs[0][3]], ignore_eos=True),
+        SamplingParams.greedy(10),  # ends at the end-of-sequence token set below
+        SamplingParams(max_tokens=9, temperature=0.9, seed=5, ignore_eos=True),
+        SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True),
+        SamplingParams(max_tokens=14, temperature=0.6, top_k=7, seed=6, ignore_eos=True),
+        SamplingParams(max_tokens=60, temperature=0.0, ignore_eos=True),  # the model length ends it
+    ]
+    return prompts, params, frozenset({runs[1][5]})
+
+
+@pytest.mark.parametrize("how", [dict(), dict(max_num_batched_tokens=8), dict(pages=7, max_num_batched_tokens=64),
+                                 dict(enable_chunked_prefill=False)])
+def test_async_scheduling_changes_no_token(model_dirs, how):
+    """Launching a step before the tokens of the step before it are read must give the same
+    tokens, finish reasons and an empty cache afterwards, whatever ends the requests."""
+    name = "tiny_b"
+    prompts, params, eos = _mixed_workload(name, model_dirs[name])
+    results = []
+    for async_on in (False, True):
+        llm = make_llm(model_dirs[name], name, async_scheduling=async_on, **how)
+        llm.engine.config.max_model_len = 40
+        llm.engine.eos_token_ids = eos
+        llm.engine.keep_stats = True
+        res = llm.generate(prompts, params)
+        results.append([(r.output_token_ids, r.finish_reason) for r in res])
+        st = llm.engine.runner.cache.stats()
+        assert st.num_free == st.num_pages and st.num_sequences == 0
+        assert all(t >= 0 for r in res for t in r.output_token_ids)
+        if "pages" in how:
+            assert sum(s.num_preempted for s in llm.engine.stats) >= 1, "the pool was not tight enough"
+    assert results[0] == results[1]
+    reasons = [r for _, r in results[0]]
+    assert reasons[:2] == [FinishReason.STOP, FinishReason.STOP] and FinishReason.LENGTH in reasons
+
+
+def test_async_step_returns_the_step_before(model_dirs):
+    name = "tiny_a"
+    llm = make_llm(model_dirs[name], name)
+    eng = llm.engine
+    eng.add_request("a", prompts_for(name, [5])[0], SamplingParams.greedy(3, ignore_eos=True))
+    outs = [eng.step() for _ in range(4)]
+    assert [len(o) for o in outs] == [0, 1, 1, 1]  # the prompt's token arrives with the second call
+    assert outs[3][0].finished and not eng.has_unfinished_requests()
+    assert eng.step() == []
+    # an abort while a token is on its way drops the token
+    eng.add_request("b", prompts_for(name, [5])[0], SamplingParams.greedy(5, ignore_eos=True))
+    eng.step()
+    eng.abort_request("b")
+    assert eng.step() == [] and eng.runner.cache.stats().num_sequences == 0
+
+
+@pytest.mark.parametrize("async_on", [False, True])
+def test_request_that_outgrows_the_pool_is_dropped(model_dirs, async_on):
+    """Three pages of eight tokens: a prompt of 15 fits, its 30 tokens of output do not.  The
+    request preempts itself, can never be admitted again, and ends with ABORT and the tokens it
+    had; a request beside it that fits is served."""
+    name = "tiny_b"
+    prompts = prompts_for(name, [15, 4], seed=6)
+    llm = make_llm(model_dirs[name], name, pages=3, async_scheduling=async_on)
+    res = llm.generate(prompts, [SamplingParams.greedy(30, ignore_eos=True), SamplingParams.greedy(3, ignore_eos=True)])
+    assert res[0].finish_reason == FinishReason.ABORT and 0 < len(res[0].output_token_ids) < 30
+    assert res[1].finish_reason == FinishReason.LENGTH and len(res[1].output_token_ids) == 3
+    st = llm.engine.runner.cache.stats()
+    assert st.num_free == st.num_pages and st.num_sequences == 0
+
+
+def test_repetition_penalty_steps_without_lag(model_dirs):
+    """A request whose sampling reads its token history keeps the engine on plain stepping,
+    and the tokens equal those of an engine with async scheduling off."""
+    name = "tiny_a"
+    prompts = prompts_for(name, [6, 9], seed=4)
+    params = [SamplingParams(max_tokens=8, temperature=0.0, repetition_penalty=1.3, ignore_eos=True),
+              SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)]
+    a = make_llm(model_dirs[name], name, async_scheduling=True)
+    a.engine.add_request("p", prompts[0], params[0])
+    assert len(a.engine.step()) == 1  # no lag: the first call already returns the token
+    a.engine.reset()
+    outs = [[r.output_token_ids for r in make_llm(model_dirs[name], name, async_scheduling=flag).generate(prompts, params)]
+            for flag in (True, False)]
+    assert outs[0] == outs[1]
+
+
 def test_max_model_len_ends_a_request(model_dirs):
     name = "tiny_a"
     llm = make_llm(model_dirs[name], name)

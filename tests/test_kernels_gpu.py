@@ -56,6 +56,15 @@ def test_embedding(dtype, n, h, v):
     K().embedding(table, tokens, got)
     ref.embedding(table, tokens, want)
     assert torch.equal(got, want)
+    # tokens that stand for entries of a device buffer: -(k + 1) reads deferred[k]
+    deferred = torch.randint(0, v, (9,), device=dev(), generator=g).to(torch.int32)
+    mixed = tokens.clone()
+    mixed[::2] = -(torch.arange(mixed[::2].numel(), device=dev(), dtype=torch.int32) % 9 + 1)
+    K().embedding(table, mixed, got, deferred=deferred)
+    ref.embedding(table, mixed, want, deferred=deferred)
+    assert torch.equal(got, want)
+    resolved = torch.where(mixed < 0, deferred[(-(mixed + 1)).clamp(min=0).long()], mixed)
+    assert torch.equal(got, table[resolved[:n].long()].float())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
