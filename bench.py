@@ -229,16 +229,26 @@ def run_ours(args) -> dict:
         for _ in range(warmup):
             engine.step()
         torch.cuda.synchronize()
+        clocks = ClockSampler()
+        clocks.__enter__()
+        time.sleep(0.3)
         t0 = time.perf_counter()
         produced = 0
+        marks = []
         for _ in range(steps):
             produced += len(engine.step())
+            marks.append(time.perf_counter())
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
+        time.sleep(0.2)
+        clocks.__exit__()
+        if os.environ.get("EMBERSERVE_BENCH_TRACE"):
+            print("e2e step ms:", [round((b - a) * 1e3, 2) for a, b in zip([t0] + marks, marks)],
+                  "tail", round((t0 + dt - marks[-1]) * 1e3, 2), file=sys.stderr)
         h2d = runner.last_meta_bytes
         engine.reset()
         return {"value": produced / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt * 1e3 / steps}
+                "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt * 1e3 / steps, "clocks": clocks.summary()}
 
     def kernel_times(fn) -> list:
         """Device time per kernel name over one call of `fn` (torch's profiler)."""
