@@ -597,3 +597,165 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                 assert np.abs(got[(rid, p)] - want[rid][p]).max() <= 3e-5 * np.abs(want[rid]).max()
         runner.cache.check()
         assert runner.cache.stats().free_state_slots == 2
+
+
+# ---- a toy architecture with routed experts, learned positions and a shared cache entry -----------
+
+def test_toy_routing_learned_positions_and_shared_cache_entry(tmp_path):
+    """Three more kinds of part defined HERE, none of them a model of anyone's: a feed-forward
+    that routes every token to 2 of 4 small experts (router logits and their softmax in 32
+    bits), a position encoding that adds a learned vector per position to the embedding
+    (attention then runs without rotary), and an order of layers that names layer 0 twice
+    (its weights at two depths, a cache entry for each) and lets the last call read the keys
+    and values that layer 1 wrote instead of writing its own.  Built from a random model
+    folder and replayed under every cut against a plain float64 restatement."""
+    from emberserve_b200.config.model import ModelConfig
+    from emberserve_b200.engine.replay import TraceReplayer
+    from emberserve_b200.engine.runner import ModelRunner
+    from emberserve_b200.parts.attention import AttentionSpec
+    from emberserve_b200.parts.base import FeedForward, ParamSpec, PositionEncoding, Source, register_part
+    from emberserve_b200.parts.block import PreNormBlockSpec
+    from emberserve_b200.parts.decoder import DecoderSpec, LayerCall
+    from emberserve_b200.parts.mlp import SwiGLUSpec
+    from emberserve_b200.parts.norm import RMSNormSpec
+    from emberserve_b200.registry import register_architecture
+    from emberserve_b200.weights.loader import write_random_model
+
+    @dataclass(frozen=True)
+    class ToyExpertsSpec:
+        hidden: int
+        inter: int
+        experts: int
+        top_k: int
+        name: str
+        kind: str = "toy_top_k_experts"
+
+    @register_part("feed_forward", "toy_top_k_experts")
+    class ToyExperts(FeedForward):
+        def param_specs(self):
+            s = self.spec
+            specs = {"router": ParamSpec((s.experts, s.hidden), [Source(f"{s.name}.router.weight")])}
+            for e in range(s.experts):
+                specs[f"up{e}"] = ParamSpec((s.inter, s.hidden), [Source(f"{s.name}.{e}.up.weight")])
+                specs[f"down{e}"] = ParamSpec((s.hidden, s.inter), [Source(f"{s.name}.{e}.down.weight")])
+            return specs
+
+        def forward(self, x, ctx):
+            s = self.spec
+            logits = x.float() @ self.router.float().t()  # 32-bit, whatever the activations are
+            top, idx = logits.topk(s.top_k, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            y = torch.zeros(x.shape[0], s.hidden, dtype=torch.float32, device=x.device)
+            for e in range(s.experts):
+                weight = (gate * (idx == e)).sum(-1, keepdim=True)  # 0 where the token skips the expert
+                h = torch.nn.functional.gelu(x.float() @ getattr(self, f"up{e}").float().t())
+                y += weight * (h @ getattr(self, f"down{e}").float().t())
+            return y.to(x.dtype)
+
+    @dataclass(frozen=True)
+    class ToyLearnedPositionSpec:
+        hidden: int
+        max_positions: int
+        name: str
+        kind: str = "toy_learned_position"
+
+    @register_part("position", "toy_learned_position")
+    class ToyLearnedPosition(PositionEncoding):
+        def param_specs(self):
+            s = self.spec
+            return {"table": ParamSpec((s.max_positions, s.hidden), [Source(f"{s.name}.weight")])}
+
+        def on_embedding(self, hidden, ctx):
+            hidden += self.table.float()[ctx.positions.long()]
+
+        @property
+        def max_positions(self):
+            return self.spec.max_positions
+
+    @dataclass(frozen=True)
+    class ToyRoutedConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyRoutedForCausalLM"
+        vocab_size: int = 70
+        hidden_size: int = 40
+        expert_size: int = 24
+        num_experts: int = 4
+        experts_per_token: int = 2
+        max_positions: int = 96
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{f.name: cfg[f.name] for f in dataclasses.fields(cls) if f.name in cfg})
+
+        def to_dict(self):
+            return dict(dataclasses.asdict(self), architectures=[self.architecture])
+
+    heads, kv_heads, head_dim = 2, 1, 16
+
+    def build(cfg: ToyRoutedConfig) -> DecoderSpec:
+        def attention(p):
+            return AttentionSpec(cfg.hidden_size, heads, kv_heads, head_dim, False, None, f"{p}.q", f"{p}.k",
+                                 f"{p}.v", f"{p}.o")
+
+        def routed(p):
+            return ToyExpertsSpec(cfg.hidden_size, cfg.expert_size, cfg.num_experts, cfg.experts_per_token, f"{p}.moe")
+
+        layers = []
+        for i, ff in enumerate((routed, lambda p: SwiGLUSpec(cfg.hidden_size, 56, f"{p}.g", f"{p}.u", f"{p}.d"),
+                                routed)):
+            p = f"toy.{i}"
+            layers.append(PreNormBlockSpec(mixer=attention(p), feed_forward=ff(p),
+                                           mixer_norm=RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n1"),
+                                           ffn_norm=RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n2")))
+        order = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(2, 1, write=False)]
+        return DecoderSpec(vocab_size=cfg.vocab_size, hidden=cfg.hidden_size, embed_name="toy.embed",
+                           layers=layers, order=order, final_norm=RMSNormSpec(cfg.hidden_size, 1e-5, "toy.norm"),
+                           head_name="toy.head", max_positions=cfg.max_positions,
+                           embedding_position=ToyLearnedPositionSpec(cfg.hidden_size, cfg.max_positions, "toy.pos"))
+
+    register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig, build)
+    cfg = ToyRoutedConfig()
+    folder = write_random_model(cfg, tmp_path / "toy_routed", seed=8, std=0.2, store_dtype=torch.float32)
+
+    def plain_toy(tokens):
+        from safetensors.torch import load_file
+
+        w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+        t = len(tokens)
+        h = w["toy.embed"][torch.tensor(tokens)] + w["toy.pos.weight"][:t]
+        kept = {}  # cache entry -> (k, v)
+        for layer, entry, write in ((0, 0, True), (1, 1, True), (0, 2, True), (2, 1, False)):
+            p = f"toy.{layer}"
+            x = plain.rms_norm(h, w[f"{p}.n1"], 1e-5)
+            q = (x @ w[f"{p}.q.weight"].T).view(t, heads, head_dim)
+            if write:
+                kept[entry] = ((x @ w[f"{p}.k.weight"].T).view(t, kv_heads, head_dim),
+                               (x @ w[f"{p}.v.weight"].T).view(t, kv_heads, head_dim))
+            k, v = kept[entry]
+            h = h + plain.causal_attention(q, k, v).reshape(t, heads * head_dim) @ w[f"{p}.o.weight"].T
+            y = plain.rms_norm(h, w[f"{p}.n2"], 1e-5)
+            if layer == 1:
+                h = h + (torch.nn.functional.silu(y @ w[f"{p}.g.weight"].T) * (y @ w[f"{p}.u.weight"].T)) @ w[f"{p}.d.weight"].T
+                continue
+            top, idx = (y @ w[f"{p}.moe.router.weight"].T).topk(cfg.experts_per_token, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            out = torch.zeros_like(h)
+            for j in range(t):
+                for slot in range(cfg.experts_per_token):
+                    e = int(idx[j, slot])
+                    hid = torch.nn.functional.gelu(y[j] @ w[f"{p}.moe.{e}.up.weight"].T)
+                    out[j] += gate[j, slot] * (hid @ w[f"{p}.moe.{e}.down.weight"].T)
+            h = h + out
+        return (plain.rms_norm(h, w["toy.norm"], 1e-5) @ w["toy.head"].T).numpy()
+
+    runner = ModelRunner.from_dir(folder, torch.float32, device=DEV, page_size=8, num_pages=40)
+    assert len(runner.decoder.cache_entries()) == 3 and len(runner.decoder.blocks) == 3
+    assert runner.max_positions == cfg.max_positions
+    reqs = rc.make_requests(cfg.vocab_size, [23, 31, 18], seed=4)
+    want = {rid: plain_toy(toks) for rid, toks in reqs}
+    for steps in (rc.whole(reqs), rc.portions(reqs), rc.mixed(reqs, max_live=2, seed=3, decode_tail=6)):
+        rp = TraceReplayer(runner)
+        got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+        for rid, toks in reqs:
+            for p in range(len(toks)):
+                assert np.abs(got[(rid, p)] - want[rid][p]).max() <= 3e-5 * np.abs(want[rid]).max()
+        runner.cache.check()
