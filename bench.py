@@ -345,25 +345,47 @@ def run_kernel(args) -> dict:
         return statistics.median(times)
 
     if args.kernel == "decode_attention":
+        # the attention of one layer of a decode step: rotation of q and k, write of the new key
+        # and value, attention over the cache (and the merge of the key splits), either as the
+        # three kernels of the unfused path or as the one fused kernel (--fused)
         b, ctx = args.batch, args.context
         width = ctx // ps + 1
         pages = b * width
-        kc = torch.randn(pages, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
-        vc = torch.randn(pages, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)
+        nbytes = 2 * b * ctx * nkv * d * 2
+        copies = max(2, int(300e6 // nbytes) + 1)  # used in turn, so that no key is found in L2
+        caches = [(torch.randn(pages, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16),
+                   torch.randn(pages, nkv, ps, d, device=dev, generator=g).to(torch.bfloat16)) for _ in range(copies)]
         bt = torch.randperm(pages, device=dev, generator=g).view(b, width).to(torch.int32)
         qkv = torch.randn(b, (nh + 2 * nkv) * d, device=dev, generator=g).to(torch.bfloat16)
         out = torch.empty(b, nh * d, device=dev, dtype=torch.bfloat16)
         cu = torch.arange(b + 1, device=dev, dtype=torch.int32)
         st = torch.full((b,), ctx - 1, device=dev, dtype=torch.int32)
+        rows = torch.arange(b, device=dev, dtype=torch.int32)
         from emberserve_b200.parts.attention import decode_splits
+        from emberserve_b200.parts.rope import inv_frequencies
 
+        table = K.rope_table(inv_frequencies(d, 1e6).to(dev), ctx + 1)
         splits = args.splits or decode_splits(b, nkv, ctx)
         scratch = torch.empty(max(1, K.attention_scratch_bytes(b, nh, d, splits) // 4), device=dev)
-        ms = timed(lambda: K.paged_attention(qkv, out, kc, vc, bt, cu, st, b, b, nh, nkv, d,
-                                             1 / math.sqrt(d), 1, splits=splits, scratch=scratch))
-        nbytes = 2 * b * ctx * nkv * d * 2
-        return {"kernel": "decode_attention", "batch": b, "context": ctx, "splits": splits, "ms": ms,
-                "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
+        state = {"i": 0}
+
+        def unfused():
+            kc, vc = caches[state["i"] % copies]
+            state["i"] += 1
+            K.rope_kv_write(qkv, nh, nkv, d, st, rows, table, d, kc, vc, bt, ps)
+            K.paged_attention(qkv, out, kc, vc, bt, cu, st, b, b, nh, nkv, d, 1 / math.sqrt(d), 1, splits=splits,
+                              scratch=scratch)
+
+        def fused():
+            kc, vc = caches[state["i"] % copies]
+            state["i"] += 1
+            K.decode_attention_fused(qkv, out, kc, vc, bt, cu, st, b, nh, nkv, d, 1 / math.sqrt(d), table, d, True,
+                                     splits=splits, scratch=scratch)
+
+        ms = timed(fused if args.fused else unfused, reps=copies)
+        return {"kernel": "decode_attention", "fused": bool(args.fused), "batch": b, "context": ctx,
+                "splits": splits, "ms": ms, "gbs": nbytes / ms / 1e6,
+                "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"], "bytes": nbytes}
     if args.kernel == "prefill_attention":
         t, s0 = args.context, args.start  # a portion of t tokens behind s0 cached keys
         width = (s0 + t) // ps + 1
@@ -584,6 +606,8 @@ def main() -> int:
     ap.add_argument("--shape", choices=["qkv", "o", "gate_up", "down", "head"], default="qkv",
                     help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
+    ap.add_argument("--fused", action="store_true",
+                    help="with --kernel decode_attention: the fused kernel instead of the three")
     ap.add_argument("--start", type=int, default=0,
                     help="with --kernel prefill_attention: keys cached before the portion")
     ap.add_argument("--splits", type=int, default=0, help="with --only kernel: key splits (0 = the engine's rule)")

@@ -12,7 +12,15 @@
 // with float32 accumulators; softmax is float32 (base-2 exponentials of scores scaled by
 // log2(e) / sqrt(D)).  At the end the four warps' partial (max, sum, O) are merged in
 // shared memory and written out, or handed to the merge kernel when the keys of a
-// request are split over several blocks.
+// request are split over several blocks.  (Letting the block that finishes last merge the
+// splits was tried and dropped: one block reading every partial costs as much at the end of
+// the kernel as the merge kernel does behind it.)
+//
+// The kernel is launched as a programmatic dependent of the kernel before it: the tiles of keys
+// that earlier steps cached (all but the tile that holds the row's new key) are requested
+// before it waits for that kernel.  In the fused form that kernel is the qkv projection: the
+// block rotates q itself, and the warp that owns the last tile rotates the new key, writes it
+// and the new value into the cache and into its tile.
 //
 // Formulas: emberserve/attn/paged_torch.py:87-98 (decode form of base.py:105-128);
 // the reference's own kernel of this kind is attn/paged_triton.py:100-183 (split-K
@@ -63,7 +71,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D, bool PAGE16>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_mma_kernel(const DecodeParams p) {
-    pdl_prologue();
+    asm volatile("griddepcontrol.launch_dependents;" ::);
     constexpr int CH = D / 8;                  // 16-byte chunks per key row
     constexpr int ROW_BYTES = D * 2;
     constexpr int TILE_BYTES = DEC_TK * ROW_BYTES;           // K (or V) of one 16-key tile
@@ -90,6 +98,9 @@ decode_attention_mma_kernel(const DecodeParams p) {
     unsigned char* ring = smem_raw + warp * WARP_BYTES;
     const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
     const int* table = p.bt + (size_t)b * p.bt_stride;
+    // fused form with a write: the row's own key is not in the cache yet; its row of the last
+    // tile is filled with zeros by the copy and patched once the tile has landed
+    const int new_key = (p.fused && p.write_kv) ? ctx - 1 : -1;
 
     auto issue_tile = [&](int i) {  // stream the warp's i-th tile into stage i % DEC_STAGES
         const int tile = my_first + i * DEC_WARPS;
@@ -106,7 +117,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
             for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
                 const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
                 const int key = key0 + row;
-                const bool valid = key >= k_begin && key < ctx;
+                const bool valid = key >= k_begin && key < ctx && key != new_key;
                 const uint32_t sw = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
                 cp_async16(kdst + sw, valid ? ksrc + it * 256 : p.kc, valid);
                 cp_async16(vdst + sw, valid ? vsrc + it * 256 : p.vc, valid);
@@ -117,7 +128,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
         for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
             const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
             const int key = tile * DEC_TK + row;
-            const bool valid = key >= k_begin && key < ctx;
+            const bool valid = key >= k_begin && key < ctx && key != new_key;
             size_t off = 0;
             if (valid) {
                 const int page = table[key / p.page_size];
@@ -128,6 +139,18 @@ decode_attention_mma_kernel(const DecodeParams p) {
             cp_async16(vdst + sw, p.vc + off, valid);
         }
     };
+
+    // Tiles of keys that were cached by earlier steps do not depend on the kernel before this
+    // one: request them first.  The tile that holds the row's own key (the last one) waits.
+    int issued = 0;
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES; ++s) {
+        if (s < my_count && my_first + s * DEC_WARPS == tile_hi) break;
+        if (s < my_count) issue_tile(s);
+        cp_async_commit();
+        ++issued;
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // query fragments: rows of the m16 tile are the G heads of the group (rows >= G are zero)
     uint32_t qf[KS][4];
@@ -142,6 +165,31 @@ decode_attention_mma_kernel(const DecodeParams p) {
             qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(qrow + r0 * D + col + 8) : 0u;
             qf[ks][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(qrow + r1 * D + col + 8) : 0u;
         }
+        if (p.fused && p.rot == D) {
+            // rotate-half over the whole head: column j < D/2 pairs with j + D/2, which this thread
+            // holds in the fragment KS/2 steps on (emberserve/model/ops.py:66-81); the same
+            // expressions as the rotary kernel of the unfused path
+            const float* cs = p.rope_table + (size_t)(ctx - 1) * (D / 2) * 2;
+#pragma unroll
+            for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = ks * 16 + c + (e >> 1) * 8;  // column of the low element of the pair
+                    const float2 cs0 = *reinterpret_cast<const float2*>(cs + 2 * j);
+                    const float2 cs1 = *reinterpret_cast<const float2*>(cs + 2 * (j + 1));
+                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&qf[ks][e]);
+                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&qf[ks + KS / 2][e]);
+                    const float a0 = __bfloat162float(lo.x), a1 = __bfloat162float(lo.y);
+                    const float b0 = __bfloat162float(hi.x), b1 = __bfloat162float(hi.y);
+                    __nv_bfloat162 nlo, nhi;
+                    nlo.x = __float2bfloat16_rn(a0 * cs0.x - b0 * cs0.y);
+                    nhi.x = __float2bfloat16_rn(b0 * cs0.x + a0 * cs0.y);
+                    nlo.y = __float2bfloat16_rn(a1 * cs1.x - b1 * cs1.y);
+                    nhi.y = __float2bfloat16_rn(b1 * cs1.x + a1 * cs1.y);
+                    qf[ks][e] = *reinterpret_cast<const uint32_t*>(&nlo);
+                    qf[ks + KS / 2][e] = *reinterpret_cast<const uint32_t*>(&nhi);
+                }
+        }
     }
 
     float o[D / 8][4];
@@ -149,8 +197,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
     for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows lane/4 and lane/4 + 8
 
-#pragma unroll
-    for (int s = 0; s < DEC_STAGES; ++s) {
+    for (int s = issued; s < DEC_STAGES; ++s) {
         if (s < my_count) issue_tile(s);
         cp_async_commit();
     }
@@ -161,6 +208,43 @@ decode_attention_mma_kernel(const DecodeParams p) {
         const uint32_t kst = ring_addr + (i % DEC_STAGES) * 2 * TILE_BYTES;
         const uint32_t vst = kst + TILE_BYTES;
         const int key0 = (my_first + i * DEC_WARPS) * DEC_TK;
+        if (new_key >= 0 && my_first + i * DEC_WARPS == tile_hi) {
+            // the row's own key and value: from the qkv row into the cache and into this tile
+            const int row = new_key - key0;
+            const bf16* kraw = p.q + (size_t)tok * p.q_stride + (size_t)(p.nh + hk) * D;
+            const bf16* vraw = kraw + (size_t)p.nkv * D;
+            const int page = table[new_key / p.page_size];
+            const size_t off = (((size_t)page * p.nkv + hk) * p.page_size + new_key % p.page_size) * D;
+            bf16* kdst = const_cast<bf16*>(p.kc) + off;
+            bf16* vdst = const_cast<bf16*>(p.vc) + off;
+            unsigned char* ktile = ring + (i % DEC_STAGES) * 2 * TILE_BYTES;
+            unsigned char* vtile = ktile + TILE_BYTES;
+            auto put = [&](unsigned char* tile, int col, bf16 v) {
+                *reinterpret_cast<bf16*>(tile + row * ROW_BYTES + (((col >> 3) ^ (row & 7)) << 4) + (col & 7) * 2) = v;
+            };
+            if (p.rot == D) {
+                const float* cs = p.rope_table + (size_t)new_key * (D / 2) * 2;
+                for (int j = lane; j < D / 2; j += 32) {
+                    const float c = cs[2 * j], sn = cs[2 * j + 1];
+                    const float x1 = __bfloat162float(kraw[j]), x2 = __bfloat162float(kraw[j + D / 2]);
+                    const bf16 o1 = __float2bfloat16_rn(x1 * c - x2 * sn), o2 = __float2bfloat16_rn(x2 * c + x1 * sn);
+                    kdst[j] = o1;
+                    kdst[j + D / 2] = o2;
+                    put(ktile, j, o1);
+                    put(ktile, j + D / 2, o2);
+                }
+            } else {
+                for (int j = lane; j < D; j += 32) {
+                    kdst[j] = kraw[j];
+                    put(ktile, j, kraw[j]);
+                }
+            }
+            for (int j = lane; j < D; j += 32) {
+                vdst[j] = vraw[j];
+                put(vtile, j, vraw[j]);
+            }
+            __syncwarp();
+        }
 
         float s[2][4];
 #pragma unroll
@@ -290,9 +374,12 @@ template <int D, bool PAGE16>
 int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t stream) {
     constexpr int smem = DEC_WARPS * DEC_STAGES * 2 * DEC_TK * D * 2;
     auto kernel = decode_attention_mma_kernel<D, PAGE16>;
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return EMS_ERR_LAUNCH;
+    static bool raised = false;  // (dynamic + the kernel's few static bytes pass the 48 KB default at D = 64)
+    if (!raised) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return EMS_ERR_LAUNCH;
+        raised = true;
+    }
     if (p.nkv > 65535 || B > 65535) return EMS_ERR_SHAPE;
     const dim3 grid((unsigned)p.splits, (unsigned)p.nkv, (unsigned)B);
     return launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, p);
@@ -304,6 +391,11 @@ bool decode_mma_supported(int dtype, int D, int G, long long q_stride, const voi
     if (dtype != EMS_BF16 || (D != 64 && D != 128) || G > 16) return false;
     if ((q_stride * 2) % 4 || ((uintptr_t)q % 4) || ((uintptr_t)kc % 16) || ((uintptr_t)vc % 16)) return false;
     return true;
+}
+
+bool decode_fused_supported(int D, int G, int rot, long long q_stride, const void* q, const void* kc,
+                            const void* vc) {
+    return decode_mma_supported(EMS_BF16, D, G, q_stride, q, kc, vc) && (rot == 0 || rot == D);
 }
 
 int run_decode_mma(const DecodeParams& p, int B, int D, cudaStream_t stream) {

@@ -19,11 +19,20 @@ struct DecodeParams {
     long long q_stride;
     int bt_stride, page_size, nh, nkv, G, window, splits;
     float scale_log2;   // log2(e) / sqrt(D)
+    // The fused decode form (attention_decode_mma.cu): `q` is the raw qkv row [q | k | v]; the
+    // kernel rotates q (and k) itself with `rope_table` [positions, rot / 2, (cos, sin)] and, with
+    // write_kv, puts the row's new key and value into the cache (and into its own tile of them).
+    const float* rope_table = nullptr;
+    int rot = 0;        // 0 (no rotation) or D
+    int fused = 0;
+    int write_kv = 0;
 };
 
 bool decode_mma_supported(int dtype, int D, int G, long long q_stride, const void* q, const void* kc,
                           const void* vc);
 int run_decode_mma(const DecodeParams& p, int B, int D, cudaStream_t stream);
+bool decode_fused_supported(int D, int G, int rot, long long q_stride, const void* q, const void* kc,
+                            const void* vc);
 
 // The tensor-core kernel for prompt portions and mixed rows (attention_prefill_mma.cu);
 // it uses the same parameter block (no split of the keys: part_o / part_ml unused).

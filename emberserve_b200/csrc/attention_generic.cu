@@ -411,3 +411,37 @@ EMS_EXPORT int ems_paged_attention_static_scratch(
                                page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
                                splits, scratch, (long long)EMS_STATIC_SCRATCH_BYTES, 0, stream);
 }
+
+// Decode attention of a step whose rows all bring one token, fused with what precedes it in the
+// unfused path: `qkv` holds the raw projections [q | k | v] of the rows; the kernel rotates q
+// and k (rot = D, or 0 for none), writes the new key and value into the cache (write_kv) and
+// attends.  With splits > 1, `scratch` holds the partials and the merge kernel follows.  bfloat16, head sizes
+// 64 and 128, at most 16 query heads per KV head; anything else returns EMS_ERR_SHAPE.
+EMS_EXPORT int ems_decode_attention_fused(const void* qkv, long long q_stride, void* out, void* kcache,
+                                          void* vcache, const int* block_tables, int bt_stride, int page_size,
+                                          const int* cu_q, const int* starts, int B, int nh, int nkv, int D,
+                                          int window, float scale, const float* rope_table, int rot, int write_kv,
+                                          int splits, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+    if (B <= 0) return EMS_OK;
+    if (nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 || (rot != 0 && rope_table == nullptr))
+        return EMS_ERR_SHAPE;
+    if (!decode_fused_supported(D, nh / nkv, rot, q_stride, qkv, kcache, vcache)) return EMS_ERR_SHAPE;
+    DecodeParams d;
+    d.q = reinterpret_cast<const bf16*>(qkv); d.out = reinterpret_cast<bf16*>(out);
+    d.kc = reinterpret_cast<const bf16*>(kcache); d.vc = reinterpret_cast<const bf16*>(vcache);
+    d.bt = block_tables; d.cu_q = cu_q; d.starts = starts; d.part_o = nullptr; d.part_ml = nullptr;
+    d.q_stride = q_stride; d.bt_stride = bt_stride; d.page_size = page_size; d.nh = nh; d.nkv = nkv;
+    d.G = nh / nkv; d.window = window; d.splits = splits;
+    d.scale_log2 = scale * 1.4426950408889634f;
+    d.rope_table = rope_table; d.rot = rot; d.fused = 1; d.write_kv = write_kv;
+    if (splits > 1) {
+        const long long need = (long long)B * nh * splits * (D + 2) * (long long)sizeof(float);
+        if (scratch == nullptr || scratch_bytes < need) return EMS_ERR_SCRATCH;
+        d.part_o = reinterpret_cast<float*>(scratch);
+        d.part_ml = d.part_o + (size_t)B * nh * splits * D;
+    }
+    const int rc = run_decode_mma(d, B, D, stream);
+    if (rc != EMS_OK || splits == 1) return rc;
+    return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)B * nh)), dim3(D >= 128 ? 128 : 64), 0,
+                      stream, (const float*)d.part_o, (const float*)d.part_ml, reinterpret_cast<bf16*>(out), splits, D);
+}

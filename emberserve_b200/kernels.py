@@ -62,6 +62,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_table": [P, P, I, I, P],
         "ems_rope_kv_write": [P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, P],
         "ems_to_f32": [P, I, P, L, P],
+        "ems_decode_attention_fused": [P, L, P, P, P, P, I, I, P, P, I, I, I, I, I, F, P, I, I, I, P, L, P],
         "ems_paged_attention": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I, P, L, I, P],
         "ems_argmax": [P, P, I, I, P, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
@@ -246,6 +247,34 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vc
         _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
         _ATTENTION_IMPL["generic" if generic else ("tcgen05" if tcgen05 else kernel)], _stream()),
         "paged_attention", 2 if splits > 1 else 1)
+
+
+def decode_attention_fused_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
+                                     rotary_dim: int) -> bool:
+    """Whether `decode_attention_fused` takes the geometry (the alignment of the tensors is
+    checked by the call itself)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and num_heads // num_kv_heads <= 16
+            and rotary_dim in (0, head_dim))
+
+
+def decode_attention_fused(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                           block_tables: torch.Tensor, cu_q: torch.Tensor, starts: torch.Tensor, num_rows: int,
+                           num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                           rope_table: torch.Tensor | None, rotary_dim: int, write_kv: bool,
+                           window: int | None = None, splits: int = 1, scratch: torch.Tensor | None = None) -> None:
+    """A decode step's attention (every row brings one token) with the rotary encoding of q and
+    k and the write of the new key and value done by the attention kernel itself: `qkv` holds
+    the raw projections [q | k | v].  With `splits` > 1, `scratch` takes the partials and the merge
+    kernel follows."""
+    assert qkv.stride(1) == 1 and out.is_contiguous() and qkv.dtype == out.dtype == kcache.dtype == torch.bfloat16
+    assert rope_table is None or rope_table.dtype == torch.float32
+    _check(library().ems_decode_attention_fused(
+        qkv.data_ptr(), qkv.stride(0), _ptr(out, "out"), _ptr(kcache, "kcache"), _ptr(vcache, "vcache"),
+        _i32(block_tables, "block_tables"), block_tables.shape[1], kcache.shape[2], _i32(cu_q, "cu_q"),
+        _i32(starts, "starts"), num_rows, num_heads, num_kv_heads, head_dim, int(window or 0), float(scale),
+        _ptr(rope_table, "rope_table"), rotary_dim, 1 if write_kv else 0, splits, _ptr(scratch, "scratch"),
+        0 if scratch is None else scratch.numel() * scratch.element_size(), _stream()),
+        "decode_attention_fused", 2 if splits > 1 else 1)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -102,13 +102,28 @@ class GQAttention(Mixer):
             r = self.position.rotary(ctx.device)
             if r is not None:
                 table, rot = r
+        b = ctx.num_rows
+        if (ctx.all_decode and n == b and x.is_cuda
+                and K.decode_attention_fused_supported(ctx.dtype, s.num_heads, s.num_kv_heads, s.head_dim, rot)):
+            # a decode step in bfloat16: rotation, cache write and attention in one kernel
+            out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
+            splits = ctx.extra.get("decode_splits") or decode_splits(b, s.num_kv_heads, ctx.max_ctx_len)
+            scratch = None
+            if splits > 1:
+                nbytes = K.attention_scratch_bytes(b, s.num_heads, s.head_dim, splits)
+                scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)
+            K.decode_attention_fused(qkv, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts, b,
+                                     s.num_heads, s.num_kv_heads, s.head_dim, self.scale, table, rot,
+                                     cache.write, window=cache.window, splits=splits, scratch=scratch)
+            y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
+            linear(out, self.wo, None, y, ctx.scratch)
+            return y
         K.rope_kv_write(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions,
                         ctx.row_of_token, table, rot, cache.k, cache.v, cache.block_tables,
                         cache.page_size, write_kv=cache.write)
         out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
         # Rows that bring one token and stand first (the scheduler puts decoding requests
         # first) go to the split-key decode kernel; the rest, prompt portions, follow.
-        b = ctx.num_rows
         nd = 0
         while nd < b and ctx.q_lens[nd] == 1:
             nd += 1

@@ -384,6 +384,59 @@ def test_prefill_far_key_stands_out(kernel):
         torch.testing.assert_close(got[qtok, :d].float(), vc[page, 0, slot].float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("nh,nkv,d,ps", [(28, 4, 128, 16), (14, 2, 64, 16), (16, 1, 128, 16), (8, 8, 64, 8),
+                                         (7, 1, 128, 4), (6, 3, 64, 32), (12, 4, 128, 1), (4, 2, 64, 48)])
+@pytest.mark.parametrize("splits,window", [(1, None), (5, None), (2, 100), (16, 33), (1, 16)])
+@pytest.mark.parametrize("rotary", [True, False])
+def test_decode_attention_fused_equals_the_three_kernels(nh, nkv, d, ps, splits, window, rotary):
+    """Rotation of q and k, the write of the new key and value and the attention in one kernel
+    against the same done by the rotary kernel and the attention kernel, and against the
+    restatement; then once
+    more without the write, reading what the first call wrote."""
+    from emberserve_b200.parts.rope import inv_frequencies
+
+    dtype = torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(31)
+    starts = [0, 1, 15, 16, 700, 255, 31]
+    b = len(starts)
+    width = max(starts) // ps + 2
+    pages = b * width + 3
+    bt = torch.randperm(pages, device=dev(), generator=g)[: b * width].view(b, width).to(torch.int32)
+    kc0 = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    vc0 = torch.randn(pages, nkv, ps, d, device=dev(), generator=g).to(dtype)
+    qkv0 = (torch.randn(b, (nh + 2 * nkv) * d, device=dev(), generator=g) * 2).to(dtype)
+    rot = d if rotary else 0
+    table = K().rope_table(inv_frequencies(d, 1e4).to(dev()), 1024) if rotary else None
+    cu = torch.arange(b + 1, device=dev(), dtype=torch.int32)
+    st = torch.tensor(starts, device=dev(), dtype=torch.int32)
+    rows = torch.arange(b, device=dev(), dtype=torch.int32)
+    scale = 1 / math.sqrt(d)
+
+    def scratch():
+        return (torch.empty(K().attention_scratch_bytes(b, nh, d, splits) // 4, device=dev()) if splits > 1 else None)
+
+    for write in (True, False):
+        # the three kernels
+        qa, ka, va = qkv0.clone(), kc0.clone(), vc0.clone()
+        K().rope_kv_write(qa, nh, nkv, d, st, rows, table, rot, ka, va, bt, ps, write_kv=write)
+        want = torch.empty(b, nh * d, device=dev(), dtype=dtype)
+        K().paged_attention(qa, want, ka, va, bt, cu, st, b, b, nh, nkv, d, scale, 1, window=window, splits=splits,
+                            scratch=scratch())
+        # the one kernel
+        kb, vb = kc0.clone(), vc0.clone()
+        got = torch.full((b, nh * d), float("nan"), device=dev(), dtype=dtype)
+        K().decode_attention_fused(qkv0, got, kb, vb, bt, cu, st, b, nh, nkv, d, scale, table, rot, write,
+                                   window=window, splits=splits, scratch=scratch())
+        torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+        assert torch.equal(kb, ka) and torch.equal(vb, va)  # the same rounding of the rotated key
+        # the restatement, from the caches the three kernels left
+        plain_out = torch.empty_like(want)
+        ref.paged_attention(qa, plain_out, ka, va, bt, cu, st, b, b, nh, nkv, d, scale, 1, window=window,
+                            compute_dtype=torch.float64)
+        torch.testing.assert_close(got.float(), plain_out.float(), **tol(dtype))
+        kc0, vc0 = ka, va  # the second round reads the keys that the first one wrote
+
+
 def test_paged_attention_far_key_stands_out():
     """One far key among hundreds carries the whole result: its score is made to dominate,
     so a kernel that skipped or misplaced it would be plainly wrong."""
