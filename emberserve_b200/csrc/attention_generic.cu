@@ -224,26 +224,35 @@ paged_attention_kernel(const AttnParams p) {
 // Merge the partial results of the splits: out = sum_s o_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
 // (emberserve/attn/paged_triton.py:185-208).  One block per (token, head); splits are
 // added in index order.
+constexpr int MERGE_MAX_SPLITS = 256;
+
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
                                        int splits, int D) {
     pdl_prologue();
+    __shared__ float weight[MERGE_MAX_SPLITS];
+    __shared__ float red[33];
     const size_t prow = blockIdx.x;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(prow * splits + s) * 2]);
-    float denom = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[(prow * splits + s) * 2];
-        if (ms != -INFINITY) denom += part_ml[(prow * splits + s) * 2 + 1] * expf(ms - M);
+    const float* ml = part_ml + prow * splits * 2;
+    // the splits' maxima and sums are read side by side (a thread per split), the partial
+    // outputs a column per thread with the loads of several splits in flight
+    float m_loc = -INFINITY;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) m_loc = fmaxf(m_loc, ml[s * 2]);
+    const float M = block_max(m_loc, red);
+    float d_loc = 0.f;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float ms = ml[s * 2];
+        const float f = ms == -INFINITY ? 0.f : expf(ms - M);
+        weight[s] = f;
+        d_loc += ml[s * 2 + 1] * f;
     }
-    const float inv = 1.0f / denom;
+    const float inv = 1.0f / block_sum(d_loc, red);  // (block_sum synchronises: the weights are written)
+    const float* po = part_o + prow * splits * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(prow * splits + s) * 2];
-            if (ms != -INFINITY) acc += part_o[(prow * splits + s) * D + d] * expf(ms - M);
-        }
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) acc += po[(size_t)s * D + d] * weight[s];  // in split order
         out[prow * D + d] = from_f32<T>(acc * inv);
     }
 }
@@ -313,7 +322,8 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
     // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel, 2 = the
     // tcgen05 prompt kernel or an error, 3 = the mma.sync kernels where they take the case.
     if (B <= 0 || N <= 0) return EMS_OK;
-    if (D <= 0 || D % 16 || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1)
+    if (D <= 0 || D % 16 || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 ||
+        splits > MERGE_MAX_SPLITS)
         return EMS_ERR_SHAPE;
     const int esize = dtype == EMS_F32 ? 4 : 2;
     if ((q_stride * esize) % 16 || ((uintptr_t)q % 16) || ((uintptr_t)kcache % 16) || ((uintptr_t)vcache % 16))
@@ -423,7 +433,8 @@ EMS_EXPORT int ems_decode_attention_fused(const void* qkv, long long q_stride, v
                                           int window, float scale, const float* rope_table, int rot, int write_kv,
                                           int splits, void* scratch, long long scratch_bytes, cudaStream_t stream) {
     if (B <= 0) return EMS_OK;
-    if (nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 || (rot != 0 && rope_table == nullptr))
+    if (nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 || splits > MERGE_MAX_SPLITS ||
+        (rot != 0 && rope_table == nullptr))
         return EMS_ERR_SHAPE;
     if (!decode_fused_supported(D, nh / nkv, rot, q_stride, qkv, kcache, vcache)) return EMS_ERR_SHAPE;
     DecodeParams d;

@@ -26,8 +26,8 @@ from emberserve_b200.parts.linear import linear
 # Blocks wanted in flight before keys are split among several blocks of a decode step:
 # two per SM of a B200.
 _TARGET_BLOCKS = 2 * 148
-_MAX_SPLITS = 32
-_MIN_KEYS_PER_SPLIT = 256
+_MAX_SPLITS = 64
+_MIN_KEYS_PER_SPLIT = 128
 
 
 @dataclass(frozen=True)
