@@ -495,6 +495,7 @@ def run_serving(args) -> dict:
             "output_tokens": out_tokens, "prompt_tokens": in_tokens, "steps": len(engine.stats),
             "step_ms_p50": fwd[len(fwd) // 2], "step_ms_p99": fwd[int(len(fwd) * 0.99)],
             "ms_per_step_wall": dt * 1e3 / max(1, len(engine.stats)),
+            "host_launch_seconds": sum(fwd) / 1e3,
             "preemptions": sum(s.num_preempted for s in engine.stats), "dtype": "bf16",
             "data": "synthetic: uniform random token ids and lengths (seed 0), random weights",
             "config": {"model": "Qwen2.5-0.5B shape", "layers": cfg.num_hidden_layers, "max_num_seqs": 256,

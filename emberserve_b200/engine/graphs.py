@@ -180,9 +180,7 @@ class DecodeGraphs:
             if n < bucket:
                 bt[n:, 0] = r.scratch_page
         g.meta_dev.copy_(g.host[turn], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        g.events[turn] = ev
+        g.events[turn] = K.record_event()
         g.graph.replay()
         K.add_launches(g.launches)
         r.last_meta_bytes = 4 * g.meta_dev.numel()

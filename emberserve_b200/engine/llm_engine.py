@@ -27,6 +27,7 @@ from dataclasses import dataclass, field
 
 import torch
 
+from emberserve_b200 import kernels as K
 from emberserve_b200.config.engine import EngineConfig
 from emberserve_b200.config.model import ModelConfig
 from emberserve_b200.engine.request import (FinishReason, Request, RequestOutput, check_stop)
@@ -248,8 +249,7 @@ class LLMEngine:
                     self._token_host[turn] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
                 host = self._token_host[turn]
                 host[:n].copy_(dev_tokens, non_blocking=True)
-                event = torch.cuda.Event()
-                event.record()
+                event = K.record_event()
             else:
                 tokens = dev_tokens.tolist()
         t2 = time.perf_counter()

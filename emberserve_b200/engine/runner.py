@@ -25,6 +25,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from emberserve_b200 import kernels as K
 from emberserve_b200.cache.manager import CacheManager, plan_groups
 from emberserve_b200.cache.storage import CacheStorage
 from emberserve_b200.config.model import ModelConfig
@@ -263,9 +264,7 @@ class ModelRunner:
         self._meta_dev[:total].copy_(host[:total], non_blocking=True)
         self.last_meta_bytes = 4 * total
         if self._on_cuda:
-            ev = torch.cuda.Event()
-            ev.record()
-            self._meta_events[turn] = ev
+            self._meta_events[turn] = K.record_event()
 
         def dev(i: int) -> torch.Tensor:
             return self._meta_dev[offsets[i]:offsets[i] + sections[i].size]

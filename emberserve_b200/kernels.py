@@ -135,6 +135,22 @@ def _stream() -> int:
     return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
+_stream_objects: dict[tuple[int, int], "torch.cuda.Stream"] = {}
+
+
+def record_event() -> "torch.cuda.Event":
+    """A new event recorded on the current stream.  The stream object is looked up by its raw
+    handle and kept: ``torch.cuda.current_stream()`` asks the driver for the device count at every
+    call, which is slow and can stall behind other users of the driver."""
+    key = (torch._C._cuda_getDevice(), _stream())
+    stream = _stream_objects.get(key)
+    if stream is None:
+        stream = _stream_objects[key] = torch.cuda.current_stream()
+    event = torch.cuda.Event()
+    event.record(stream)
+    return event
+
+
 # ---------------------------------------------------------------------------------------
 
 
