@@ -40,6 +40,39 @@ def seed_of(request: Request) -> int:
 class Sampler:
     def __init__(self, device: torch.device | str) -> None:
         self.device = torch.device(device)
+        # the per-row parameters of a step travel in one pinned buffer and one copy (two buffers
+        # in turn, each guarded by the event of the copy that last read it)
+        self._host: list[torch.Tensor | None] = [None, None]
+        self._events: list["torch.cuda.Event | None"] = [None, None]
+        self._dev: torch.Tensor | None = None
+        self._turn = 0
+
+    def _upload(self, sections: list[tuple[torch.dtype, list]]) -> list[torch.Tensor]:
+        """Device tensors of the given (dtype, values) lists: one host-to-device copy for all of
+        them on a CUDA device (each section starts on an 8-byte boundary)."""
+        if self.device.type != "cuda":
+            return [torch.tensor(v, dtype=dt, device=self.device) for dt, v in sections]
+        sizes = [torch.empty((), dtype=dt).element_size() * len(v) for dt, v in sections]
+        offsets, total = [], 0
+        for size in sizes:
+            offsets.append(total)
+            total += (size + 7) & ~7
+        turn = self._turn
+        self._turn ^= 1
+        if self._host[turn] is None or self._host[turn].numel() < total:
+            self._host[turn] = torch.empty(max(total, 4096), dtype=torch.uint8, pin_memory=True)
+            self._events[turn] = None
+        if self._dev is None or self._dev.numel() < total:
+            self._dev = torch.empty(max(total, 4096), dtype=torch.uint8, device=self.device)
+        if self._events[turn] is not None:
+            self._events[turn].synchronize()
+        host = self._host[turn]
+        for (dt, values), off, size in zip(sections, offsets, sizes):
+            if size:
+                host[off:off + size].view(dt).copy_(torch.tensor(values, dtype=dt))
+        self._dev[:total].copy_(host[:total], non_blocking=True)
+        self._events[turn] = K.record_event()
+        return [self._dev[off:off + size].view(dt) for (dt, _), off, size in zip(sections, offsets, sizes)]
 
     def sample_tensor(self, logits: torch.Tensor, requests: list[Request],
                       out: torch.Tensor | None = None) -> torch.Tensor:
@@ -51,28 +84,34 @@ class Sampler:
         if out is None:
             out = torch.empty(r, dtype=torch.int32, device=self.device)
         assert out.dtype == torch.int32 and out.numel() == r and out.is_contiguous()
-        if any(p.repetition_penalty != 1.0 for p in params):
+        penalised = any(p.repetition_penalty != 1.0 for p in params)
+        if all(p.is_greedy for p in params) and not penalised:
+            K.argmax(logits, out)
+            return out
+        sections: list[tuple[torch.dtype, list]] = []
+        if penalised:
             ptr, flat = [0], []
             for q, p in zip(requests, params):
                 if p.repetition_penalty != 1.0:
                     flat.extend(sorted(set(q.all_token_ids)))
                 ptr.append(len(flat))
-            K.repetition_penalty(
-                logits, torch.tensor(ptr, dtype=torch.int32, device=self.device),
-                torch.tensor(flat or [0], dtype=torch.int32, device=self.device),
-                torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32,
-                             device=self.device))
-        if all(p.is_greedy for p in params):
+            sections += [(torch.int32, ptr), (torch.int32, flat or [0]),
+                         (torch.float32, [p.repetition_penalty for p in params])]
+        greedy = all(p.is_greedy for p in params)
+        if not greedy:
+            sections += [(torch.float32, [p.temperature for p in params]),
+                         (torch.int32, [p.top_k for p in params]),
+                         (torch.float32, [p.top_p for p in params]),
+                         (torch.int64, [_signed64(seed_of(q)) for q in requests]),
+                         (torch.int64, [q.num_output_tokens for q in requests])]
+        dev = self._upload(sections)
+        if penalised:
+            K.repetition_penalty(logits, dev[0], dev[1], dev[2])
+            dev = dev[3:]
+        if greedy:
             K.argmax(logits, out)
-            return out
-        K.sample(
-            logits,
-            torch.tensor([p.temperature for p in params], dtype=torch.float32, device=self.device),
-            torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device),
-            torch.tensor([p.top_p for p in params], dtype=torch.float32, device=self.device),
-            torch.tensor([_signed64(seed_of(q)) for q in requests], dtype=torch.int64, device=self.device),
-            torch.tensor([q.num_output_tokens for q in requests], dtype=torch.int64, device=self.device),
-            out)
+        else:
+            K.sample(logits, dev[0], dev[1], dev[2], dev[3], dev[4], out)
         return out
 
     def sample(self, logits: torch.Tensor, requests: list[Request]) -> list[int]:
