@@ -469,7 +469,8 @@ def run_serving(args) -> dict:
     n_req = args.requests
     rng = random.Random(0)
     prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(64, 1024))] for _ in range(n_req)]
-    params = [SamplingParams(max_tokens=rng.randint(128, 512), temperature=0.0, ignore_eos=True) for _ in range(n_req)]
+    params = [SamplingParams(max_tokens=rng.randint(128, 512), temperature=args.temperature, top_k=args.top_k,
+                             top_p=args.top_p, seed=i, ignore_eos=True) for i in range(n_req)]
     max_len = 2048
     pages = n_req * (max_len // PAGE_SIZE) + 64
     runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0", page_size=PAGE_SIZE,
@@ -498,6 +499,7 @@ def run_serving(args) -> dict:
             "host_launch_seconds": sum(fwd) / 1e3,
             "preemptions": sum(s.num_preempted for s in engine.stats), "dtype": "bf16",
             "data": "synthetic: uniform random token ids and lengths (seed 0), random weights",
+            "sampling": {"temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p},
             "config": {"model": "Qwen2.5-0.5B shape", "layers": cfg.num_hidden_layers, "max_num_seqs": 256,
                        "max_num_batched_tokens": 2048, "page_size": PAGE_SIZE}, "clocks": clocks.summary()}
 
@@ -607,6 +609,9 @@ def main() -> int:
     ap.add_argument("--shape", choices=["qkv", "o", "gate_up", "down", "head"], default="qkv",
                     help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
+    ap.add_argument("--temperature", type=float, default=0.0, help="with --workload serve-0.5b (0 = greedy)")
+    ap.add_argument("--top-k", type=int, default=-1, help="with --workload serve-0.5b")
+    ap.add_argument("--top-p", type=float, default=1.0, help="with --workload serve-0.5b")
     ap.add_argument("--fused", action="store_true",
                     help="with --kernel decode_attention: the fused kernel instead of the three")
     ap.add_argument("--start", type=int, default=0,

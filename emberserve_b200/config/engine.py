@@ -41,6 +41,10 @@ class EngineConfig:
     enable_chunked_prefill: bool = True
     # Replay pure-decode steps from CUDA graphs (one per batch-size bucket).
     enable_cuda_graphs: bool = True
+    # Capture the graphs of all batch-size buckets when the engine is built (as the reference
+    # does at boot) instead of at the first step that needs each: a capture costs tens of
+    # milliseconds, which a served request would otherwise wait for.
+    eager_graph_capture: bool = True
     # Launch a step before the tokens of the step before it have been read on the host: the
     # sampled tokens stay on the device and feed the next step there, and step() returns the
     # outputs of the step before the one it launched.  Requests whose sampling needs their

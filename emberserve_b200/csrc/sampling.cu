@@ -121,6 +121,26 @@ __global__ void penalty_kernel(float* __restrict__ logits, int V, const int* __r
     }
 }
 
+// hist[bin] += 1 (or mass[bin] += q) for the lanes with `valid`, one atomic per distinct bin of
+// the warp: the scores of a row crowd into a few bins, and a shared-memory atomic per element on
+// the same few words (64-bit ones are compare-and-swap loops) was most of the kernel's time.
+// Every lane of the warp calls these.
+__device__ __forceinline__ void warp_hist_add(unsigned* hist, bool valid, unsigned bin) {
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? bin : 0xffffffffu);
+    if (valid && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[bin], (unsigned)__popc(peers));
+}
+// `qf` is the element's probability in 2^-40 units as a float in [0, 2^40]; what is added is
+// floor(qf), split as a * 2^20 + b so that two 32-bit conversions and two 32-bit warp sums do
+// (a <= 2^20 and b < 2^20, so sums over 32 lanes fit).
+__device__ __forceinline__ void warp_mass_add(unsigned long long* mass, bool valid, unsigned bin, float qf) {
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? bin : 0xffffffffu);
+    const unsigned a = (unsigned)(qf * 9.5367431640625e-07f);          // floor(qf / 2^20)
+    const unsigned b = (unsigned)(qf - (float)a * 1048576.0f);          // exact: both are multiples of qf's ulp
+    const unsigned sa = __reduce_add_sync(peers, a), sb = __reduce_add_sync(peers, b);
+    if (valid && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1))
+        atomicAdd(&mass[bin], ((unsigned long long)sa << 20) + sb);
+}
+
 struct SampleShared {
     float red[33];
     float red_v[33];
@@ -165,9 +185,12 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
             for (int i = tid; i < 256; i += blockDim.x) sh.hist[i] = 0;
             __syncthreads();
             const unsigned prefix = sh.prefix, mask = sh.mask;
-            for (int i = tid; i < V; i += blockDim.x) {
-                const unsigned key = ordered_key(x[i] / temp);
-                if ((key & mask) == prefix) atomicAdd(&sh.hist[(key >> shift) & 255u], 1u);
+            for (int i0 = 0; i0 < V; i0 += blockDim.x) {  // whole warps stay in the loop
+                const int i = i0 + tid;
+                const unsigned key = i < V ? ordered_key(x[i] / temp) : 0u;
+                const bool valid = i < V && (key & mask) == prefix;
+                if (!__any_sync(0xffffffffu, valid)) continue;
+                warp_hist_add(sh.hist, valid, (key >> shift) & 255u);
             }
             __syncthreads();
             if (tid == 0) {
@@ -206,13 +229,13 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
             for (int i = tid; i < 256; i += blockDim.x) sh.mass[i] = 0;
             __syncthreads();
             const unsigned prefix = sh.prefix, mask = sh.mask;
-            for (int i = tid; i < V; i += blockDim.x) {
-                const float zi = x[i] / temp;
+            for (int i0 = 0; i0 < V; i0 += blockDim.x) {
+                const int i = i0 + tid;
+                const float zi = i < V ? x[i] / temp : 0.f;
                 const unsigned key = ordered_key(zi);
-                if (key >= thr_key && (key & mask) == prefix) {
-                    const unsigned long long q = (unsigned long long)(expf(zi - mx) * to_fixed);
-                    atomicAdd(&sh.mass[(key >> shift) & 255u], q);
-                }
+                const bool valid = i < V && key >= thr_key && (key & mask) == prefix;
+                if (!__any_sync(0xffffffffu, valid)) continue;
+                warp_mass_add(sh.mass, valid, (key >> shift) & 255u, valid ? expf(zi - mx) * to_fixed : 0.f);
             }
             __syncthreads();
             if (tid == 0 && sh.crossed) {
@@ -257,23 +280,40 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
         int best = -1;
         for (int w = 0; w < (int)(blockDim.x >> 5); ++w) best = max(best, sh.red_i[w]);
         sh.found = best;
-        // serial prefix over the chunk sums: the same order for every batch
-        const uint4 rnd = philox4x32_10(
-            make_uint2((unsigned)(seeds[r] & 0xffffffffull), (unsigned)(seeds[r] >> 32)),
-            make_uint4((unsigned)(counters[r] & 0xffffffffull), (unsigned)(counters[r] >> 32), 0u, 0u));
-        const float u = (float)(rnd.x >> 8) * (1.0f / 16777216.0f);
-        float total = 0.f;
-        for (int t = 0; t < (int)blockDim.x; ++t) total += sh.chunk[t];
-        const float target = u * total;
-        float run = 0.f;
-        int sel = -1;
-        for (int t = 0; t < (int)blockDim.x; ++t) {
-            if (run + sh.chunk[t] > target) { sel = t; break; }
-            run += sh.chunk[t];
-        }
-        sh.red[0] = target - run;  // what is left to cover inside chunk `sel`
-        sh.red_i[0] = sel;
+        sh.red_i[0] = 0x7fffffff;
     }
+    // prefix sums of the chunk sums, the same tree for every batch: inside each warp by shuffles,
+    // then over the warps' totals
+    const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    float incl = part;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    if (lane == 31) sh.red[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < nwarps ? sh.red[lane] : 0.f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += up;
+        }
+        sh.red_v[lane] = w;  // inclusive totals of the warps
+    }
+    __syncthreads();
+    const float before_warp = warp > 0 ? sh.red_v[warp - 1] : 0.f;
+    incl += before_warp;
+    const float total = sh.red_v[nwarps - 1];
+    const uint4 rnd = philox4x32_10(
+        make_uint2((unsigned)(seeds[r] & 0xffffffffull), (unsigned)(seeds[r] >> 32)),
+        make_uint4((unsigned)(counters[r] & 0xffffffffull), (unsigned)(counters[r] >> 32), 0u, 0u));
+    const float u = (float)(rnd.x >> 8) * (1.0f / 16777216.0f);
+    const float target = u * total;
+    if (incl > target) atomicMin(&sh.red_i[0], tid);  // the first chunk whose prefix passes the target
+    __syncthreads();
+    if (tid == sh.red_i[0]) sh.red[0] = target - (incl - part);  // what is left to cover inside it
     __syncthreads();
     if (tid == sh.red_i[0]) {
         const float want = sh.red[0];
@@ -290,6 +330,282 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     }
     __syncthreads();
     if (tid == 0) out[r] = sh.found;
+}
+
+
+// ---------------------------------------------------------------------------------------
+// The same selection with a row spread over a thread-block cluster of 8 blocks.  One block per
+// row leaves all but a few SMs idle at decode batch sizes and makes a dozen passes over the row
+// from global memory, dividing by the temperature in each.  Here every block keeps its slice of
+// z = x / temperature in shared memory (read and divided once) and the blocks of a row exchange
+// their partial results (maxima, histograms, sums) through distributed shared memory.  All the
+// combinations are in rank order or of integers, so the token drawn is the same as from the
+// one-block kernel up to the order of the 32-bit additions of the draw.
+
+constexpr int SC_CLUSTER = 8;
+constexpr int SC_THREADS = 1024;
+
+__device__ __forceinline__ void sc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned sc_cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned sc_remote(const void* local, unsigned rank) {
+    unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ unsigned sc_ld_u32(const void* local, unsigned rank) {
+    unsigned v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(sc_remote(local, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ float sc_ld_f32(const void* local, unsigned rank) { return __uint_as_float(sc_ld_u32(local, rank)); }
+__device__ __forceinline__ unsigned long long sc_ld_u64(const void* local, unsigned rank) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(sc_remote(local, rank)) : "memory");
+    return v;
+}
+
+struct ClusterShared {
+    float red[33];
+    float red_v[33];
+    int red_i[33];
+    unsigned hist[2][256];             // this block's counts, two buffers used in turn
+    unsigned long long mass[2][256];   // this block's probability mass (2^-40 units)
+    unsigned ghist[256];               // the row's counts / mass, summed over the cluster
+    unsigned long long gmass[256];
+    float pub_f[2][2];                 // values published to the cluster, two slots used in turn
+    int pub_i[2][2];
+    unsigned prefix, mask, remaining;
+    unsigned long long mass_above;
+    int crossed, found, turn;
+};
+
+__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p,
+                      const unsigned long long* __restrict__ seeds,
+                      const unsigned long long* __restrict__ counters, int* __restrict__ out) {
+    __shared__ ClusterShared sh;
+    extern __shared__ float zs[];  // this block's slice of z
+    const int r = blockIdx.y, tid = threadIdx.x;
+    const unsigned rank = sc_cluster_rank();
+    const float* x = logits + (size_t)r * V;
+    const float temp = temperature[r];
+    const int per = (V + SC_CLUSTER - 1) / SC_CLUSTER;
+    const int lo = min(V, (int)rank * per), n = min(V, lo + per) - lo;  // the slice [lo, lo + n)
+    int phase = 0;  // which of the two published slots / histogram buffers is in use
+
+    if (temp == 0.f) {  // greedy row: first maximum of the row
+        const int idx = n > 0 ? block_argmax(x + lo, n, sh.red_v, sh.red_i) : 0;
+        if (tid == 0) { sh.pub_f[0][0] = n > 0 ? x[lo + idx] : -INFINITY; sh.pub_i[0][0] = lo + idx; }
+        sc_cluster_sync();
+        if (rank == 0 && tid == 0) {
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (unsigned c = 0; c < SC_CLUSTER; ++c) {
+                const float v = sc_ld_f32(&sh.pub_f[0][0], c);
+                const int i = (int)sc_ld_u32(&sh.pub_i[0][0], c);
+                if (v > best || (v == best && i < bi) || bi == 0x7fffffff) { best = v; bi = i; }
+            }
+            out[r] = bi;
+        }
+        sc_cluster_sync();  // nobody leaves while rank 0 may still read its shared memory
+        return;
+    }
+
+    // ---- z = x / temp into shared memory, and the row's maximum -----------------------------
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += SC_THREADS) {
+        const float z = x[lo + i] / temp;
+        zs[i] = z;
+        mx = fmaxf(mx, z);
+    }
+    mx = block_max(mx, sh.red);
+    if (tid == 0) sh.pub_f[phase][0] = mx;
+    sc_cluster_sync();
+    mx = -INFINITY;
+    for (unsigned c = 0; c < SC_CLUSTER; ++c) mx = fmaxf(mx, sc_ld_f32(&sh.pub_f[phase][0], c));
+    phase ^= 1;
+
+    // ---- top-k: key of the k-th largest z -----------------------------------------------------
+    unsigned thr_key = 0;  // keep keys >= thr_key
+    const int k = top_k[r];
+    if (k > 0 && k < V) {
+        if (tid == 0) { sh.prefix = 0; sh.mask = 0; sh.remaining = (unsigned)k; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            unsigned* hist = sh.hist[phase];
+            for (int i = tid; i < 256; i += SC_THREADS) hist[i] = 0;
+            __syncthreads();
+            const unsigned prefix = sh.prefix, mask = sh.mask;
+            for (int i0 = 0; i0 < n; i0 += SC_THREADS) {  // whole warps stay in the loop
+                const int i = i0 + tid;
+                const unsigned key = i < n ? ordered_key(zs[i]) : 0u;
+                const bool valid = i < n && (key & mask) == prefix;
+                if (!__any_sync(0xffffffffu, valid)) continue;  // after the first pass few elements match
+                warp_hist_add(hist, valid, (key >> shift) & 255u);
+            }
+            sc_cluster_sync();
+            if (tid < 256) {
+                unsigned total = 0;
+                for (unsigned c = 0; c < SC_CLUSTER; ++c) total += sc_ld_u32(&hist[tid], c);
+                sh.ghist[tid] = total;
+            }
+            __syncthreads();
+            if (tid == 0) {  // every block of the row takes the same decision
+                unsigned running = 0;
+                int bsel = 0;
+                for (int bin = 255; bin >= 0; --bin) {
+                    if (running + sh.ghist[bin] >= sh.remaining) { bsel = bin; break; }
+                    running += sh.ghist[bin];
+                }
+                sh.remaining -= running;
+                sh.prefix = prefix | ((unsigned)bsel << shift);
+                sh.mask = mask | (255u << shift);
+            }
+            __syncthreads();
+            phase ^= 1;
+        }
+        thr_key = sh.prefix;
+    }
+
+    // ---- top-p over what top-k kept -------------------------------------------------------------
+    const int cper = (n + SC_THREADS - 1) / SC_THREADS;       // a thread's contiguous chunk of the slice
+    const int clo = min(n, tid * cper), chi = min(n, clo + cper);
+    const float p = top_p[r];
+    if (p < 1.0f) {
+        float z = 0.f;
+        for (int i = clo; i < chi; ++i)
+            if (ordered_key(zs[i]) >= thr_key) z += expf(zs[i] - mx);
+        z = block_sum(z, sh.red);
+        if (tid == 0) sh.pub_f[phase][0] = z;
+        sc_cluster_sync();
+        float Z = 0.f;
+        for (unsigned c = 0; c < SC_CLUSTER; ++c) Z += sc_ld_f32(&sh.pub_f[phase][0], c);  // rank order
+        phase ^= 1;
+        const float to_fixed = 1099511627776.0f / Z;  // 2^40 / Z
+        const unsigned long long target = (unsigned long long)((double)p * 1099511627776.0);
+        if (tid == 0) { sh.prefix = 0; sh.mask = 0; sh.mass_above = 0; sh.crossed = 1; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            unsigned long long* mass = sh.mass[phase];
+            for (int i = tid; i < 256; i += SC_THREADS) mass[i] = 0;
+            __syncthreads();
+            const unsigned prefix = sh.prefix, mask = sh.mask;
+            for (int i0 = 0; i0 < n; i0 += SC_THREADS) {
+                const int i = i0 + tid;
+                const float zi = i < n ? zs[i] : 0.f;
+                const unsigned key = ordered_key(zi);
+                const bool valid = i < n && key >= thr_key && (key & mask) == prefix;
+                if (!__any_sync(0xffffffffu, valid)) continue;
+                warp_mass_add(mass, valid, (key >> shift) & 255u, valid ? expf(zi - mx) * to_fixed : 0.f);
+            }
+            sc_cluster_sync();
+            if (tid < 256) {
+                unsigned long long total = 0;
+                for (unsigned c = 0; c < SC_CLUSTER; ++c) total += sc_ld_u64(&mass[tid], c);
+                sh.gmass[tid] = total;
+            }
+            __syncthreads();
+            if (tid == 0 && sh.crossed) {
+                unsigned long long running = sh.mass_above;
+                int bsel = -1;
+                for (int bin = 255; bin >= 0; --bin) {
+                    if (sh.gmass[bin] == 0) continue;
+                    if (running + sh.gmass[bin] >= target) { bsel = bin; break; }
+                    running += sh.gmass[bin];
+                }
+                if (bsel < 0) {
+                    sh.crossed = 0;  // rounding left the total below p: keep everything
+                } else {
+                    sh.mass_above = running;
+                    sh.prefix = prefix | ((unsigned)bsel << shift);
+                    sh.mask = mask | (255u << shift);
+                }
+            }
+            __syncthreads();
+            phase ^= 1;
+        }
+        if (sh.crossed) thr_key = max(thr_key, sh.prefix);
+    }
+
+    // ---- draw: first index whose cumulative probability exceeds u ---------------------------------
+    float part = 0.f;
+    int last_kept = -1;
+    for (int i = clo; i < chi; ++i)
+        if (ordered_key(zs[i]) >= thr_key) { part += expf(zs[i] - mx); last_kept = lo + i; }
+    const int lane = tid & 31, warp = tid >> 5;
+    float incl = part;  // prefix sums of the chunk sums, the same tree for every batch
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    int lk = last_kept;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lk = max(lk, __shfl_xor_sync(0xffffffffu, lk, o));
+    if (lane == 31) sh.red[warp] = incl;
+    if (lane == 0) sh.red_i[warp] = lk;
+    __syncthreads();
+    if (warp == 0) {
+        float w = sh.red[lane];
+        int l = sh.red_i[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += up;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l = max(l, __shfl_xor_sync(0xffffffffu, l, o));
+        sh.red_v[lane] = w;  // inclusive totals of the warps
+        if (lane == 0) sh.pub_i[phase][0] = l;  // this block's last kept index
+    }
+    __syncthreads();
+    if (tid == 0) sh.pub_f[phase][0] = sh.red_v[31];  // this block's total
+    incl += warp > 0 ? sh.red_v[warp - 1] : 0.f;
+    sc_cluster_sync();
+    float before = 0.f, total = 0.f;
+    int last_of_row = -1;
+    for (unsigned c = 0; c < SC_CLUSTER; ++c) {  // rank order = index order
+        const float t = sc_ld_f32(&sh.pub_f[phase][0], c);
+        if (c < rank) before += t;
+        total += t;
+        last_of_row = max(last_of_row, (int)sc_ld_u32(&sh.pub_i[phase][0], c));
+    }
+    phase ^= 1;
+    const uint4 rnd = philox4x32_10(
+        make_uint2((unsigned)(seeds[r] & 0xffffffffull), (unsigned)(seeds[r] >> 32)),
+        make_uint4((unsigned)(counters[r] & 0xffffffffull), (unsigned)(counters[r] >> 32), 0u, 0u));
+    const float u = (float)(rnd.x >> 8) * (1.0f / 16777216.0f);
+    const float target = u * total;
+    if (tid == 0) sh.found = 0x7fffffff;
+    __syncthreads();
+    if (before + incl > target) atomicMin(&sh.found, (int)rank * SC_THREADS + tid);  // first chunk past the target
+    __syncthreads();
+    if (tid == 0) sh.pub_i[phase][0] = sh.found;
+    sc_cluster_sync();
+    int first = 0x7fffffff;
+    for (unsigned c = 0; c < SC_CLUSTER; ++c) first = min(first, (int)sc_ld_u32(&sh.pub_i[phase][0], c));
+    if (first == 0x7fffffff) {  // rounding put u * total at or past the total: the last kept token
+        if (rank == 0 && tid == 0) out[r] = last_of_row;
+    } else if (first == (int)rank * SC_THREADS + tid) {
+        const float want = target - (before + incl - part);  // what is left to cover inside this chunk
+        float run = 0.f;
+        int sel = last_kept;
+        for (int i = clo; i < chi; ++i) {
+            if (ordered_key(zs[i]) >= thr_key) {
+                run += expf(zs[i] - mx);
+                if (run > want) { sel = lo + i; break; }
+            }
+        }
+        out[r] = sel;
+    }
+    sc_cluster_sync();  // nobody leaves while a peer may still read its shared memory
 }
 
 }  // namespace ems
@@ -329,6 +645,21 @@ EMS_EXPORT int ems_sample(const float* logits, int R, int V, const float* temper
                           const unsigned long long* counters, int* out, cudaStream_t stream) {
     if (R <= 0) return EMS_OK;
     if (V <= 0) return EMS_ERR_SHAPE;
+    // A large vocabulary is spread over a cluster of blocks per row, each holding its slice of
+    // the row in shared memory; small ones (and slices that would not fit) take one block per row.
+    const size_t slice_bytes = (size_t)((V + SC_CLUSTER - 1) / SC_CLUSTER) * sizeof(float);
+    if (V >= 8192 && slice_bytes <= 160 * 1024 && R <= 65535) {
+        static bool raised = false;
+        if (!raised) {
+            if (cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     160 * 1024) != cudaSuccess)
+                return EMS_ERR_LAUNCH;
+            raised = true;
+        }
+        sample_cluster_kernel<<<dim3(SC_CLUSTER, R), SC_THREADS, slice_bytes, stream>>>(
+            logits, V, temperature, top_k, top_p, seeds, counters, out);
+        return launch_status();
+    }
     sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_k, top_p, seeds,
                                                     counters, out);
     return launch_status();

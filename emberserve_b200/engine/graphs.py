@@ -149,6 +149,17 @@ class DecodeGraphs:
         return _Graph(bucket, graph, meta, host, [None, None], offsets, logits, K.launch_count() - before,
                       keep=(arena, ctx, handles, bts, want))
 
+    def capture_all(self) -> int:
+        """Capture every bucket now (largest first), so that no step of a served request pays for
+        a capture; returns how many graphs were captured (``emberserve/engine.py:322-334`` captures
+        at boot as well)."""
+        done = 0
+        for bucket in sorted(self.buckets, reverse=True):
+            if bucket not in self._graphs:
+                self._graphs[bucket] = self._capture(bucket)
+                done += 1
+        return done
+
     def run(self, rows) -> torch.Tensor:
         r = self.runner
         n = len(rows)

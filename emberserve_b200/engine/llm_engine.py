@@ -82,6 +82,8 @@ class LLMEngine:
         self._token_turn = 0
         if config.enable_cuda_graphs:
             runner.enable_graphs(config.max_model_len, config.max_num_seqs)
+            if config.eager_graph_capture and runner.graphs is not None:
+                runner.graphs.capture_all()
 
     @classmethod
     def from_pretrained(cls, model_dir: str | os.PathLike, engine_config: EngineConfig | None = None,

@@ -498,7 +498,7 @@ def test_repetition_penalty():
     torch.testing.assert_close(logits.cpu(), want)
 
 
-@pytest.mark.parametrize("v", [320, 5000, 152064])
+@pytest.mark.parametrize("v", [320, 5000, 8192, 9001, 40003, 152064])
 def test_sample_matches_restated_draw(v):
     """Temperature, top-k and top-p rows against the restated draw (same Philox uniform,
     same kept set, inverse CDF in index order)."""
