@@ -476,7 +476,8 @@ def run_serving(args) -> dict:
     runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0", page_size=PAGE_SIZE,
                                      num_pages=pages)
     ecfg = EngineConfig(dtype=torch.bfloat16, block_size=PAGE_SIZE, max_model_len=max_len, max_num_seqs=256,
-                        max_num_batched_tokens=2048, enable_chunked_prefill=True)
+                        max_num_batched_tokens=2048, enable_chunked_prefill=True,
+                        async_scheduling=not args.sync_steps)
     engine = LLMEngine.from_runner(runner, ecfg)
     engine.keep_stats = True
     llm = LLM.from_engine(engine)
@@ -609,6 +610,8 @@ def main() -> int:
     ap.add_argument("--shape", choices=["qkv", "o", "gate_up", "down", "head"], default="qkv",
                     help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
+    ap.add_argument("--sync-steps", action="store_true",
+                    help="with --workload serve-0.5b: read every step's tokens before the next is planned")
     ap.add_argument("--temperature", type=float, default=0.0, help="with --workload serve-0.5b (0 = greedy)")
     ap.add_argument("--top-k", type=int, default=-1, help="with --workload serve-0.5b")
     ap.add_argument("--top-p", type=float, default=1.0, help="with --workload serve-0.5b")

@@ -218,3 +218,60 @@ def test_step_logits_all_positions(model_dirs):
     want = plain.forward_logits(cfg, w, prompt, torch.float64)
     assert logits.shape == want.shape
     assert float((logits.double() - want).abs().max()) < 2e-5 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_async_scheduling_under_random_workloads(model_dirs, seed):
+    """Random requests (prompt lengths, token limits, stop tokens, sampled and greedy), random
+    pool sizes and token budgets, requests added while others run and some aborted on the way:
+    async and plain stepping must give every request the same tokens and finish reason, and leave
+    the cache empty."""
+    import random
+
+    name = "tiny_a"
+    rng = random.Random(seed)
+    vocab = ALL[name].vocab_size
+    n_req = rng.randint(2, 7)
+    prompts = [[rng.randrange(vocab) for _ in range(rng.randint(1, 30))] for _ in range(n_req)]
+    params = []
+    for i in range(n_req):
+        stop = [rng.randrange(vocab) for _ in range(rng.randint(0, 6))]
+        params.append(SamplingParams(max_tokens=rng.randint(1, 20), temperature=rng.choice([0.0, 0.0, 0.7, 1.2]),
+                                     top_k=rng.choice([-1, 5]), top_p=rng.choice([1.0, 0.9]), seed=100 + i,
+                                     stop_token_ids=stop, ignore_eos=rng.random() < 0.5))
+    eos = frozenset(rng.randrange(vocab) for _ in range(8))
+    chunked = rng.random() < 0.7
+    how = dict(pages=rng.choice([24, 40, 256]), max_num_batched_tokens=rng.choice([4, 9, 64]) if chunked else 64,
+               enable_chunked_prefill=chunked, max_num_seqs=rng.choice([2, 3, 256]))
+    arrivals = sorted(rng.randint(0, 12) for _ in range(n_req))  # the step at which each request arrives
+    abort_at = {rng.randrange(n_req): rng.randint(1, 15)} if rng.random() < 0.5 else {}
+
+    def run(async_on):
+        llm = make_llm(model_dirs[name], name, async_scheduling=async_on, **how)
+        eng = llm.engine
+        eng.eos_token_ids = eos
+        done, step, added = {}, 0, 0
+        while added < n_req or eng.has_unfinished_requests():
+            while added < n_req and arrivals[added] <= step:
+                eng.add_request(f"r{added}", prompts[added], params[added])
+                added += 1
+            for i, when in abort_at.items():
+                if when == step and i < added:
+                    eng.abort_request(f"r{i}")
+            for out in eng.step():
+                if out.finished:
+                    done[out.request_id] = (out.output_token_ids, out.finish_reason)
+            step += 1
+            assert step < 2000, "the engine does not come to an end"
+        st = eng.runner.cache.stats()
+        assert st.num_free == st.num_pages and st.num_sequences == 0
+        eng.runner.cache.check()
+        return done
+
+    plain_run, async_run = run(False), run(True)
+    aborted = {f"r{i}" for i in abort_at}
+    for rid in plain_run.keys() | async_run.keys():
+        if rid in aborted:
+            continue  # an abort lands a step apart in the two modes; it may or may not come too late
+        assert plain_run.get(rid) == async_run.get(rid), rid
+    assert all(t >= 0 for toks, _ in async_run.values() for t in toks)
