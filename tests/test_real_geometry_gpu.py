@@ -71,3 +71,52 @@ def test_real_layer_sizes_under_every_cut(case, dtype):
                     for rid, toks in reqs for p in range(len(toks)))
         assert worst <= TOL[dtype] * scale, f"{name} {cut} {dtype}: {worst:.3e} vs scale {scale:.3f}"
         runner.cache.check()
+
+
+@pytest.mark.parametrize("name", ["qwen2.5-0.5b", "qwen2.5-7b"])
+def test_long_prompt_through_the_tcgen05_attention(name, tmp_path):
+    """A prompt long enough that its portions go to the tcgen05 attention kernel (at least 2048
+    query rows per KV head): whole in one step, and in portions that start behind a cached prefix
+    at positions that are no multiple of the key tile, beside a short request; bfloat16 against
+    the plain implementation in float32."""
+    from emberserve_b200.engine.replay import TraceReplayer
+    from emberserve_b200.engine.runner import ModelRunner
+    from emberserve_b200.weights.loader import write_random_model
+    from emberserve_b200 import kernels as K
+
+    cfg = config_of(name)
+    folder = write_random_model(cfg, tmp_path / "m", seed=12)
+    g = torch.Generator().manual_seed(5)
+    long_toks = torch.randint(0, cfg.vocab_size, (700,), generator=g).tolist()
+    short_toks = torch.randint(0, cfg.vocab_size, (9,), generator=g).tolist()
+    cfgd, w = plain.read_model_dir(folder)
+    want_long = plain.forward_logits(cfgd, w, long_toks, torch.float32).double().numpy()
+    want_short = plain.forward_logits(cfgd, w, short_toks, torch.float32).double().numpy()
+    scale = float(np.abs(want_long).max())
+    probe = [0, 127, 128, 399, 400, 401, 402, 699]
+    runner = ModelRunner.from_dir(folder, torch.bfloat16, page_size=16, num_pages=64)
+    cuts = {
+        "whole": [[("L", 0, 700, probe)]],
+        "portions": [[("L", 0, 400, [p for p in probe if p < 400])],
+                     [("S", 0, 9, [8]), ("L", 400, 402, [0, 1])],
+                     [("L", 402, 700, [0, 297])]],
+    }
+    for cut, plan in cuts.items():
+        rp = TraceReplayer(runner)
+        for i, step in enumerate(plan):
+            entries = []
+            for rid, a, b, want in step:
+                toks = long_toks if rid == "L" else short_toks
+                entries.append({"id": rid, "tokens": toks[a:b], "want": want})
+            last = i == len(plan) - 1
+            got = rp.run_step({"step": i, "entries": entries, "end": ["L", "S"] if last and cut == "portions" else (["L"] if last else [])})
+            row = 0
+            for rid, a, b, want in step:
+                ref = want_long if rid == "L" else want_short
+                for wpos in want:
+                    err = float(np.abs(got[row] - ref[a + wpos]).max())
+                    assert err <= TOL[torch.bfloat16] * scale, f"{name} {cut} step {i} {rid}@{a + wpos}: {err:.3e}"
+                    row += 1
+        torch.cuda.synchronize()
+        K.check_status()
+        runner.cache.check()
