@@ -411,7 +411,8 @@ EMS_EXPORT int ems_paged_attention_static_scratch(
     if (splits <= 1)
         return ems_paged_attention(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride,
                                    page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
-                                   1, nullptr, 0, 0, stream);
+                                   1, nullptr, 0, /*impl: never the tcgen05 kernel, whose first use
+                                   allocates a status word and tensor maps*/ 3, stream);
     if (N <= 0 || nh <= 0 || D <= 0) return B <= 0 || N <= 0 ? EMS_OK : EMS_ERR_SHAPE;
     const long long need = ems_paged_attention_scratch_bytes(N, nh, D, splits);
     if (need > (long long)EMS_STATIC_SCRATCH_BYTES) return EMS_ERR_SCRATCH;
@@ -419,7 +420,7 @@ EMS_EXPORT int ems_paged_attention_static_scratch(
     if (scratch == nullptr) return EMS_ERR_LAUNCH;
     return ems_paged_attention(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride,
                                page_size, cu_q, starts, B, N, nh, nkv, D, window, scale, max_q_len,
-                               splits, scratch, (long long)EMS_STATIC_SCRATCH_BYTES, 0, stream);
+                               splits, scratch, (long long)EMS_STATIC_SCRATCH_BYTES, 3, stream);
 }
 
 // Decode attention of a step whose rows all bring one token, fused with what precedes it in the
