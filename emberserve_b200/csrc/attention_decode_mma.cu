@@ -374,11 +374,14 @@ template <int D, bool PAGE16>
 int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t stream) {
     constexpr int smem = DEC_WARPS * DEC_STAGES * 2 * DEC_TK * D * 2;
     auto kernel = decode_attention_mma_kernel<D, PAGE16>;
-    static bool raised = false;  // (dynamic + the kernel's few static bytes pass the 48 KB default at D = 64)
-    if (!raised) {
+    // (dynamic + the kernel's few static bytes pass the 48 KB default at D = 64); once per device
+    static int raised_on = -1;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return EMS_ERR_LAUNCH;
+    if (raised_on != device) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return EMS_ERR_LAUNCH;
-        raised = true;
+        raised_on = device;
     }
     if (p.nkv > 65535 || B > 65535) return EMS_ERR_SHAPE;
     const dim3 grid((unsigned)p.splits, (unsigned)p.nkv, (unsigned)B);

@@ -649,12 +649,14 @@ EMS_EXPORT int ems_sample(const float* logits, int R, int V, const float* temper
     // the row in shared memory; small ones (and slices that would not fit) take one block per row.
     const size_t slice_bytes = (size_t)((V + SC_CLUSTER - 1) / SC_CLUSTER) * sizeof(float);
     if (V >= 8192 && slice_bytes <= 160 * 1024 && R <= 65535) {
-        static bool raised = false;
-        if (!raised) {
+        static int raised_on = -1;  // once per device
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return EMS_ERR_LAUNCH;
+        if (raised_on != device) {
             if (cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      160 * 1024) != cudaSuccess)
                 return EMS_ERR_LAUNCH;
-            raised = true;
+            raised_on = device;
         }
         sample_cluster_kernel<<<dim3(SC_CLUSTER, R), SC_THREADS, slice_bytes, stream>>>(
             logits, V, temperature, top_k, top_p, seeds, counters, out);
