@@ -30,7 +30,9 @@ namespace ems {
 
 constexpr int G5_BM = 128;      // output features per block (MMA M)
 constexpr int G5_BK = 64;       // K per stage: 64 bf16 = one 128-byte swizzle span
-constexpr int G5_STAGES = 6;
+// Stages of the ring: as many as let two blocks share an SM (the blocks of the next kernel must
+// be able to move in while this one drains, and two rings in flight feed the memory better).
+template <int NT, bool DUAL> constexpr int g5_stages() { return DUAL ? 5 : (NT <= 16 ? 6 : (NT <= 32 ? 5 : 4)); }
 constexpr int G5_THREADS = 128;
 constexpr uint32_t G5_SPIN_LIMIT = 1u << 18;  // tries of a wait; each try may itself block for microseconds
 
@@ -140,7 +142,7 @@ template <int NT, bool DUAL>
 __global__ void __launch_bounds__(G5_THREADS)
 gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            const Gemm5Params p) {
-    constexpr int STAGES = DUAL ? 5 : G5_STAGES;
+    constexpr int STAGES = g5_stages<NT, DUAL>();
     constexpr uint32_t W_BYTES = G5_BM * G5_BK * 2;               // 16 KB per weight tile
     constexpr uint32_t A_BYTES = (DUAL ? 2 : 1) * W_BYTES;
     constexpr uint32_t B_BYTES = NT * G5_BK * 2;                  // 2..8 KB
@@ -411,7 +413,7 @@ bool tc_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_r
 template <int NT, bool DUAL>
 static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
                         cudaStream_t stream) {
-    constexpr int stages = DUAL ? 5 : G5_STAGES;
+    constexpr int stages = g5_stages<NT, DUAL>();
     constexpr int smem = stages * ((DUAL ? 2 : 1) * G5_BM * G5_BK * 2 + NT * G5_BK * 2) + (2 * stages + 1) * 8 +
                          16 + 1024;
     auto kernel = gemm_smallm_tcgen05_kernel<NT, DUAL>;
