@@ -120,6 +120,34 @@ def load_weights(decoder: Decoder, model_dir: str | os.PathLike, device: str | t
 
 
 # ---------------------------------------------------------------------------------------
+# export: the inverse of the load
+
+
+def export_checkpoint(decoder: Decoder) -> dict[str, torch.Tensor]:
+    """The bound parameters of `decoder` as CPU tensors under their checkpoint names: fused
+    parameters are cut back into the tensors they were assembled from, a tied head is not
+    written twice (``emberserve/model/weights.py:145-161`` is the reference's inverse map)."""
+    params = decoder.parameters()
+    out: dict[str, torch.Tensor] = {}
+    for path, spec in decoder.param_table().items():
+        tensor = params[path]
+        for src in spec.sources:
+            part = tensor if src.rows is None else tensor[src.rows[0]:src.rows[1]]
+            out[src.name] = part.detach().to("cpu").contiguous()
+    return out
+
+
+def save_model(decoder: Decoder, config: ModelConfig, out_dir: str | os.PathLike) -> Path:
+    """Write `decoder`'s weights as a model folder (``config.json``, ``model.safetensors``) that
+    ``load_weights`` reads back bit for bit."""
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    config.save(out)
+    write_safetensors(out / "model.safetensors", export_checkpoint(decoder), metadata={"format": "pt"})
+    return out
+
+
+# ---------------------------------------------------------------------------------------
 # random weights
 
 

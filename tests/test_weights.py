@@ -126,3 +126,23 @@ def test_seed_and_deviation(tmp_path):
     assert abs(float(c["model.embed_tokens.weight"].std()) - 0.5) < 5e-2
     assert abs(float(c["model.layers.0.self_attn.q_proj.bias"].std()) - 0.1) < 3e-2
     assert torch.equal(a["model.layers.2.input_layernorm.weight"], torch.ones(cfg.hidden_size))
+
+
+@pytest.mark.parametrize("name", list(ALL))
+def test_export_is_the_inverse_of_the_load(tmp_path, name):
+    """A loaded model written out again carries the checkpoint's names and bits (the fused
+    projections cut back into q / k / v and gate / up, a tied head written once) and loads
+    back into equal parameters."""
+    from emberserve_b200.weights.loader import export_checkpoint, save_model
+
+    folder = write_random_model(ALL[name], tmp_path / "src", SEEDS[name])
+    original = SafetensorsFile(folder / "model.safetensors")
+    decoder = build_decoder(ALL[name])
+    params = load_weights(decoder, folder, "cpu", torch.bfloat16)
+    exported = export_checkpoint(decoder)
+    assert set(exported) == set(original.tensors)
+    for key, tensor in exported.items():
+        assert torch.equal(tensor, original.get(key)), key
+    copy = save_model(decoder, ALL[name], tmp_path / "copy")
+    again = load_weights(build_decoder(ALL[name]), copy, "cpu", torch.bfloat16)
+    assert set(again) == set(params) and all(torch.equal(again[k], params[k]) for k in params)
