@@ -30,6 +30,7 @@ import torch
 from emberserve_b200 import kernels as K
 from emberserve_b200.config.engine import EngineConfig
 from emberserve_b200.config.model import ModelConfig
+from emberserve_b200.engine.detokenizer import Detokenizer
 from emberserve_b200.engine.request import (FinishReason, Request, RequestOutput, check_stop)
 from emberserve_b200.engine.runner import ModelRunner, StepRow
 from emberserve_b200.engine.scheduler import Scheduler, SchedulerOutput
@@ -69,6 +70,7 @@ class LLMEngine:
         self.config = config
         self.model_config: ModelConfig = runner.config
         self.tokenizer = tokenizer
+        self.detokenizer = Detokenizer(tokenizer)
         self.scheduler = Scheduler(config, runner.cache)
         self.sampler = Sampler(runner.device)
         self.eos_token_ids = frozenset(getattr(self.model_config, "eos_token_ids", ()))
@@ -133,6 +135,7 @@ class LLMEngine:
 
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
+        self.detokenizer.drop(request_id)
 
     def has_unfinished_requests(self) -> bool:
         # (a launched step whose tokens are still to be read belongs to requests that are
@@ -143,6 +146,7 @@ class LLMEngine:
         self._inflight = None
         for req in list(self.scheduler.running) + list(self.scheduler.waiting):
             self.scheduler.abort_request(req.request_id)
+            self.detokenizer.drop(req.request_id)
         self.runner.cache.reset()
         self.stats.clear()
 
@@ -292,11 +296,15 @@ class LLMEngine:
                 reason = FinishReason.STOP
             elif by_count:
                 reason = FinishReason.LENGTH
-            text = self.tokenizer.decode([int(tok)]) if self.tokenizer is not None else ""
+            text, matched = self.detokenizer.feed(req.request_id, req.output_token_ids[:place + 1], params.stop,
+                                                  final=reason is not None)
+            if matched is not None and reason is None:
+                reason = FinishReason.STOP  # the text has reached a stop string
             if reason is not None:
                 del req.output_token_ids[place + 1:]  # a placeholder of the step launched since
                 req.hold = False
                 self.scheduler.finish_request(req, reason)
+                self.detokenizer.drop(req.request_id)
             outputs.append(RequestOutput(
                 request_id=req.request_id, new_token_ids=[int(tok)],
                 output_token_ids=req.output_token_ids[:place + 1], finished=reason is not None,
@@ -314,11 +322,13 @@ class LLMEngine:
             if req.first_token_time is None:
                 req.first_token_time = now
             reason = check_stop(req, int(tok), self.eos_token_ids, self.config.max_model_len)
-            text = ""
-            if self.tokenizer is not None:
-                text = self.tokenizer.decode([int(tok)])
+            text, matched = self.detokenizer.feed(req.request_id, req.output_token_ids, req.sampling_params.stop,
+                                                  final=reason is not None)
+            if matched is not None and reason is None:
+                reason = FinishReason.STOP  # the text has reached a stop string
             if reason is not None:
                 self.scheduler.finish_request(req, reason)
+                self.detokenizer.drop(req.request_id)
             outputs.append(RequestOutput(
                 request_id=req.request_id, new_token_ids=[int(tok)],
                 output_token_ids=list(req.output_token_ids), finished=reason is not None,

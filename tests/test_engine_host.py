@@ -275,3 +275,84 @@ def test_async_scheduling_under_random_workloads(model_dirs, seed):
             continue  # an abort lands a step apart in the two modes; it may or may not come too late
         assert plain_run.get(rid) == async_run.get(rid), rid
     assert all(t >= 0 for toks, _ in async_run.values() for t in toks)
+
+
+class _LetterTokenizer:
+    """Token i is the letter chr(97 + i % 26); tokens 200.. are the two halves of a two-byte
+    character, which decodes to U+FFFD until both halves are there."""
+
+    def encode(self, text):
+        return [ord(c) - 97 for c in text]
+
+    def decode(self, ids):
+        out, i = [], 0
+        while i < len(ids):
+            if ids[i] == 200:
+                if i + 1 < len(ids) and ids[i + 1] == 201:
+                    out.append("é")
+                    i += 2
+                    continue
+                out.append("�")
+            elif ids[i] != 201:
+                out.append(chr(97 + ids[i] % 26))
+            i += 1
+        return "".join(out)
+
+
+def test_detokenizer_pieces_stop_strings_and_incomplete_characters():
+    from emberserve_b200.engine.detokenizer import Detokenizer, held_back
+
+    assert held_back("xxab", ["abc", "bd"]) == 2 and held_back("xxa", ["b"]) == 0 and held_back("xa", ["ab"]) == 1
+    d = Detokenizer(_LetterTokenizer())
+    ids, pieces = [], []
+    for tok in [0, 1, 2, 23, 24, 3, 4]:  # a b c x y d e ; stop at "xyd"
+        ids.append(tok)
+        piece, hit = d.feed("r", list(ids), ["xyd", "zz"])
+        pieces.append(piece)
+        if hit:
+            break
+    assert hit == "xyd" and "".join(pieces) == "abc"       # the stop string is no part of the text
+    assert pieces[3] == "" and pieces[4] == ""             # "x", "xy" were kept back
+    d.drop("r")
+    # no match in the end: what was kept back comes out with the last piece
+    ids, text = [], ""
+    for n, tok in enumerate([0, 23, 24, 0]):               # a x y a
+        ids.append(tok)
+        piece, hit = d.feed("r", list(ids), ["xyd"], final=n == 3)
+        text += piece
+        assert hit is None
+    assert text == "axya"
+    # a character whose second half comes a step later is not handed out in halves
+    d.drop("r")
+    p1, _ = d.feed("r", [0, 200], [])
+    p2, _ = d.feed("r", [0, 200, 201], [])
+    p3, _ = d.feed("r", [0, 200, 201, 1], [])
+    assert (p1, p2, p3) == ("a", "é", "b") or (p1 + p2 + p3 == "aéb" and "�" not in p1 + p2 + p3)
+    assert Detokenizer(None).feed("r", [1, 2], ["x"]) == ("", None)
+
+
+@pytest.mark.parametrize("async_on", [False, True])
+def test_stop_strings_end_a_request(model_dirs, async_on):
+    """With a tokenizer, a request ends when its text reaches one of its stop strings: the text
+    returned ends before the string, the tokens up to the one that completed it are kept, and
+    the reason is STOP; a request beside it without stop strings runs on."""
+    name = "tiny_a"
+    cfg, w = plain.read_model_dir(model_dirs[name])
+    prompts = prompts_for(name, [6, 9], seed=8)
+    free = plain.greedy_generate(cfg, w, prompts[0], 12)
+    tok = _LetterTokenizer()
+    text = tok.decode(free)
+    stop = text[4:6]                                       # the fifth and sixth characters
+    first = text.find(stop)
+    llm = make_llm(model_dirs[name], name, async_scheduling=async_on)
+    llm.engine.tokenizer = tok
+    llm.engine.detokenizer.tokenizer = tok
+    res = llm.generate(prompts, [SamplingParams.greedy(12, stop=[stop, "never"], ignore_eos=True),
+                                 SamplingParams.greedy(12, ignore_eos=True)])
+    assert res[0].finish_reason == FinishReason.STOP
+    assert res[0].text == text[:first]
+    assert res[0].output_token_ids == free[:first + len(stop)]
+    assert res[1].finish_reason == FinishReason.LENGTH and len(res[1].output_token_ids) == 12
+    assert res[1].text == tok.decode(res[1].output_token_ids)
+    st = llm.engine.runner.cache.stats()
+    assert st.num_free == st.num_pages and st.num_sequences == 0
