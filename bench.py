@@ -137,13 +137,17 @@ def run_ours(args) -> dict:
     torch.manual_seed(0)
     max_b = max(64, args.batch)
     pages = max_b * (CONTEXT // PAGE_SIZE + 1) + PREFILL_TOKENS // PAGE_SIZE + 64
-    runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0",
+    dtype = torch.float32 if args.dtype == "float32" else torch.bfloat16
+    runner = ModelRunner.from_random(cfg, seed=0, dtype=dtype, device="cuda:0",
                                      page_size=PAGE_SIZE, num_pages=pages)
     if not args.no_graphs:
         runner.enable_graphs(CONTEXT + 64, max_b)
     for t in runner.storage.tensors:  # keys and values of the "earlier" tokens: random, not zero
         t.normal_(0, 1)
     m = model_bytes_and_flops(cfg, layers)
+    if dtype == torch.float32:  # the true 32-bit path: twice the bytes, CUDA-core kernels
+        m["weight_bytes"] *= 2
+        m["kv_bytes_per_token"] *= 2
     gen = torch.Generator().manual_seed(1)
 
     def rand_tokens(n):
@@ -264,13 +268,13 @@ def run_ours(args) -> dict:
 
     if args.only == "decode":
         d = decode(args.batch, args.steps, args.warmup)
-        out = {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": d["ms"],
+        out = {"only": "decode", "dtype": args.dtype, "batch": args.batch, "layers": layers, "ms_per_step": d["ms"],
                "tok_s": d["tok_s"], "hbm_frac": d["gbs"] / peaks["hbm_gbs"]}
         if args.kernel_times:
             out["kernels"] = kernel_times(lambda: decode(args.batch, args.steps, args.warmup))
         return out
     if args.only == "prefill":
-        out = dict(prefill(max(1, args.steps)), only="prefill", layers=layers)
+        out = dict(prefill(max(1, args.steps)), only="prefill", layers=layers, dtype=args.dtype)
         if args.kernel_times:
             out["kernels"] = kernel_times(lambda: prefill(1))
         return out
@@ -505,6 +509,64 @@ def run_serving(args) -> dict:
                        "max_num_batched_tokens": 2048, "page_size": PAGE_SIZE}, "clocks": clocks.summary()}
 
 
+SHAPE_32B = dict(vocab_size=152064, hidden_size=5120, intermediate_size=27648, num_hidden_layers=64,
+                 num_attention_heads=40, num_key_value_heads=8, head_dim=128, max_position_embeddings=32768,
+                 rms_norm_eps=1e-5, rope_theta=1_000_000.0, tie_word_embeddings=False, attention_bias=True)
+
+
+def run_mixed_32b(args) -> dict:
+    """Chunked prefill of long prompts beside decoding requests at the Qwen2.5-32B shape: 32
+    requests with prompts of 8192 uniform-random tokens and 32 output tokens each, a token budget
+    of 2048 per step, through LLM.generate(); bfloat16, random weights (65.5 GB) and 69 GB of keys
+    and values.  Wall clock around the whole call; the steps that only decode are timed apart."""
+    import random
+
+    import torch
+
+    from emberserve_b200 import kernels as K
+    from emberserve_b200.config.engine import EngineConfig
+    from emberserve_b200.config.model import Qwen2Config
+    from emberserve_b200.engine.llm_engine import LLMEngine
+    from emberserve_b200.engine.runner import ModelRunner
+    from emberserve_b200.llm import LLM
+    from emberserve_b200.sampling.params import SamplingParams
+
+    cfg = Qwen2Config.from_dict(dict(SHAPE_32B, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    K.library()
+    n_req, prompt_len, out_len = args.requests if args.requests != 256 else 32, 8192, 32
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(prompt_len)] for _ in range(n_req)]
+    params = SamplingParams(max_tokens=out_len, temperature=0.0, ignore_eos=True)
+    max_len = prompt_len + out_len + 16
+    pages = n_req * (max_len // PAGE_SIZE + 1) + 64
+    runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0", page_size=PAGE_SIZE,
+                                     num_pages=pages)
+    ecfg = EngineConfig(dtype=torch.bfloat16, block_size=PAGE_SIZE, max_model_len=max_len, max_num_seqs=n_req,
+                        max_num_batched_tokens=2048, enable_chunked_prefill=True)
+    engine = LLMEngine.from_runner(runner, ecfg)
+    engine.keep_stats = True
+    llm = LLM.from_engine(engine)
+    llm.generate([prompts[0][:300]], [SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True)])  # warm-up
+    engine.stats.clear()
+    torch.cuda.synchronize()
+    with ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        results = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    out_tokens = sum(len(r.output_token_ids) for r in results)
+    mixed = [s for s in engine.stats if s.num_prefill_tokens and s.num_decode_tokens]
+    return {"metric": "chunked prefill beside decode, 32 requests of 8192 prompt tokens (Qwen2.5-32B shape)",
+            "value": (n_req * prompt_len + out_tokens) / dt, "unit": "tok/s (prompt + output)", "n_gpus": 1,
+            "seconds": dt, "requests": n_req, "prompt_tokens": n_req * prompt_len, "output_tokens": out_tokens,
+            "steps": len(engine.stats), "mixed_steps": len(mixed),
+            "ms_per_step_wall": dt * 1e3 / max(1, len(engine.stats)), "dtype": "bf16",
+            "data": "synthetic: uniform random token ids (seed 0), random weights",
+            "config": {"model": "Qwen2.5-32B shape", "layers": cfg.num_hidden_layers, "max_num_seqs": n_req,
+                       "max_num_batched_tokens": 2048, "page_size": PAGE_SIZE, "prompt_len": prompt_len,
+                       "output_len": out_len}, "clocks": clocks.summary()}
+
+
 def run_reference(args) -> dict:
     """The unmodified reference, installed under baseline/_ref, through its own LLMEngine."""
     ref = ROOT / "baseline" / "_ref"
@@ -598,8 +660,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b"], default="decode-7b",
-                    help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests")
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b"], default="decode-7b",
+                    help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests; "
+                         "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
     ap.add_argument("--only", choices=["decode", "prefill", "kernel"], default=None,
@@ -610,6 +673,9 @@ def main() -> int:
     ap.add_argument("--shape", choices=["qkv", "o", "gate_up", "down", "head"], default="qkv",
                     help="with --kernel gemm: which projection of the 7B shape")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only kernel: keys (or prompt tokens)")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="with --only decode / prefill: float32 times the true 32-bit path (the line's "
+                         "prefill fraction stays relative to the bfloat16 peak)")
     ap.add_argument("--sync-steps", action="store_true",
                     help="with --workload serve-0.5b: read every step's tokens before the next is planned")
     ap.add_argument("--temperature", type=float, default=0.0, help="with --workload serve-0.5b (0 = greedy)")
@@ -637,6 +703,9 @@ def main() -> int:
         return 0
     if args.workload == "serve-0.5b":
         print(json.dumps(run_serving(args)))
+        return 0
+    if args.workload == "mixed-32b":
+        print(json.dumps(run_mixed_32b(args)))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
