@@ -153,9 +153,9 @@ def run_ours(args) -> dict:
     def rand_tokens(n):
         return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
 
-    def decode(batch: int, steps: int, warmup: int, sample_clocks: bool = False) -> dict:
-        """Device time of exactly `steps` decode steps at `batch`, contexts ending at CONTEXT."""
-        start_ctx = CONTEXT - (steps + warmup)
+    def decode(batch: int, steps: int, warmup: int, sample_clocks: bool = False, context: int = CONTEXT) -> dict:
+        """Device time of exactly `steps` decode steps at `batch`, contexts ending at `context`."""
+        start_ctx = context - (steps + warmup)
         seqs = list(range(1000, 1000 + batch))
         for s in seqs:
             runner.cache.admit(s, start_ctx)
@@ -191,21 +191,25 @@ def run_ours(args) -> dict:
         ms = ev0.elapsed_time(ev1) / steps
         for s in seqs:
             runner.cache.release(s)
-        mean_ctx = start_ctx + warmup + (steps + 1) / 2
+        mean_ctx = start_ctx + warmup + (steps + 1) / 2  # (of the timed steps)
         nbytes = m["weight_bytes"] + batch * mean_ctx * m["kv_bytes_per_token"]
         return {"ms": ms, "tok_s": batch * 1e3 / ms, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
                 "launches": K.launch_count() - launches0,
                 "clocks": clocks.summary() if clocks else None}
 
-    def prefill(iters: int = 3) -> dict:
+    def prefill(iters: int = 3, portions: int = 1) -> dict:
+        """One prompt of PREFILL_TOKENS tokens, in one step or in `portions` equal steps."""
         times = []
+        part = PREFILL_TOKENS // portions
         for it in range(iters + 1):
             runner.cache.admit(5000 + it, PREFILL_TOKENS)
-            rows = [StepRow(5000 + it, rand_tokens(PREFILL_TOKENS), 0, [PREFILL_TOKENS - 1])]
+            toks = rand_tokens(PREFILL_TOKENS)
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             ev0.record()
-            runner.step(rows)
+            for j in range(portions):
+                last = j == portions - 1
+                runner.step([StepRow(5000 + it, toks[j * part:(j + 1) * part], j * part, [part - 1] if last else [])])
             ev1.record()
             torch.cuda.synchronize()
             runner.cache.release(5000 + it)
@@ -282,6 +286,8 @@ def run_ours(args) -> dict:
     pre = prefill()
     b1 = decode(1, min(args.steps, 32), 3)
     b64 = decode(64, min(args.steps, 32), 3)
+    half = decode(args.batch, min(args.steps, 32), 3, context=CONTEXT // 2)
+    pre4 = prefill(2, portions=4)
     e2e = end_to_end(args.batch, args.steps, args.warmup)
     return {
         "metric": "decode tok/s at batch 8, context 4096 (Qwen2.5-7B shape)",
@@ -302,6 +308,7 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": main["gbs"] / peaks["hbm_gbs"]},
         "points": {"decode_b1": b1["tok_s"], "decode_b64": b64["tok_s"],
+                   f"decode_b{args.batch}_ctx{CONTEXT // 2}": half["tok_s"], "prefill_4x512": pre4["value"],
                    "decode_b1_hbm_frac": b1["gbs"] / peaks["hbm_gbs"],
                    "decode_b64_hbm_frac": b64["gbs"] / peaks["hbm_gbs"]},
         "reference_a100_fp16_b8_tok_s": A100_FP16_B8_TOK_S,
