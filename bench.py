@@ -424,6 +424,31 @@ def run_kernel(args) -> dict:
         ws = [(torch.randn(n_out, k, device=dev, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
         out = torch.empty(m, n_out, device=dev, dtype=torch.bfloat16)
+        if m > 64:  # prompt portions: the two-SM kernel against cuBLAS (and its activation kernel)
+            act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
+            bias = None
+            st = {"i": 0}
+
+            def ours_large():
+                if args.shape == "gate_up":
+                    K.gemm_large_gated(x, ws[st["i"] % copies], act)
+                else:
+                    K.gemm_large(x, ws[st["i"] % copies], bias, out)
+                st["i"] += 1
+
+            def lib_large():
+                torch.mm(x, ws[st["i"] % copies].t(), out=out)
+                if args.shape == "gate_up":
+                    K.silu_mul(out, act)
+                st["i"] += 1
+
+            ms = timed(ours_large, reps=copies)
+            ms_lib = timed(lib_large, reps=copies)
+            K.check_status()
+            flops = 2.0 * m * n_out * k
+            return {"kernel": "gemm", "shape": args.shape, "m": m, "n": n_out, "k": k, "ms": ms,
+                    "tflops": flops / ms / 1e9, "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"],
+                    "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9}
         from emberserve_b200.parts.linear import smallm_ksplit
 
         ksplit = args.splits or smallm_ksplit(m, n_out, k)

@@ -25,6 +25,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace ems {
 
@@ -34,7 +35,6 @@ constexpr int G5_BK = 64;       // K per stage: 64 bf16 = one 128-byte swizzle s
 // be able to move in while this one drains, and two rings in flight feed the memory better).
 template <int NT, bool DUAL> constexpr int g5_stages() { return DUAL ? 5 : (NT <= 16 ? 6 : (NT <= 32 ? 5 : 4)); }
 constexpr int G5_THREADS = 128;
-constexpr uint32_t G5_SPIN_LIMIT = 1u << 18;  // tries of a wait; each try may itself block for microseconds
 
 struct Gemm5Params {
     float* partial;      // [ksplit, M_tok, N_out] float32 (ksplit > 1) or unused
@@ -45,91 +45,6 @@ struct Gemm5Params {
     int cluster_reduce;  // 1: the ksplit blocks of a row tile are a cluster and reduce on chip
     int dual_offset;     // DUAL kernels: row distance between the two weight tiles
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false (and a code in *status) if the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    for (uint32_t i = 0; i < G5_SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    volatile int* word = status;  // host-mapped memory: a plain store, the first code wins
-    if (*word == 0) *word = code;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// Programmatic dependent launch: this kernel may be started while the kernel before it in the
-// stream is still running; everything that reads that kernel's output comes after this wait
-// (which returns once the earlier kernel has completed and its writes are visible).
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 16 consecutive float32 columns of this thread's accumulator lane
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
-// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), version 1, layout type 2.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    const uint64_t lo = (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16);
-    const uint64_t hi = (uint64_t)(1024 >> 4) | ((uint64_t)1 << 14) | ((uint64_t)2 << 29);
-    return lo | (hi << 32);
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// float at shared-memory address `addr` of the block with rank `rank` in this cluster
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
 
 // NT: token columns of the MMA (16, 32 or 64).
 // DUAL: the block owns TWO weight tiles, rows [tile*128, +128) and the same rows `dual_offset`
@@ -214,24 +129,29 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int it = max(0, armed - STAGES); it < armed; ++it)
                 mbar_wait(full0 + 8 * (it % STAGES), (uint32_t)(it / STAGES) & 1u, p.status, 4);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----------------------------------------------------------------
+    } else if (warp == 1) {
+        // ---- MMA issue: the warp runs the loop, one elected lane issues (a lone diverged lane
+        // leaves the tensor pipe idle for a while after every commit) -----------------------
+        const bool issuer = elect_one();
         for (int it = 0; it < nk && ok; ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-            ok = mbar_wait(full0 + 8 * s, ph, p.status, 2);
+            ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph, p.status, 2));
             if (!ok) break;
             tc_fence_after();
             const uint64_t da = smem_desc_sw128(a_s + s * A_BYTES), db = smem_desc_sw128(b_s + s * B_BYTES);
+            if (issuer) {
 #pragma unroll
-            for (int k = 0; k < G5_BK / 16; ++k) {  // 16 K per MMA = 32 bytes = 2 descriptor units
-                const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-                tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, acc);
-                if (DUAL) tc_mma_bf16(tmem_d + NT, da + (W_BYTES >> 4) + 2 * k, db + 2 * k, IDESC, acc);
+                for (int k = 0; k < G5_BK / 16; ++k) {  // 16 K per MMA = 32 bytes = 2 descriptor units
+                    const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                    tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, acc);
+                    if (DUAL) tc_mma_bf16(tmem_d + NT, da + (W_BYTES >> 4) + 2 * k, db + 2 * k, IDESC, acc);
+                }
+                tc_commit(empty0 + 8 * s);  // arrives once these MMAs have read the stage
             }
-            tc_commit(empty0 + 8 * s);  // arrives once these MMAs have read the stage
+            __syncwarp();
         }
-        tc_commit(done_bar);            // arrives once every MMA issued above has completed
+        if (issuer) tc_commit(done_bar);    // arrives once every MMA issued above has completed
     }
     __syncwarp();
 

@@ -69,11 +69,15 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
         "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, L, P],
         "ems_gemm_smallm_gated": [P, P, P, I, I, I, P],
+        "ems_gemm_large_gated": [P, P, P, I, I, I, P],
+        "ems_gemm_large": [P, P, P, P, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int
+    lib.ems_gemm_large_gated_supported.argtypes = [I, I, I]
+    lib.ems_gemm_large_gated_supported.restype = c_int
     lib.ems_gemm_smallm_status.argtypes = []
     lib.ems_gemm_smallm_status.restype = c_int
     lib.ems_gemm_smallm_scratch_bytes.argtypes = [I, I, I]
@@ -360,13 +364,41 @@ def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) 
                                            _stream()), "gemm_smallm_gated")
 
 
+def gemm_large_gated_supported(m: int, inter: int, k: int) -> bool:
+    """Whether gemm_large_gated takes these sizes (bfloat16 tensors)."""
+    return bool(library().ems_gemm_large_gated_supported(m, inter, k))
+
+
+def gemm_large_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, i] = silu(x . weight[i]) * (x . weight[I + i]) for weight [2 I, K] and any number
+    of rows m: the two-SM tcgen05 kernel of prompt steps (256 x 256 tiles, persistent grid), with
+    the activation in its epilogue.  I a multiple of 128, K a multiple of 8."""
+    m, k = x.shape
+    inter = out.shape[1]
+    assert weight.shape == (2 * inter, k) and out.shape[0] == m
+    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    _check(library().ems_gemm_large_gated(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(out, "out"), m, inter, k,
+                                          _stream()), "gemm_large_gated")
+
+
+def gemm_large(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[m, n] = x . weight[n] (+ bias[n]) on the same two-SM tcgen05 kernel; n and K multiples of 8."""
+    m, k = x.shape
+    n = weight.shape[0]
+    assert weight.shape == (n, k) and out.shape == (m, n)
+    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
+    _check(library().ems_gemm_large(_ptr(x, "x"), _ptr(weight, "weight"), None if bias is None else _ptr(bias, "bias"),
+                                    _ptr(out, "out"), m, n, k, _stream()), "gemm_large")
+
+
 def gemm_smallm_status() -> int:
     """0, or the code of the first bounded wait that ran out in the tcgen05 kernel (after a
-    synchronisation point): 1 producer, 2 MMA issuer, 3 epilogue, 4 drain."""
+    synchronisation point): 1 producer, 2 MMA issuer, 3 epilogue, 4 drain of the small-row kernel;
+    11 producer, 12 and 13 MMA issuer, 14 epilogue of the two-SM kernel."""
     return int(library().ems_gemm_smallm_status())
 
 
 def check_status() -> None:
     code = gemm_smallm_status()
     if code != 0:
-        raise KernelError(f"a wait inside the tcgen05 GEMM kernel ran out (code {code}); its results are invalid")
+        raise KernelError(f"a wait inside a tcgen05 GEMM kernel ran out (code {code}); its results are invalid")

@@ -45,7 +45,7 @@ class SwiGLU(FeedForward):
         s: SwiGLUSpec = self.spec
         n = x.shape[0]
         act = ctx.scratch("ffn_act", (n, s.intermediate), ctx.dtype)
-        if not gated_linear(x, self.wgu, act):  # few rows: both projections and SiLU in one kernel
+        if not gated_linear(x, self.wgu, act):  # both projections and SiLU in one kernel, where one takes the sizes
             gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
             linear(x, self.wgu, None, gu, ctx.scratch)
             K.silu_mul(gu, act)

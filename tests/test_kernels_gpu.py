@@ -602,6 +602,75 @@ def test_gemm_smallm_cluster_split(m, n, k, ksplit):
     assert torch.equal(out, again)  # fixed order of additions
 
 
+@pytest.mark.parametrize("m,inter,k", [(300, 256, 128), (2048, 1152, 896), (513, 4864, 896), (65, 128, 72),
+                                       (1000, 2560, 3584), (256, 128, 64), (129, 384, 200)])
+def test_gemm_large_gated(m, inter, k):
+    """The two-SM kernel of prompt steps (256 x 256 tiles over a pair of blocks, two accumulators
+    in tensor memory, silu(gate) * up in the epilogue), against the float32 computation of the
+    same bfloat16 inputs: rows that end inside a tile and inside the peer's half, K that ends
+    inside a stage, more tiles than SM pairs (both accumulators and every stage used again)."""
+    g = torch.Generator(device="cuda").manual_seed(m * 31 + inter)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    out = torch.full((m + 3, inter), float("nan"), dtype=torch.bfloat16, device=dev())
+    assert K().gemm_large_gated_supported(m, inter, k)
+    K().gemm_large_gated(x, w, out[:m])
+    torch.cuda.synchronize()
+    K().check_status()
+    y = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    assert float((out[:m].float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
+    assert bool(torch.isnan(out[m:].float()).all())  # nothing is written past the last row
+    again = torch.empty_like(out[:m])
+    K().gemm_large_gated(x, w, again)
+    assert torch.equal(out[:m], again)
+
+
+def test_gemm_large_gated_one_row_stands_out():
+    """Each output comes from its own token row and its own weight rows: one (token, feature)
+    pair is made large and must land at exactly that place."""
+    m, inter, k = 700, 640, 256
+    x = torch.zeros(m, k, dtype=torch.bfloat16, device=dev())
+    w = torch.zeros(2 * inter, k, dtype=torch.bfloat16, device=dev())
+    for tok, feat in ((0, 0), (127, 127), (128, 128), (255, 639), (256, 1), (699, 300), (511, 512)):
+        x[tok, tok % k] = 2.0
+        w[feat, tok % k] += 3.0          # gate = 6
+        w[inter + feat, tok % k] += 0.5  # up = 1
+    out = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+    K().gemm_large_gated(x, w, out)
+    torch.cuda.synchronize()
+    K().check_status()
+    y = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    assert int((want != 0).sum()) >= 7
+    assert torch.allclose(out.float(), want, rtol=1e-2, atol=1e-6)
+
+
+def test_gemm_large_gated_refuses():
+    assert not K().gemm_large_gated_supported(512, 200, 128)   # I not a multiple of 128
+    assert not K().gemm_large_gated_supported(512, 256, 100)   # K not a multiple of 8
+    x = torch.zeros(512, 128, dtype=torch.bfloat16, device=dev())
+    w = torch.zeros(400, 128, dtype=torch.bfloat16, device=dev())
+    with pytest.raises(Exception):
+        K().gemm_large_gated(x, w, torch.empty(512, 200, dtype=torch.bfloat16, device=dev()))
+
+
+@pytest.mark.parametrize("m,n,k,bias", [(300, 256, 128, True), (2048, 4608, 896, True), (513, 896, 4864, False),
+                                        (65, 136, 72, True), (1000, 3584, 3584, False), (257, 1000, 200, True)])
+def test_gemm_large_plain(m, n, k, bias):
+    g = torch.Generator(device="cuda").manual_seed(m * 31 + n)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16) if bias else None
+    out = torch.full((m + 3, n), float("nan"), dtype=torch.bfloat16, device=dev())
+    K().gemm_large(x, w, b, out[:m])
+    torch.cuda.synchronize()
+    K().check_status()
+    want = x.float() @ w.float().t() + (b.float() if bias else 0.0)
+    assert float((out[:m].float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
+    assert bool(torch.isnan(out[m:].float()).all())
+
+
 @pytest.mark.parametrize("m,inter,k", [(1, 256, 128), (8, 18944, 3584), (16, 1000, 3584), (17, 4864, 896),
                                        (33, 640, 1024), (64, 2048, 512), (5, 130, 72)])
 def test_gemm_smallm_gated(m, inter, k):
