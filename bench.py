@@ -452,7 +452,7 @@ def run_kernel(args) -> dict:
         from emberserve_b200.parts.linear import smallm_ksplit
 
         ksplit = args.splits or smallm_ksplit(m, n_out, k)
-        on_chip = ksplit in (1, 2, 4, 8)  # the blocks of a split reduce as a cluster
+        on_chip = ksplit <= 8  # the blocks of a split reduce as a cluster, as in the engine
         scratch = None if on_chip else torch.empty(K.gemm_smallm_scratch_bytes(m, n_out, ksplit) // 4, device=dev)
         act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
         state = {"i": 0}

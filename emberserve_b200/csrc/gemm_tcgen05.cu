@@ -185,7 +185,7 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
     } else if (p.cluster_reduce) {
         // every block of the cluster leaves its accumulator in its own shared memory (the
-        // stage ring is idle now); the block whose rank is row % ksplit adds the row up
+        // stage ring is idle now); each block then adds up its share of the rows
         // layout red[column][row]: neighbouring threads write neighbouring words
         float* red = reinterpret_cast<float*>(base_ptr);
 #pragma unroll
@@ -197,21 +197,41 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
         cluster_sync_all();
         const int me = (int)cluster_rank();
-        const int owned = (G5_BM + p.ksplit - 1) / p.ksplit;  // this block adds rows me, me + ksplit, ...
+        // this block adds rows [me * owned, +owned), four neighbouring rows to a thread
+        const int owned = (((G5_BM + p.ksplit - 1) / p.ksplit) + 3) & ~3;
+        const int quads = owned >> 2;
         bf16* y = reinterpret_cast<bf16*>(p.y);
-        for (int idx = threadIdx.x; idx < owned * p.m_tok; idx += G5_THREADS) {
-            const int n = idx / owned, rl = (idx % owned) * p.ksplit + me;
+        for (int idx = threadIdx.x; idx < quads * p.m_tok; idx += G5_THREADS) {
+            const int n = idx / quads, rl = me * owned + (idx % quads) * 4;
             const int orow = tile * G5_BM + rl;
             if (rl >= G5_BM || orow >= p.n_out) continue;
             const uint32_t addr = a_s + (uint32_t)(n * G5_BM + rl) * 4u;
-            float part[8];
+            float4 part[8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) part[r] = r < p.ksplit ? ld_cluster_f32(addr, (uint32_t)r) : 0.f;
-            float acc = 0.f;
+            for (int r = 0; r < 8; ++r)
+                part[r] = r < p.ksplit ? ld_cluster_f32x4(addr, (uint32_t)r) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int r = 0; r < 8; ++r) acc += part[r];  // rank order, the same for every batch
-            if (p.bias) acc += __bfloat162float(p.bias[orow]);
-            y[(size_t)n * p.n_out + orow] = __float2bfloat16_rn(acc);
+            for (int r = 0; r < 8; ++r) {  // rank order, the same for every batch
+                acc[0] += part[r].x; acc[1] += part[r].y; acc[2] += part[r].z; acc[3] += part[r].w;
+            }
+            bf16* dst = y + (size_t)n * p.n_out + orow;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (orow + e < p.n_out) {
+                    const float b = p.bias ? __bfloat162float(p.bias[orow + e]) : 0.f;
+                    acc[e] += b;
+                }
+            if (orow + 3 < p.n_out && ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0)) {
+                uint2 o;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
+                o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = o;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (orow + e < p.n_out) dst[e] = __float2bfloat16_rn(acc[e]);
+            }
         }
         cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     } else if (have) {

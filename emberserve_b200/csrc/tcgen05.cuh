@@ -84,6 +84,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return lo | (hi << 32);
 }
 
+// four floats at shared-memory address `addr` (16-byte aligned) of the block with rank `rank`
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 // true in exactly one lane of a converged warp
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
