@@ -713,6 +713,9 @@ def main() -> int:
     ap.add_argument("--temperature", type=float, default=0.0, help="with --workload serve-0.5b (0 = greedy)")
     ap.add_argument("--top-k", type=int, default=-1, help="with --workload serve-0.5b")
     ap.add_argument("--top-p", type=float, default=1.0, help="with --workload serve-0.5b")
+    ap.add_argument("--library-prefill-mlp", action="store_true",
+                    help="for comparison: gate/up product of prompt steps by cuBLAS and a separate SiLU "
+                         "kernel instead of the two-SM tcgen05 kernel with SiLU in its epilogue")
     ap.add_argument("--fused", action="store_true",
                     help="with --kernel decode_attention: the fused kernel instead of the three")
     ap.add_argument("--start", type=int, default=0,
@@ -725,6 +728,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the shape has (the line then names both numbers)")
     args = ap.parse_args()
+    if args.library_prefill_mlp:
+        from emberserve_b200 import kernels as _K
+
+        _K.gemm_large_gated_supported = lambda m, inter, k: False
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py measures a one-GPU engine; --gpus {args.gpus} is not supported (N=1 only)")
         return 2

@@ -9,7 +9,7 @@
 // the loop and an elected lane issues: with a lone diverged lane every tcgen05.commit cost
 // the tensor pipe about 130 idle cycles, 583 k cycles a call against 500 k); the accumulator
 // (128 lanes x 256 float32 columns per block) lives in tensor memory twice, so that the
-// four epilogue warps of each block drain tile t while the MMAs of tile t+1 run.  The grid
+// eight epilogue warps of each block drain tile t while the MMAs of tile t+1 run.  The grid
 // is persistent: one cluster per SM pair walks the tiles in an order that keeps the tiles
 // in flight on few weight rows (they are read from memory once and from L2 after that).
 //
@@ -34,12 +34,12 @@ constexpr int GL_BM = 128;        // token rows per block (256 per pair)
 constexpr int GL_BN = 128;        // weight rows staged per block and K step (256 per pair)
 constexpr int GL_BK = 64;         // K per stage: one 128-byte swizzle span of bf16
 constexpr int GL_STAGES = 6;
-constexpr int GL_THREADS = 192;   // warp 0 TMA, warp 1 MMA and tensor memory, warps 2..5 epilogue
+constexpr int GL_THREADS = 320;   // warp 0 TMA, warp 1 MMA and tensor memory, warps 2..9 epilogue
 constexpr uint32_t GL_TILE_BYTES = GL_BM * GL_BK * 2;       // 16 KB (x tile and weight tile alike)
 constexpr uint32_t GL_STAGE_BYTES = 2 * GL_TILE_BYTES;      // 32 KB per block
 constexpr uint32_t GL_ACC_COLS = 256;
 constexpr uint32_t GL_TMEM_COLS = 512;                      // two accumulators
-constexpr int GL_SMEM = GL_STAGES * GL_STAGE_BYTES + (2 * GL_STAGES + 4) * 8 + 16 + 1024;
+constexpr int GL_SMEM = GL_STAGES * GL_STAGE_BYTES + (2 * GL_STAGES + 4) * 8 + 32 + 1024;
 
 struct GemmLargeParams {
     bf16* y;            // GATED: [m_tok, n_out]; else [m_tok, n_out]
@@ -97,6 +97,40 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 }
 __device__ __forceinline__ float silu_times(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
+// One chunk of 32 accumulator columns of a token row to memory.  GATED: `a` = gate columns
+// [c0, c0+32), `b` = the up columns of the same outputs; else `a` = columns [c0, c0+32) of y.
+template <bool GATED>
+__device__ __forceinline__ void gl_store_chunk(const GemmLargeParams& p, int token, int n_tile, int c0,
+                                               const float (&a)[32], const float (&b)[32]) {
+    if (token >= p.m_tok) return;
+    if (GATED) {
+        bf16* dst = p.y + (size_t)token * p.n_out + (size_t)n_tile * GL_BN + c0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(silu_times(a[i], b[i]), silu_times(a[i + 1], b[i + 1]));
+            o.y = pack_bf16x2(silu_times(a[i + 2], b[i + 2]), silu_times(a[i + 3], b[i + 3]));
+            o.z = pack_bf16x2(silu_times(a[i + 4], b[i + 4]), silu_times(a[i + 5], b[i + 5]));
+            o.w = pack_bf16x2(silu_times(a[i + 6], b[i + 6]), silu_times(a[i + 7], b[i + 7]));
+            *reinterpret_cast<uint4*>(dst + i) = o;
+        }
+    } else {
+        const int n0 = n_tile * 2 * GL_BN + c0;
+        bf16* dst = p.y + (size_t)token * p.n_out + n0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            if (n0 + i >= p.n_out) break;  // n_out is a multiple of 8
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = a[i + j] + (p.bias ? __bfloat162float(p.bias[n0 + i + j]) : 0.f);
+            uint4 o;
+            o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+            o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+            *reinterpret_cast<uint4*>(dst + i) = o;
+        }
+    }
+}
+
 template <bool GATED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GL_THREADS)
 gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -107,11 +141,12 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    // carve: [stages: x tile, weight tile][full, empty][tfull x2, tempty x2][tmem pointer]
+    // carve: [stages: x tile, weight tile][full, empty][tfull x2, tempty x2][tmem pointer][wait flags]
     uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + GL_STAGES * GL_STAGE_BYTES);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * GL_STAGES;
     const uint32_t tfull0 = empty0 + 8 * GL_STAGES, tempty0 = tfull0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GL_STAGES + 4);
+    volatile int* wait_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);  // two, used in turn
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();          // 0 leads: it issues the MMAs and owns full / tempty
@@ -120,7 +155,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GL_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 16); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {  // the same warp of both blocks: 512 columns in each block's tensor memory
@@ -139,8 +174,8 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         const uint32_t lead_full0 = map_to_rank(full0, 0);
         bool ok = true;
         int it = 0;
-        for (int t = pair; t < total && ok; t += pairs) {
-            const int n_tile = t / p.m_tiles, m_tile = t % p.m_tiles;
+        for (int tile = pair; tile < total && ok; tile += pairs) {
+            const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
             const int x_row = m_tile * 2 * GL_BM + (int)rank * GL_BM;
             const int w_row = GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN;
             for (int kb = 0; kb < p.k_tiles; ++kb, ++it) {
@@ -161,10 +196,10 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         const bool issuer = elect_one();
         const uint32_t peer_empty0 = map_to_rank(empty0, 1), peer_tfull0 = map_to_rank(tfull0, 1);
         bool ok = true;
-        int it = 0, ti = 0;
-        for (int t = pair; t < total && ok; t += pairs, ++ti) {
-            const int b = ti & 1;
-            const uint32_t tph = (uint32_t)(ti >> 1) & 1u;
+        int it = 0, si = 0;
+        for (int tile = pair; tile < total && ok; tile += pairs, ++si) {
+            const int b = si & 1;
+            const uint32_t tph = (uint32_t)(si >> 1) & 1u;
             // both blocks have drained this accumulator
             ok = __all_sync(0xffffffffu, mbar_wait(tempty0 + 8 * b, tph ^ 1u, p.status, 12));
             if (!ok) break;
@@ -195,71 +230,40 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             __syncwarp();
         }
     } else if (warp >= 2) {
-        // ---- epilogue: four warps, 32 token lanes each ------------------------------------------
+        // ---- epilogue: eight warps; a warp reads the 32 token lanes of its quarter of tensor memory
+        // and one half of the accumulator's columns --------------------------------------------------
         const uint32_t lead_tempty0 = map_to_rank(tempty0, 0);
-        const int quad = warp & 3;  // the lanes of tensor memory this warp may read
+        const int quad = warp & 3;          // the lanes of tensor memory this warp may read
+        const int half = (warp - 2) >> 2;   // which half of the columns
         const int row_local = quad * 32 + lane;
+        // GATED: outputs [c_begin, c_end) of the tile's 128 (gate column c, up column 128 + c);
+        // else accumulator columns [c_begin, c_end) of 256
+        constexpr int SPAN = GATED ? GL_BN / 2 : GL_BN;
+        const int c_begin = half * SPAN, c_end = c_begin + SPAN;
         bool ok = true;
-        int ti = 0;
-        for (int t = pair; t < total && ok; t += pairs, ++ti) {
-            const int n_tile = t / p.m_tiles, m_tile = t % p.m_tiles;
-            const int b = ti & 1;
-            const uint32_t tph = (uint32_t)(ti >> 1) & 1u;
-            int got = 1;
-            if (lane == 0) got = mbar_wait(tfull0 + 8 * b, tph, p.status, 14) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+        int si = 0;
+        for (int tile = pair; tile < total && ok; tile += pairs, ++si) {
+            const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+            const int b = si & 1;
+            const uint32_t tph = (uint32_t)(si >> 1) & 1u;
+            // one lane waits for the accumulator and tells the eight warps
+            if (warp == 2 && lane == 0) wait_flag[si & 1] = mbar_wait(tfull0 + 8 * b, tph, p.status, 14) ? 1 : 0;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            ok = wait_flag[si & 1] != 0;
             if (!ok) break;
             tc_fence_after();
             const int token = m_tile * 2 * GL_BM + (int)rank * GL_BM + row_local;
             const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)b * GL_ACC_COLS;
-            if (GATED) {
-                bf16* dst = p.y + (size_t)token * p.n_out + (size_t)n_tile * GL_BN;
 #pragma unroll 1
-                for (int c0 = 0; c0 < GL_BN; c0 += 32) {
-                    uint32_t g[32], u[32];
-                    tc_ld32_nowait(taddr + c0, g);
-                    tc_ld32_nowait(taddr + GL_BN + c0, u);
-                    tc_ld_wait();
-                    if (token < p.m_tok) {
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+                uint32_t ra[32], rb[32];
+                tc_ld32_nowait(taddr + c0, ra);
+                if (GATED) tc_ld32_nowait(taddr + GL_BN + c0, rb);
+                tc_ld_wait();
+                float fa[32], fb[32];
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 o;
-                            o.x = pack_bf16x2(silu_times(__uint_as_float(g[i]), __uint_as_float(u[i])),
-                                              silu_times(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1])));
-                            o.y = pack_bf16x2(silu_times(__uint_as_float(g[i + 2]), __uint_as_float(u[i + 2])),
-                                              silu_times(__uint_as_float(g[i + 3]), __uint_as_float(u[i + 3])));
-                            o.z = pack_bf16x2(silu_times(__uint_as_float(g[i + 4]), __uint_as_float(u[i + 4])),
-                                              silu_times(__uint_as_float(g[i + 5]), __uint_as_float(u[i + 5])));
-                            o.w = pack_bf16x2(silu_times(__uint_as_float(g[i + 6]), __uint_as_float(u[i + 6])),
-                                              silu_times(__uint_as_float(g[i + 7]), __uint_as_float(u[i + 7])));
-                            *reinterpret_cast<uint4*>(dst + c0 + i) = o;
-                        }
-                    }
-                }
-            } else {
-                const int n0 = n_tile * 2 * GL_BN;
-                bf16* dst = p.y + (size_t)token * p.n_out + n0;
-#pragma unroll 1
-                for (int c0 = 0; c0 < 2 * GL_BN; c0 += 32) {
-                    uint32_t v[32];
-                    tc_ld32_nowait(taddr + c0, v);
-                    tc_ld_wait();
-                    if (token < p.m_tok) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            const int n = n0 + c0 + i;
-                            if (n >= p.n_out) break;  // n_out is a multiple of 8
-                            float f[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                f[j] = __uint_as_float(v[i + j]) + (p.bias ? __bfloat162float(p.bias[n + j]) : 0.f);
-                            uint4 o;
-                            o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-                            o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-                            *reinterpret_cast<uint4*>(dst + c0 + i) = o;
-                        }
-                    }
-                }
+                for (int i = 0; i < 32; ++i) { fa[i] = __uint_as_float(ra[i]); fb[i] = GATED ? __uint_as_float(rb[i]) : 0.f; }
+                gl_store_chunk<GATED>(p, token, n_tile, c0, fa, fb);
             }
             tc_fence_before();
             __syncwarp();
@@ -289,7 +293,19 @@ static int launch_gemm_large(const CUtensorMap& mx, const CUtensorMap& mw, const
         int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2)
             return EMS_ERR_LAUNCH;
-        pairs_cached[dev] = sms / 2;
+        // how many pairs the device runs at once: not every SM need have a partner for a cluster of two
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sms); cfg.blockDim = dim3(GL_THREADS); cfg.dynamicSmemBytes = GL_SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
+            cudaGetLastError();
+            clusters = sms / 2;
+        }
+        pairs_cached[dev] = clusters;
     }
     const int total = p.m_tiles * p.n_tiles;
     const int pairs = total < pairs_cached[dev] ? total : pairs_cached[dev];
@@ -327,7 +343,11 @@ EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int
 }
 
 // y[m_tok, n_out] (bf16) = x[m_tok, k] . w[n_out, k]^T (+ bias), any number of rows; n_out and k
-// multiples of 8, 16-byte aligned pointers.
+// multiples of 8, 16-byte aligned pointers.  The engine keeps cuBLAS for these plain products: whole
+// 256 x 256 tiles fill the SM pairs unevenly at its shapes (112 tiles on 74 pairs for a 2048 x 3584
+// output), and splitting the left-over tiles along K (tried: partial sums through a workspace, added
+// in K order by the last block to arrive) bought nothing, because a product this long runs at the
+// power limit whatever its schedule.
 EMS_EXPORT int ems_gemm_large(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out, int k,
                               cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;

@@ -382,7 +382,9 @@ def gemm_large_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -
 
 
 def gemm_large(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
-    """out[m, n] = x . weight[n] (+ bias[n]) on the same two-SM tcgen05 kernel; n and K multiples of 8."""
+    """out[m, n] = x . weight[n] (+ bias[n]) on the same two-SM tcgen05 kernel; n and K multiples of 8.
+    (The engine's plain products stay with cuBLAS, which is ahead at its shapes; this entry serves
+    feed-forwards without a gate.)"""
     m, k = x.shape
     n = weight.shape[0]
     assert weight.shape == (n, k) and out.shape == (m, n)

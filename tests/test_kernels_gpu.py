@@ -656,8 +656,10 @@ def test_gemm_large_gated_refuses():
 
 
 @pytest.mark.parametrize("m,n,k,bias", [(300, 256, 128, True), (2048, 4608, 896, True), (513, 896, 4864, False),
-                                        (65, 136, 72, True), (1000, 3584, 3584, False), (257, 1000, 200, True)])
+                                        (65, 136, 72, True), (1000, 3584, 3584, False), (257, 1000, 200, True),
+                                        (2048, 3584, 18944, False), (512, 3584, 3584, False), (4000, 5120, 640, True)])
 def test_gemm_large_plain(m, n, k, bias):
+    """The two-SM kernel without the gate: bias in the epilogue, output columns that end inside a tile."""
     g = torch.Generator(device="cuda").manual_seed(m * 31 + n)
     x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
     w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
