@@ -128,7 +128,7 @@ def run_ours(args) -> dict:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA GPU"
     peaks = measured_peaks()
-    shape = dict(SHAPE_7B)
+    shape = dict({"7b": SHAPE_7B, "0.5b": SHAPE_05B, "32b": SHAPE_32B}[args.model_shape])
     full_layers = shape["num_hidden_layers"]
     shape["num_hidden_layers"] = args.layers or full_layers
     cfg = Qwen2Config.from_dict(dict(shape, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
@@ -271,11 +271,13 @@ def run_ours(args) -> dict:
                  "share": round(e.device_time_total / total, 4)} for e in rows[:25]]
 
     if args.only == "decode":
-        d = decode(args.batch, args.steps, args.warmup)
-        out = {"only": "decode", "dtype": args.dtype, "batch": args.batch, "layers": layers, "ms_per_step": d["ms"],
+        d = decode(args.batch, args.steps, args.warmup, context=args.decode_context)
+        out = {"only": "decode", "dtype": args.dtype, "batch": args.batch, "layers": layers,
+               "shape": args.model_shape, "context": args.decode_context, "ms_per_step": d["ms"],
                "tok_s": d["tok_s"], "hbm_frac": d["gbs"] / peaks["hbm_gbs"]}
         if args.kernel_times:
-            out["kernels"] = kernel_times(lambda: decode(args.batch, args.steps, args.warmup))
+            out["kernels"] = kernel_times(lambda: decode(args.batch, args.steps, args.warmup,
+                                                         context=args.decode_context))
         return out
     if args.only == "prefill":
         out = dict(prefill(max(1, args.steps)), only="prefill", layers=layers, dtype=args.dtype)
@@ -326,7 +328,7 @@ def run_kernel(args) -> dict:
     from emberserve_b200 import kernels as K
 
     peaks = measured_peaks()
-    s = SHAPE_7B
+    s = {"7b": SHAPE_7B, "0.5b": SHAPE_05B, "32b": SHAPE_32B}[args.model_shape]
     nh, nkv, d, ps = s["num_attention_heads"], s["num_key_value_heads"], s["head_dim"], PAGE_SIZE
     dev = "cuda:0"
     g = torch.Generator(device=dev).manual_seed(0)
@@ -713,6 +715,9 @@ def main() -> int:
     ap.add_argument("--temperature", type=float, default=0.0, help="with --workload serve-0.5b (0 = greedy)")
     ap.add_argument("--top-k", type=int, default=-1, help="with --workload serve-0.5b")
     ap.add_argument("--top-p", type=float, default=1.0, help="with --workload serve-0.5b")
+    ap.add_argument("--model-shape", choices=["7b", "0.5b", "32b"], default="7b",
+                    help="with --only decode / prefill: the layer sizes (the default line is always the 7B shape)")
+    ap.add_argument("--decode-context", type=int, default=CONTEXT, help="with --only decode: context the steps end at")
     ap.add_argument("--library-prefill-mlp", action="store_true",
                     help="for comparison: gate/up product of prompt steps by cuBLAS and a separate SiLU "
                          "kernel instead of the two-SM tcgen05 kernel with SiLU in its epilogue")

@@ -73,8 +73,11 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bo
     """out = silu(x Wg^T) * (x Wu^T) with weight = [Wg; Wu], in one kernel, where a hand-written
     kernel takes the case: the weight-streaming one up to 64 rows, the two-SM one (256 x 256
     tiles, persistent) above; False if the caller has to do it in steps.  At the 7B shape the
-    two-SM kernel takes 58 / 102 / 389 us at 256 / 512 / 2048 rows, cuBLAS and the activation
-    kernel behind it 76 / 101 / 395."""
+    two-SM kernel takes 55 / 93 / 352 us at 256 / 512 / 2048 rows, cuBLAS and the activation
+    kernel behind it 76 / 101 / 392.  It also pays where its tiles do not fill the SM pairs: a decode
+    step of the 0.5B shape at 256 rows (38 tiles of the 9728 x 896 weight) takes 1.53 ms with it and
+    1.57 with the library and the activation kernel, although alone the library is ahead there
+    (9.7 us against 11.9): inside a graph one launch less weighs more than the kernel's fixed cost."""
     if _use_smallm(x, weight, None, out, _GATED_ROWS):
         K.gemm_smallm_gated(x, weight, out)
         return True
@@ -83,6 +86,7 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bo
         K.gemm_large_gated(x, weight, out)
         return True
     return False
+
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
