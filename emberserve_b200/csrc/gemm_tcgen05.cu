@@ -86,6 +86,16 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The weights do not depend on the kernel before this one: the first ring of weight tiles
+        // is requested at once, before the block has even set up its tensor memory (this thread
+        // is the producer below); the activations follow after the dependency wait.
+        const int pre = min(nk, STAGES);
+        for (int it = 0; it < pre; ++it) {
+            mbar_expect_tx(full0 + 8 * it, A_BYTES + B_BYTES);
+            const int k0 = (kt_begin + it) * G5_BK;
+            tma_load_2d(a_s + it * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * it);
+            if (DUAL) tma_load_2d(a_s + it * A_BYTES + W_BYTES, &map_w, k0, p.dual_offset + tile * G5_BM, full0 + 8 * it);
+        }
     }
     if (warp == 1) {  // tensor memory for the accumulators: TMEM_COLS columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -99,16 +109,8 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     bool ok = true;
 
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer --------------------------------------------------------------
-        // The weights do not depend on the kernel before this one: the first ring of weight
-        // tiles is requested at once, the activations only after the dependency wait.
+        // ---- TMA producer (the first ring of weight tiles is on its way already) ----------
         const int pre = min(nk, STAGES);
-        for (int it = 0; it < pre; ++it) {
-            mbar_expect_tx(full0 + 8 * it, A_BYTES + B_BYTES);
-            const int k0 = (kt_begin + it) * G5_BK;
-            tma_load_2d(a_s + it * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * it);
-            if (DUAL) tma_load_2d(a_s + it * A_BYTES + W_BYTES, &map_w, k0, p.dual_offset + tile * G5_BM, full0 + 8 * it);
-        }
         grid_dependency_wait();
         for (int it = 0; it < pre; ++it)
             tma_load_2d(b_s + it * B_BYTES, &map_x, (kt_begin + it) * G5_BK, 0, full0 + 8 * it);
