@@ -65,6 +65,7 @@ def build_parser() -> argparse.ArgumentParser:
     group = gen.add_mutually_exclusive_group(required=True)
     group.add_argument("--prompt", help="text (the model folder must hold a tokenizer.json)")
     group.add_argument("--prompt-ids", help="comma-separated token ids")
+    gen.add_argument("--chat", action="store_true", help="wrap the prompt as a user chat turn")
     gen.add_argument("--max-tokens", type=int, default=128)
     gen.add_argument("--temperature", type=float, default=0.0)
     gen.add_argument("--top-p", type=float, default=1.0)
@@ -91,8 +92,13 @@ def cmd_generate(args: argparse.Namespace) -> int:
                             top_p=args.top_p, top_k=args.top_k,
                             repetition_penalty=args.repetition_penalty, seed=args.seed)
     prompt = args.prompt if args.prompt is not None else [int(t) for t in args.prompt_ids.split(",") if t.strip()]
+    if args.chat and args.prompt is None:
+        raise SystemExit("--chat needs --prompt (text)")
     t0 = time.perf_counter()
-    res = llm.generate([prompt], params)[0]
+    if args.chat:
+        res = llm.chat([[{"role": "user", "content": args.prompt}]], params)[0]
+    else:
+        res = llm.generate([prompt], params)[0]
     dt = time.perf_counter() - t0
     n = len(res.output_token_ids)
     print(res.text if res.text else " ".join(str(t) for t in res.output_token_ids))

@@ -31,6 +31,7 @@ from emberserve_b200 import kernels as K
 from emberserve_b200.config.engine import EngineConfig
 from emberserve_b200.config.model import ModelConfig
 from emberserve_b200.engine.detokenizer import Detokenizer
+from emberserve_b200.tokenizer import load_tokenizer
 from emberserve_b200.engine.request import (FinishReason, Request, RequestOutput, check_stop)
 from emberserve_b200.engine.runner import ModelRunner, StepRow
 from emberserve_b200.engine.scheduler import Scheduler, SchedulerOutput
@@ -73,7 +74,12 @@ class LLMEngine:
         self.detokenizer = Detokenizer(tokenizer)
         self.scheduler = Scheduler(config, runner.cache)
         self.sampler = Sampler(runner.device)
-        self.eos_token_ids = frozenset(getattr(self.model_config, "eos_token_ids", ()))
+        # every id that ends a request: the configuration's, and the tokenizer's own end-of-sequence
+        # id where there is a tokenizer (emberserve/engine.py:220-222)
+        eos = set(getattr(self.model_config, "eos_token_ids", ()))
+        if getattr(tokenizer, "eos_token_id", None) is not None:
+            eos.add(int(tokenizer.eos_token_id))
+        self.eos_token_ids = frozenset(eos)
         self._next_seq_id = 0
         self._step_count = 0
         self.keep_stats = False
@@ -103,7 +109,7 @@ class LLMEngine:
             model_dir, cfg.dtype, device=cfg.device, page_size=cfg.block_size,
             num_pages=cfg.num_gpu_blocks, max_pages=useful, num_state_slots=cfg.max_num_seqs,
             gpu_memory_utilization=cfg.gpu_memory_utilization)
-        return cls(runner, cfg, tokenizer=_load_tokenizer(model_dir))
+        return cls(runner, cfg, tokenizer=load_tokenizer(model_dir))
 
     @classmethod
     def from_runner(cls, runner: ModelRunner, engine_config: EngineConfig | None = None) -> "LLMEngine":
@@ -346,26 +352,3 @@ class LLMEngine:
         if req.finished_time and req.arrival_time:
             m["e2e_s"] = req.finished_time - req.arrival_time
         return m
-
-
-def _load_tokenizer(model_dir):
-    """A tokenizer, if the folder has one and a tokenizer library is installed; the engine
-    itself works on token ids and needs none."""
-    from pathlib import Path
-
-    if not (Path(model_dir) / "tokenizer.json").is_file():
-        return None
-    try:
-        from tokenizers import Tokenizer
-    except ImportError:
-        return None
-    tok = Tokenizer.from_file(str(Path(model_dir) / "tokenizer.json"))
-
-    class _Wrapper:
-        def encode(self, text: str) -> list[int]:
-            return tok.encode(text).ids
-
-        def decode(self, ids: list[int]) -> str:
-            return tok.decode(ids)
-
-    return _Wrapper()

@@ -34,6 +34,15 @@ class LLM:
         obj.engine = engine
         return obj
 
+    def chat(self, conversations: list[list[dict]],
+             sampling_params: SamplingParams | list[SamplingParams] | None = None) -> list[GenerationResult]:
+        """One reply per conversation (a list of {"role", "content"} messages), rendered through the
+        model's chat template (emberserve/llm.py:59-64); needs a tokenizer."""
+        tok = self.engine.tokenizer
+        if tok is None or not hasattr(tok, "apply_chat_template"):
+            raise ValueError("chat() needs a tokenizer")
+        return self.generate([tok.apply_chat_template(msgs) for msgs in conversations], sampling_params)
+
     def generate(self, prompts: list[str] | list[list[int]],
                  sampling_params: SamplingParams | list[SamplingParams] | None = None,
                  ) -> list[GenerationResult]:
