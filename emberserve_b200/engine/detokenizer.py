@@ -50,6 +50,11 @@ class Detokenizer:
     def drop(self, request_id: str) -> None:
         self._progress.pop(request_id, None)
 
+    def text(self, request_id: str) -> str:
+        """What has been handed out for the request so far."""
+        st = self._progress.get(request_id)
+        return "" if st is None else st.settled[:st.shown]
+
     def feed(self, request_id: str, output_ids: list[int], stop: list[str],
              final: bool = False) -> tuple[str, str | None]:
         """The new piece of text after `output_ids` (the request's whole output so far), and the

@@ -18,6 +18,7 @@ partial result, as in the eager path.
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 
 import numpy as np
@@ -141,8 +142,18 @@ class DecodeGraphs:
         # the graph is gone (an engine that was dropped): forget the workspaces, so that this
         # capture allocates its own into its own pool, and again afterwards.
         _forget_cublas_workspaces()
-        with torch.cuda.graph(graph, pool=self._pool):
-            logits = r.decoder.forward(ctx, handles, want, bucket)
+        # No cyclic garbage collection while the stream captures: it could free the graphs of an
+        # engine that was dropped earlier, and destroying a graph is not permitted during a capture
+        # (the capture would be invalidated).  Collect now, then hold the collector off.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self._pool):
+                logits = r.decoder.forward(ctx, handles, want, bucket)
+        finally:
+            if gc_was_on:
+                gc.enable()
         _forget_cublas_workspaces()
         if self._pool is None:
             self._pool = graph.pool()

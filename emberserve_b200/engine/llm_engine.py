@@ -85,6 +85,7 @@ class LLMEngine:
         self.keep_stats = False
         self.stats: list[StepStats] = []
         self._inflight: _InFlight | None = None
+        self._final_text: dict[str, str] = {}  # text of the requests that ended last, until asked for
         self._penalties_seen = False
         self._token_host: list[torch.Tensor | None] = [None, None]
         self._token_turn = 0
@@ -115,6 +116,34 @@ class LLMEngine:
     def from_runner(cls, runner: ModelRunner, engine_config: EngineConfig | None = None) -> "LLMEngine":
         cfg = engine_config or EngineConfig(dtype=runner.dtype, block_size=runner.page_size)
         return cls(runner, cfg)
+
+    # ---- convenience ------------------------------------------------------------------------
+    FINAL_TEXT_KEEP = 1024
+
+    def _keep_final_text(self, request_id: str) -> None:
+        if self.tokenizer is not None:
+            self._final_text[request_id] = self.detokenizer.text(request_id)
+            while len(self._final_text) > self.FINAL_TEXT_KEEP:
+                self._final_text.pop(next(iter(self._final_text)))
+        self.detokenizer.drop(request_id)
+
+    def output_text(self, request_id: str) -> str:
+        """Text so far of a live request, or the whole text of one that has ended (handed out once;
+        the last FINAL_TEXT_KEEP ended requests are kept; emberserve/engine.py:1102-1107)."""
+        if request_id in self._final_text:
+            return self._final_text.pop(request_id)
+        return self.detokenizer.text(request_id)
+
+    def release_graphs(self) -> None:
+        """Let go of the captured CUDA graphs; decode steps then launch their kernels one by one
+        (emberserve/engine.py:564-573)."""
+        import gc
+
+        if self.runner.device.type == "cuda":
+            torch.cuda.synchronize(self.runner.device)  # a step that was launched from a graph has run
+        self.runner.use_graphs = False
+        self.runner.graphs = None
+        gc.collect()
 
     # ---- requests --------------------------------------------------------------------------
     def add_request(self, request_id: str, prompt: str | list[int],
@@ -150,6 +179,7 @@ class LLMEngine:
 
     def reset(self) -> None:
         self._inflight = None
+        self._final_text.clear()
         for req in list(self.scheduler.running) + list(self.scheduler.waiting):
             self.scheduler.abort_request(req.request_id)
             self.detokenizer.drop(req.request_id)
@@ -310,7 +340,7 @@ class LLMEngine:
                 del req.output_token_ids[place + 1:]  # a placeholder of the step launched since
                 req.hold = False
                 self.scheduler.finish_request(req, reason)
-                self.detokenizer.drop(req.request_id)
+                self._keep_final_text(req.request_id)
             outputs.append(RequestOutput(
                 request_id=req.request_id, new_token_ids=[int(tok)],
                 output_token_ids=req.output_token_ids[:place + 1], finished=reason is not None,
@@ -334,7 +364,7 @@ class LLMEngine:
                 reason = FinishReason.STOP  # the text has reached a stop string
             if reason is not None:
                 self.scheduler.finish_request(req, reason)
-                self.detokenizer.drop(req.request_id)
+                self._keep_final_text(req.request_id)
             outputs.append(RequestOutput(
                 request_id=req.request_id, new_token_ids=[int(tok)],
                 output_token_ids=list(req.output_token_ids), finished=reason is not None,

@@ -141,6 +141,32 @@ def test_async_scheduling_changes_no_token_on_the_gpu(sharp_dirs, dtype, how):
     assert [r for _, r in results[0]][:2] == [FinishReason.STOP, FinishReason.STOP]
 
 
+def test_released_graphs_change_no_token(sharp_dirs):
+    """release_graphs() lets go of the captured decode graphs; the engine then launches its kernels
+    one by one and generates the same tokens (also with a step still in flight at the release)."""
+    from emberserve_b200 import SamplingParams
+
+    name = "tiny_b"
+    g = torch.Generator().manual_seed(23)
+    prompts = [torch.randint(0, ALL[name].vocab_size, (n,), generator=g).tolist() for n in (9, 4, 13)]
+    llm = _llm(sharp_dirs[name], name, "float32", pages=64)
+    assert llm.engine.runner.graphs is not None
+    want = [r.output_token_ids for r in llm.generate(prompts, SamplingParams.greedy(12, ignore_eos=True))]
+    for i, p in enumerate(prompts):
+        llm.engine.add_request(f"again-{i}", p, SamplingParams.greedy(12, ignore_eos=True))
+    got: dict[str, list[int]] = {}
+    steps = 0
+    while llm.engine.has_unfinished_requests():
+        for out in llm.engine.step():
+            if out.finished:
+                got[out.request_id] = out.output_token_ids
+        steps += 1
+        if steps == 5:
+            llm.engine.release_graphs()
+            assert llm.engine.runner.graphs is None
+    assert [got[f"again-{i}"] for i in range(len(prompts))] == want
+
+
 def test_command_line_generates_what_the_entry_point_generates(sharp_dirs):
     """`python -m emberserve_b200 generate --prompt-ids ...` prints the tokens that
     LLM.generate() returns, and the throughput line on standard error."""

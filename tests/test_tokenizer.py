@@ -115,6 +115,17 @@ def test_engine_ends_on_the_tokenizers_eos_and_chat_goes_through_the_template(mo
     assert res.text == llm.engine.tokenizer.decode(res.output_token_ids)
     text = llm.generate(["hello world"], SamplingParams.greedy(2, ignore_eos=True))[0]
     assert text.prompt_token_ids == ids("hello", "world")
+    # the text of a request that has ended can be asked for once, that of a live one at any time
+    assert llm.engine.output_text("req-0") == text.text
+    assert llm.engine.output_text("req-0") == ""
+    llm.engine.add_request("live", "how are you", SamplingParams.greedy(6, ignore_eos=True))
+    pieces = []
+    while llm.engine.has_unfinished_requests():
+        for out in llm.engine.step():
+            pieces.append(out.text_delta)
+            if not out.finished:
+                assert llm.engine.output_text("live") == "".join(pieces)
+    assert llm.engine.output_text("live") == "".join(pieces)
 
 
 def test_chat_needs_a_tokenizer(tmp_path, monkeypatch):
