@@ -136,12 +136,18 @@ def run_ours(args) -> dict:
     K.library()
     torch.manual_seed(0)
     max_b = max(64, args.batch)
-    pages = max_b * (CONTEXT // PAGE_SIZE + 1) + PREFILL_TOKENS // PAGE_SIZE + 64
+    ctx_cap = CONTEXT
+    if args.only == "decode":  # a single phase at another context: size the pool and the graphs for it
+        max_b, ctx_cap = args.batch, max(CONTEXT, args.decode_context)
+    ptoks = args.prefill_tokens if args.only == "prefill" else PREFILL_TOKENS
+    if args.only == "prefill":
+        max_b = 1
+    pages = max_b * (ctx_cap // PAGE_SIZE + 1) + 2 * (ptoks // PAGE_SIZE) + 64
     dtype = torch.float32 if args.dtype == "float32" else torch.bfloat16
     runner = ModelRunner.from_random(cfg, seed=0, dtype=dtype, device="cuda:0",
                                      page_size=PAGE_SIZE, num_pages=pages)
     if not args.no_graphs:
-        runner.enable_graphs(CONTEXT + 64, max_b)
+        runner.enable_graphs(ctx_cap + 64, max_b)
     for t in runner.storage.tensors:  # keys and values of the "earlier" tokens: random, not zero
         t.normal_(0, 1)
     m = model_bytes_and_flops(cfg, layers)
@@ -198,12 +204,12 @@ def run_ours(args) -> dict:
                 "clocks": clocks.summary() if clocks else None}
 
     def prefill(iters: int = 3, portions: int = 1) -> dict:
-        """One prompt of PREFILL_TOKENS tokens, in one step or in `portions` equal steps."""
+        """One prompt of `ptoks` tokens, in one step or in `portions` equal steps."""
         times = []
-        part = PREFILL_TOKENS // portions
+        part = ptoks // portions
         for it in range(iters + 1):
-            runner.cache.admit(5000 + it, PREFILL_TOKENS)
-            toks = rand_tokens(PREFILL_TOKENS)
+            runner.cache.admit(5000 + it, ptoks)
+            toks = rand_tokens(ptoks)
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             ev0.record()
@@ -216,9 +222,9 @@ def run_ours(args) -> dict:
             if it:
                 times.append(ev0.elapsed_time(ev1))
         ms = statistics.mean(times)
-        flops = (PREFILL_TOKENS * m["linear_flops_per_token"] + m["attn_flops_causal"](PREFILL_TOKENS)
+        flops = (ptoks * m["linear_flops_per_token"] + m["attn_flops_causal"](ptoks)
                  + m["head_flops"])
-        return {"value": PREFILL_TOKENS * 1e3 / ms, "tokens": PREFILL_TOKENS, "ms": ms,
+        return {"value": ptoks * 1e3 / ms, "tokens": ptoks, "ms": ms,
                 "frac": flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / ms / 1e9}
 
     def end_to_end(batch: int, steps: int, warmup: int) -> dict:
@@ -717,6 +723,7 @@ def main() -> int:
     ap.add_argument("--top-p", type=float, default=1.0, help="with --workload serve-0.5b")
     ap.add_argument("--model-shape", choices=["7b", "0.5b", "32b"], default="7b",
                     help="with --only decode / prefill: the layer sizes (the default line is always the 7B shape)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: the prompt's length")
     ap.add_argument("--decode-context", type=int, default=CONTEXT, help="with --only decode: context the steps end at")
     ap.add_argument("--library-prefill-mlp", action="store_true",
                     help="for comparison: gate/up product of prompt steps by cuBLAS and a separate SiLU "
