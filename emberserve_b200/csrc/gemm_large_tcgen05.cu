@@ -174,17 +174,34 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         const uint32_t lead_full0 = map_to_rank(full0, 0);
         bool ok = true;
         int it = 0;
+        // The weights do not depend on the kernel before this one (the launch is a programmatic
+        // dependent): the weight halves of the first stages are requested at once, the token rows
+        // after the dependency wait.
+        const int pre = pair < total ? min(p.k_tiles, GL_STAGES) : 0;
+        {
+            const int n_tile = pair / p.m_tiles;
+            const int w_row = GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN;
+            for (int kb = 0; kb < pre; ++kb) {
+                if (rank == 0) mbar_expect_tx(full0 + 8 * kb, 2 * GL_STAGE_BYTES);
+                tma_load_2d_pair(base + kb * GL_STAGE_BYTES + GL_TILE_BYTES, &map_w, kb * GL_BK, w_row, lead_full0 + 8 * kb);
+            }
+        }
+        grid_dependency_wait();
         for (int tile = pair; tile < total && ok; tile += pairs) {
             const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
             const int x_row = m_tile * 2 * GL_BM + (int)rank * GL_BM;
             const int w_row = GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN;
             for (int kb = 0; kb < p.k_tiles; ++kb, ++it) {
                 const int s = it % GL_STAGES;
+                const uint32_t dst = base + s * GL_STAGE_BYTES;
+                if (it < pre) {  // armed above, the weight half is on its way
+                    tma_load_2d_pair(dst, &map_x, kb * GL_BK, x_row, lead_full0 + 8 * s);
+                    continue;
+                }
                 const uint32_t ph = (uint32_t)(it / GL_STAGES) & 1u;
                 ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 11);
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * GL_STAGE_BYTES);
-                const uint32_t dst = base + s * GL_STAGE_BYTES;
                 tma_load_2d_pair(dst, &map_x, kb * GL_BK, x_row, lead_full0 + 8 * s);
                 tma_load_2d_pair(dst + GL_TILE_BYTES, &map_w, kb * GL_BK, w_row, lead_full0 + 8 * s);
             }
@@ -309,7 +326,21 @@ static int launch_gemm_large(const CUtensorMap& mx, const CUtensorMap& mw, const
     }
     const int total = p.m_tiles * p.n_tiles;
     const int pairs = total < pairs_cached[dev] ? total : pairs_cached[dev];
-    kernel<<<dim3(2 * pairs), dim3(GL_THREADS), GL_SMEM, stream>>>(mx, mw, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(GL_THREADS);
+    cfg.dynamicSmemBytes = GL_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    // may start while the kernel before it still runs: set-up and the first weight tiles overlap it
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, mx, mw, p) != cudaSuccess) {
+        cudaGetLastError();
+        return EMS_ERR_LAUNCH;
+    }
     return launch_status();
 }
 
