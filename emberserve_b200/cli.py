@@ -38,6 +38,8 @@ def _add_engine_args(p: argparse.ArgumentParser) -> None:
                    default=True, help="mix decode tokens and prompt portions in every step (default)")
     p.add_argument("--no-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
     p.add_argument("--no-cuda-graphs", dest="enable_cuda_graphs", action="store_false", default=True)
+    p.add_argument("--debug-scratch-guard", type=int, default=0, metavar="N",
+                   help="debugging: N guard elements around every scratch buffer, checked after each step")
     p.add_argument("--no-async-scheduling", dest="async_scheduling", action="store_false", default=True,
                    help="read every step's tokens before the next step is planned")
 
@@ -54,7 +56,8 @@ def engine_config_from_args(args: argparse.Namespace):
                         max_model_len=args.max_model_len,
                         enable_chunked_prefill=args.enable_chunked_prefill,
                         enable_cuda_graphs=args.enable_cuda_graphs,
-                        async_scheduling=args.async_scheduling)
+                        async_scheduling=args.async_scheduling,
+                        debug_scratch_guard=args.debug_scratch_guard)
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -51,6 +51,10 @@ class EngineConfig:
     # token history on the host (a repetition penalty) switch the engine to plain stepping.
     async_scheduling: bool = True
     seed: int = 0
+    # A debugging aid: scratch buffers of the steps get this many guard elements on either side
+    # and the engine checks after every step that no kernel wrote there (it waits for the device
+    # to do so, so steps no longer overlap).
+    debug_scratch_guard: int = 0
     extra: dict = field(default_factory=dict)
 
     def __post_init__(self) -> None:

@@ -116,7 +116,7 @@ class DecodeGraphs:
             return meta[offsets[name]:offsets[name] + size]
 
         kv_heads = max((g.need.num_kv_heads for g in r.groups if isinstance(g.need, PagedKV)), default=1)
-        arena = self._arena_cls(dev)
+        arena = self._arena_cls(dev, guard=r.scratch.guard)
         ctx = StepContext(
             num_tokens=bucket, num_rows=bucket, dtype=r.dtype, device=dev,
             tokens=view("tokens", bucket), positions=view("positions", bucket),
@@ -170,6 +170,10 @@ class DecodeGraphs:
                 self._graphs[bucket] = self._capture(bucket)
                 done += 1
         return done
+
+    def verify_scratch(self) -> None:
+        for g in self._graphs.values():
+            g.keep[0].verify()
 
     def run(self, rows) -> torch.Tensor:
         r = self.runner

@@ -109,7 +109,7 @@ class LLMEngine:
         runner = ModelRunner.from_dir(
             model_dir, cfg.dtype, device=cfg.device, page_size=cfg.block_size,
             num_pages=cfg.num_gpu_blocks, max_pages=useful, num_state_slots=cfg.max_num_seqs,
-            gpu_memory_utilization=cfg.gpu_memory_utilization)
+            gpu_memory_utilization=cfg.gpu_memory_utilization, scratch_guard=cfg.debug_scratch_guard)
         return cls(runner, cfg, tokenizer=load_tokenizer(model_dir))
 
     @classmethod
@@ -208,7 +208,9 @@ class LLMEngine:
         call before this one; a last call with nothing left to launch returns the rest."""
         if not self.config.async_scheduling or self._history_needed():
             outputs = self._finalize(self._take_inflight())
-            return outputs + self._step_sync()
+            outputs += self._step_sync()
+            self.runner.verify_scratch()
+            return outputs
         so = self.scheduler.schedule()
         if so.is_empty:
             if self._inflight is None:
@@ -216,6 +218,7 @@ class LLMEngine:
             return self._finalize(self._take_inflight())
         before = self._take_inflight()
         self._inflight = self._launch(so)
+        self.runner.verify_scratch()  # (does nothing unless the scratch buffers are guarded)
         return self._finalize(before)
 
     def _history_needed(self) -> bool:

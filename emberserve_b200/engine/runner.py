@@ -53,11 +53,20 @@ class StepRow:
 
 class ScratchArena:
     """Named buffers that live across steps; a request for more than a buffer holds
-    replaces it with a larger one."""
+    replaces it with a larger one.
 
-    def __init__(self, device: torch.device) -> None:
+    With `guard` > 0 every buffer gets that many extra elements before and after it, filled
+    with a pattern that `verify()` looks for again: a kernel that writes outside the buffer it
+    was given shows up there (a debugging aid; compute-sanitizer's memcheck does the same where
+    it can be run)."""
+
+    _PATTERN = 0x5A
+
+    def __init__(self, device: torch.device, guard: int = 0) -> None:
         self.device = device
+        self.guard = guard
         self._bufs: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+        self._whole: dict[tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False  # set while CUDA graphs hold pointers into the buffers
 
     def __call__(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -69,9 +78,30 @@ class ScratchArena:
         if buf is None or buf.numel() < numel:
             if self.frozen and buf is not None:
                 raise RuntimeError(f"scratch buffer {name!r} would move while graphs hold it")
-            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            if self.guard:
+                # guards of a multiple of 16 bytes keep the buffer as aligned as the allocation
+                g = -(-self.guard * dtype.itemsize // 16) * 16 // dtype.itemsize
+                whole = torch.empty(max(numel, 1) + 2 * g, dtype=dtype, device=self.device)
+                whole.view(torch.uint8).fill_(self._PATTERN)
+                self._whole[key] = whole
+                buf = whole[g:g + max(numel, 1)]
+            else:
+                buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:numel].view(shape)
+
+    def verify(self) -> None:
+        """Raise if the elements around a buffer no longer hold the pattern (guard > 0)."""
+        for (name, dtype), whole in self._whole.items():
+            n = self._bufs[(name, dtype)].numel()
+            g = (whole.numel() - n) // 2
+            raw = whole.view(torch.uint8)
+            size = dtype.itemsize
+            for what, part in (("before", raw[:g * size]), ("after", raw[(g + n) * size:])):
+                if bool((part != self._PATTERN).any()):
+                    where = int((part != self._PATTERN).nonzero()[0])
+                    raise RuntimeError(f"scratch buffer {name!r} ({dtype}): something wrote {what} it "
+                                       f"(byte {where} of the guard)")
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
@@ -89,7 +119,8 @@ class ModelRunner:
     def __init__(self, config: ModelConfig, decoder: Decoder, dtype: torch.dtype,
                  device: str | torch.device = "cuda:0", page_size: int = 16,
                  num_pages: int | None = None, max_pages: int | None = None,
-                 num_state_slots: int = 256, gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES) -> None:
+                 num_state_slots: int = 256, gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES,
+                 scratch_guard: int = 0) -> None:
         self.device = torch.device(device)
         if self._require_cuda and (self.device.type != "cuda" or not torch.cuda.is_available()):
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path "
@@ -120,7 +151,7 @@ class ModelRunner:
         self.scratch_page = num_pages
         self.storage = CacheStorage(self.groups, [num_pages + 1] * len(paged), page_size,
                                     num_state_slots if has_state else 0, dtype, self.device)
-        self.scratch = ScratchArena(self.device)
+        self.scratch = ScratchArena(self.device, guard=scratch_guard)
         self._meta_dev = torch.empty(1 << 12, dtype=torch.int32, device=self.device)
         self._meta_host = [torch.empty(1 << 12, dtype=torch.int32, pin_memory=self._on_cuda)
                            for _ in range(2)]
@@ -277,6 +308,17 @@ class ModelRunner:
             deferred=self.token_feedback)
         bt = [dev(7 + k).view(b, tables[k].shape[1]) for k in range(npaged)]
         return ctx, bt, dev(6), dev(5), num_want
+
+    def verify_scratch(self) -> None:
+        """With guarded scratch buffers (scratch_guard > 0): wait for the device and raise if a
+        kernel wrote outside a buffer of a step."""
+        if not self.scratch.guard:
+            return
+        if self._on_cuda:
+            torch.cuda.synchronize(self.device)
+        self.scratch.verify()
+        if self.graphs is not None:
+            self.graphs.verify_scratch()
 
     @torch.inference_mode()
     def step(self, rows: list[StepRow]) -> torch.Tensor:

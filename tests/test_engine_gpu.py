@@ -141,6 +141,28 @@ def test_async_scheduling_changes_no_token_on_the_gpu(sharp_dirs, dtype, how):
     assert [r for _, r in results[0]][:2] == [FinishReason.STOP, FinishReason.STOP]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d"])
+def test_no_kernel_writes_outside_its_scratch_buffers(sharp_dirs, name, dtype):
+    """Generation with guard elements around every scratch buffer of the steps (eager and graph
+    arenas): whole prompts, portions, decode steps from graphs, sampled and greedy.  The engine
+    checks the guards after every step and raises if a kernel wrote there."""
+    from emberserve_b200 import SamplingParams
+
+    g = torch.Generator().manual_seed(5)
+    top = min(100, ALL[name].max_position_embeddings - 20)
+    prompts = [torch.randint(0, ALL[name].vocab_size, (n,), generator=g).tolist() for n in (1, 9, 33, top, 70)]
+    params = [SamplingParams.greedy(8, ignore_eos=True), SamplingParams(max_tokens=8, temperature=0.8, seed=1, ignore_eos=True),
+              SamplingParams(max_tokens=8, temperature=1.0, top_k=5, top_p=0.9, seed=2, ignore_eos=True),
+              SamplingParams.greedy(8, ignore_eos=True), SamplingParams.greedy(8, ignore_eos=True)]
+    for how in (dict(), dict(max_num_batched_tokens=16), dict(enable_cuda_graphs=False, async_scheduling=False)):
+        llm = _llm(sharp_dirs[name], name, dtype, debug_scratch_guard=64, **how)
+        assert llm.engine.runner.scratch.guard == 64
+        res = llm.generate(prompts, params)
+        assert all(len(r.output_token_ids) == 8 for r in res)
+        llm.engine.runner.verify_scratch()
+
+
 def test_released_graphs_change_no_token(sharp_dirs):
     """release_graphs() lets go of the captured decode graphs; the engine then launches its kernels
     one by one and generates the same tokens (also with a step still in flight at the release)."""

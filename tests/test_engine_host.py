@@ -356,3 +356,27 @@ def test_stop_strings_end_a_request(model_dirs, async_on):
     assert res[1].text == tok.decode(res[1].output_token_ids)
     st = llm.engine.runner.cache.stats()
     assert st.num_free == st.num_pages and st.num_sequences == 0
+
+
+def test_scratch_guards_catch_a_write_outside_a_buffer():
+    """The debugging arena: guard elements around every buffer keep their pattern unless
+    something writes outside the buffer it was given."""
+    from emberserve_b200.engine.runner import ScratchArena
+
+    arena = ScratchArena(torch.device("cpu"), guard=8)
+    a = arena("a", (3, 5), torch.float32)
+    b = arena("b", (7,), torch.bfloat16)
+    a.fill_(1.0)
+    b.fill_(2.0)
+    arena.verify()
+    assert a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+    grown = arena("a", (4, 5), torch.float32)  # a larger request replaces the buffer, guards and all
+    grown.zero_()
+    arena.verify()
+    flat = grown.view(-1)
+    torch.as_strided(flat, (1,), (1,), storage_offset=flat.storage_offset() + flat.numel())[0] = 3.0
+    with pytest.raises(RuntimeError, match="wrote after"):
+        arena.verify()
+    plain_arena = ScratchArena(torch.device("cpu"))
+    plain_arena("x", (4,), torch.float32)
+    plain_arena.verify()  # nothing to check without guards

@@ -57,7 +57,9 @@ def test_real_layer_sizes_under_every_cut(case, dtype):
 
     name, folder, reqs, want = case
     scale = max(float(np.abs(v).max()) for v in want.values())
-    runner = ModelRunner.from_dir(folder, dtype, page_size=16, num_pages=40)
+    # (guard elements around every scratch buffer: a kernel that writes outside its buffer at
+    # these sizes is caught by verify_scratch below)
+    runner = ModelRunner.from_dir(folder, dtype, page_size=16, num_pages=40, scratch_guard=64)
     runner.enable_graphs(1024, 4)
     cuts = {"whole": rc.whole(reqs), "tail": rc.bulk_then_tail(reqs, 32), "portions": rc.portions(reqs),
             "mixed": rc.mixed(reqs, max_live=3, seed=5, decode_tail=16)}
@@ -71,6 +73,7 @@ def test_real_layer_sizes_under_every_cut(case, dtype):
                     for rid, toks in reqs for p in range(len(toks)))
         assert worst <= TOL[dtype] * scale, f"{name} {cut} {dtype}: {worst:.3e} vs scale {scale:.3f}"
         runner.cache.check()
+        runner.verify_scratch()
 
 
 @pytest.mark.parametrize("name", ["qwen2.5-0.5b", "qwen2.5-7b"])
@@ -94,7 +97,7 @@ def test_long_prompt_through_the_tcgen05_attention(name, tmp_path):
     want_short = plain.forward_logits(cfgd, w, short_toks, torch.float32).double().numpy()
     scale = float(np.abs(want_long).max())
     probe = [0, 127, 128, 399, 400, 401, 402, 699]
-    runner = ModelRunner.from_dir(folder, torch.bfloat16, page_size=16, num_pages=64)
+    runner = ModelRunner.from_dir(folder, torch.bfloat16, page_size=16, num_pages=64, scratch_guard=64)
     cuts = {
         "whole": [[("L", 0, 700, probe)]],
         "portions": [[("L", 0, 400, [p for p in probe if p < 400])],
@@ -120,3 +123,4 @@ def test_long_prompt_through_the_tcgen05_attention(name, tmp_path):
         torch.cuda.synchronize()
         K.check_status()
         runner.cache.check()
+        runner.verify_scratch()
