@@ -21,6 +21,8 @@ follow ``emberserve/engine.py``: ``from_pretrained`` (``:383-426``), ``add_reque
 
 from __future__ import annotations
 
+import dataclasses
+import json
 import os
 import time
 from dataclasses import dataclass, field
@@ -86,6 +88,10 @@ class LLMEngine:
         self.stats: list[StepStats] = []
         self._inflight: _InFlight | None = None
         self._final_text: dict[str, str] = {}  # text of the requests that ended last, until asked for
+        # EMBERSERVE_STEP_TRACE=path: a line of step statistics per step is appended to that file
+        # (the reference's switch of the same name, emberserve/steptrace.py:94-101)
+        trace_path = os.environ.get("EMBERSERVE_STEP_TRACE")
+        self._trace_file = open(trace_path, "a") if trace_path else None
         self._penalties_seen = False
         self._token_host: list[torch.Tensor | None] = [None, None]
         self._token_turn = 0
@@ -266,13 +272,20 @@ class LLMEngine:
         return outputs
 
     def _record(self, so: SchedulerOutput, forward_ms: float, sample_ms: float) -> None:
+        if not self.keep_stats and self._trace_file is None:
+            return
+        st = StepStats(
+            step=self._step_count, is_prefill=so.is_prefill, num_seqs=len(so.scheduled),
+            num_tokens=so.num_tokens, num_preempted=len(so.preempted),
+            forward_ms=forward_ms, sample_ms=sample_ms,
+            num_free_pages=self.runner.cache.num_free_pages(0) if self.runner.cache.pools else 0,
+            num_prefill_tokens=so.num_prefill_tokens, num_decode_tokens=so.num_decode_tokens)
         if self.keep_stats:
-            self.stats.append(StepStats(
-                step=self._step_count, is_prefill=so.is_prefill, num_seqs=len(so.scheduled),
-                num_tokens=so.num_tokens, num_preempted=len(so.preempted),
-                forward_ms=forward_ms, sample_ms=sample_ms,
-                num_free_pages=self.runner.cache.num_free_pages(0) if self.runner.cache.pools else 0,
-                num_prefill_tokens=so.num_prefill_tokens, num_decode_tokens=so.num_decode_tokens))
+            self.stats.append(st)
+        if self._trace_file is not None:  # one JSON line per step (emberserve/steptrace.py:48-76)
+            self._trace_file.write(json.dumps(dict(dataclasses.asdict(st), t=time.time(),
+                                                   async_scheduling=self.config.async_scheduling)) + "\n")
+            self._trace_file.flush()
 
     def _launch(self, so: SchedulerOutput) -> _InFlight:
         """Run the step and sample on the device; nothing here waits for the device.  The

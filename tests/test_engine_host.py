@@ -380,3 +380,19 @@ def test_scratch_guards_catch_a_write_outside_a_buffer():
     plain_arena = ScratchArena(torch.device("cpu"))
     plain_arena("x", (4,), torch.float32)
     plain_arena.verify()  # nothing to check without guards
+
+
+def test_step_trace_file(model_dirs, tmp_path, monkeypatch):
+    """EMBERSERVE_STEP_TRACE=path: one JSON line of step statistics per step."""
+    import json
+
+    path = tmp_path / "steps.jsonl"
+    monkeypatch.setenv("EMBERSERVE_STEP_TRACE", str(path))
+    name = "tiny_a"
+    llm = make_llm(model_dirs[name], name, max_num_batched_tokens=8)
+    llm.generate(prompts_for(name, [11, 3]), SamplingParams.greedy(4, ignore_eos=True))
+    lines = [json.loads(x) for x in path.read_text().splitlines()]
+    assert len(lines) >= 4 and [x["step"] for x in lines] == sorted(x["step"] for x in lines)
+    assert sum(x["num_prefill_tokens"] for x in lines) == 14
+    assert sum(x["num_decode_tokens"] for x in lines) == 6
+    assert all(x["num_tokens"] <= 8 for x in lines)
