@@ -38,6 +38,9 @@ def _add_engine_args(p: argparse.ArgumentParser) -> None:
                    default=True, help="mix decode tokens and prompt portions in every step (default)")
     p.add_argument("--no-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
     p.add_argument("--no-cuda-graphs", dest="enable_cuda_graphs", action="store_false", default=True)
+    p.add_argument("--attn-backend", choices=["auto", "mma", "generic"], default="auto",
+                   help="attention kernels of the bfloat16 path: the fastest that takes the case, the mma.sync "
+                        "kernels only, or the 32-bit CUDA-core kernel everywhere")
     p.add_argument("--debug-scratch-guard", type=int, default=0, metavar="N",
                    help="debugging: N guard elements around every scratch buffer, checked after each step")
     p.add_argument("--no-async-scheduling", dest="async_scheduling", action="store_false", default=True,
@@ -57,7 +60,7 @@ def engine_config_from_args(args: argparse.Namespace):
                         enable_chunked_prefill=args.enable_chunked_prefill,
                         enable_cuda_graphs=args.enable_cuda_graphs,
                         async_scheduling=args.async_scheduling,
-                        debug_scratch_guard=args.debug_scratch_guard)
+                        debug_scratch_guard=args.debug_scratch_guard, attn_backend=args.attn_backend)
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -51,6 +51,11 @@ class EngineConfig:
     # token history on the host (a repetition penalty) switch the engine to plain stepping.
     async_scheduling: bool = True
     seed: int = 0
+    # Which attention kernels the bfloat16 path may use (the reference's `attn_backend` chooses
+    # among its implementations in the same way, emberserve/config.py:258-312): "auto" the
+    # fastest that takes the case, "mma" the mma.sync kernels only (no tcgen05 prompt kernel),
+    # "generic" the 32-bit CUDA-core kernel everywhere (the one the float32 path always uses).
+    attn_backend: str = "auto"
     # A debugging aid: scratch buffers of the steps get this many guard elements on either side
     # and the engine checks after every step that no kernel wrote there (it waits for the device
     # to do so, so steps no longer overlap).
@@ -62,6 +67,8 @@ class EngineConfig:
             self.dtype = dtype_from_str(self.dtype)
         if self.dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"unsupported dtype {self.dtype}; choose float32 or bfloat16")
+        if self.attn_backend not in ("auto", "mma", "generic"):
+            raise ValueError(f"attn_backend {self.attn_backend!r}: choose auto, mma or generic")
         if self.block_size <= 0:
             raise ValueError("block_size must be positive")
         if self.max_num_seqs <= 0 or self.max_num_batched_tokens <= 0 or self.max_model_len <= 1:

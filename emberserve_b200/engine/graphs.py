@@ -122,7 +122,8 @@ class DecodeGraphs:
             tokens=view("tokens", bucket), positions=view("positions", bucket),
             row_of_token=view("row_of", bucket), cu_q=view("cu", bucket + 1), starts=view("starts", bucket),
             q_lens=[1] * bucket, start_list=[0] * bucket, max_q_len=1, max_ctx_len=self.max_ctx_len,
-            scratch=arena, extra={"decode_splits": decode_splits(bucket, kv_heads, self.max_ctx_len)},
+            scratch=arena, extra={"decode_splits": decode_splits(bucket, kv_heads, self.max_ctx_len),
+                                    "attn_kernel": r.attn_kernel},
             deferred=r.token_feedback)
         bts = [view(f"bt{k}", bucket * self.width).view(bucket, self.width) for k in range(self.npaged)]
         handles = [None if call.cache is None else r.storage.handle(call.cache, call.write, bts, None)

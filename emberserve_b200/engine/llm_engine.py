@@ -95,6 +95,7 @@ class LLMEngine:
         self._penalties_seen = False
         self._token_host: list[torch.Tensor | None] = [None, None]
         self._token_turn = 0
+        runner.attn_kernel = config.attn_backend
         if config.enable_cuda_graphs:
             runner.enable_graphs(config.max_model_len, config.max_num_seqs)
             if config.eager_graph_capture and runner.graphs is not None:

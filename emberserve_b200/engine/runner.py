@@ -152,6 +152,7 @@ class ModelRunner:
         self.storage = CacheStorage(self.groups, [num_pages + 1] * len(paged), page_size,
                                     num_state_slots if has_state else 0, dtype, self.device)
         self.scratch = ScratchArena(self.device, guard=scratch_guard)
+        self.attn_kernel = "auto"  # "auto", "mma" or "generic": handed to the mixers with every step
         self._meta_dev = torch.empty(1 << 12, dtype=torch.int32, device=self.device)
         self._meta_host = [torch.empty(1 << 12, dtype=torch.int32, pin_memory=self._on_cuda)
                            for _ in range(2)]
@@ -305,7 +306,7 @@ class ModelRunner:
             tokens=dev(0), positions=dev(1), row_of_token=dev(2), cu_q=dev(3), starts=dev(4),
             q_lens=q_lens, start_list=starts, max_q_len=max(q_lens),
             max_ctx_len=max(s + q for s, q in zip(starts, q_lens)), scratch=self.scratch,
-            deferred=self.token_feedback)
+            deferred=self.token_feedback, extra={"attn_kernel": self.attn_kernel})
         bt = [dev(7 + k).view(b, tables[k].shape[1]) for k in range(npaged)]
         return ctx, bt, dev(6), dev(5), num_want
 

@@ -103,7 +103,8 @@ class GQAttention(Mixer):
             if r is not None:
                 table, rot = r
         b = ctx.num_rows
-        if (ctx.all_decode and n == b and x.is_cuda
+        kern = ctx.extra.get("attn_kernel", "auto")  # the engine's choice of attention kernels
+        if (kern != "generic" and ctx.all_decode and n == b and x.is_cuda
                 and K.decode_attention_fused_supported(ctx.dtype, s.num_heads, s.num_kv_heads, s.head_dim, rot)):
             # a decode step in bfloat16: rotation, cache write and attention in one kernel
             out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
@@ -136,11 +137,11 @@ class GQAttention(Mixer):
                 scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)
             K.paged_attention(qkv, out, cache.k, cache.v, cache.block_tables[:nd], ctx.cu_q[:nd + 1],
                               ctx.starts[:nd], nd, nd, s.num_heads, s.num_kv_heads, s.head_dim,
-                              self.scale, 1, window=cache.window, splits=splits, scratch=scratch)
+                              self.scale, 1, window=cache.window, splits=splits, scratch=scratch, kernel=kern)
         if nd < b:
             K.paged_attention(qkv, out, cache.k, cache.v, cache.block_tables[nd:], ctx.cu_q[nd:],
                               ctx.starts[nd:], b - nd, n, s.num_heads, s.num_kv_heads, s.head_dim,
-                              self.scale, max(ctx.q_lens[nd:]), window=cache.window)
+                              self.scale, max(ctx.q_lens[nd:]), window=cache.window, kernel=kern)
         y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
         linear(out, self.wo, None, y, ctx.scratch)
         return y

@@ -88,7 +88,7 @@ def attention_scratch_bytes(num_tokens, num_heads, head_dim, splits):
 
 def paged_attention(q, out, kcache, vcache, block_tables, cu_q, starts, num_rows, num_tokens,
                     num_heads, num_kv_heads, head_dim, scale, max_q_len, window=None, splits=1,
-                    scratch=None, generic=False, compute_dtype=torch.float32):
+                    scratch=None, generic=False, tcgen05=False, kernel="auto", compute_dtype=torch.float32):
     """Per request: gather its keys and values from the pages, dense masked softmax."""
     page_size = kcache.shape[2]
     groups = num_heads // num_kv_heads

@@ -163,6 +163,37 @@ def test_no_kernel_writes_outside_its_scratch_buffers(sharp_dirs, name, dtype):
         llm.engine.runner.verify_scratch()
 
 
+@pytest.mark.parametrize("backend", ["auto", "mma", "generic"])
+def test_attention_backend_of_the_engine(sharp_dirs, backend, monkeypatch):
+    """EngineConfig.attn_backend reaches the kernels (every attention launch of the engine names
+    it; the fused decode kernel is not used with "generic") and the logits stay those of the
+    plain implementation."""
+    from emberserve_b200 import SamplingParams
+    from emberserve_b200 import kernels as K
+
+    name = "tiny_d"
+    cfg, w = plain.read_model_dir(sharp_dirs[name])
+    seen, fused = [], []
+    real_paged, real_fused = K.paged_attention, K.decode_attention_fused
+    monkeypatch.setattr(K, "paged_attention", lambda *a, **kw: (seen.append(kw.get("kernel")), real_paged(*a, **kw))[1])
+    monkeypatch.setattr(K, "decode_attention_fused", lambda *a, **kw: (fused.append(1), real_fused(*a, **kw))[1])
+    llm = _llm(sharp_dirs[name], name, "bfloat16", attn_backend=backend, enable_cuda_graphs=False)
+    g = torch.Generator().manual_seed(31)
+    prompt = torch.randint(0, ALL[name].vocab_size, (40,), generator=g).tolist()
+    res = llm.generate([prompt], SamplingParams.greedy(5, ignore_eos=True))[0]
+    assert len(res.output_token_ids) == 5
+    assert seen and set(seen) == {backend}
+    assert bool(fused) == (backend != "generic")
+    eng = llm.engine
+    eng.add_request("logits", prompt, SamplingParams.greedy(1))
+    logits = eng.step_logits(eng.scheduler.schedule(), all_positions=True).double().cpu()
+    eng.abort_request("logits")
+    ref = plain.forward_logits(cfg, w, prompt)
+    assert float((logits - ref).abs().max()) <= 3e-2 * float(ref.abs().max())
+    with pytest.raises(ValueError, match="attn_backend"):
+        _llm(sharp_dirs[name], name, "bfloat16", attn_backend="flash")
+
+
 def test_released_graphs_change_no_token(sharp_dirs):
     """release_graphs() lets go of the captured decode graphs; the engine then launches its kernels
     one by one and generates the same tokens (also with a step still in flight at the release)."""
