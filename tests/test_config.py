@@ -96,3 +96,24 @@ def test_engine_config():
     with pytest.raises(ValueError):
         EngineConfig(block_size=0)
     assert EngineConfig(dtype="float32").dtype == dtype_from_str("fp32")
+    assert EngineConfig().attn_backend == "auto" and EngineConfig(attn_backend="generic").attn_backend == "generic"
+    with pytest.raises(ValueError, match="attn_backend"):
+        EngineConfig(attn_backend="paged_flash")
+    assert EngineConfig().debug_scratch_guard == 0
+
+
+def test_command_line_options_map_to_the_engine_configuration():
+    """The reference's option names (emberserve/cli.py:12-66) with this engine's choices."""
+    from emberserve_b200.cli import build_parser, engine_config_from_args
+
+    args = build_parser().parse_args(["generate", "--model", "m", "--prompt-ids", "1,2", "--dtype", "float32",
+                                      "--block-size", "32", "--num-blocks", "77", "--max-num-seqs", "9",
+                                      "--max-model-len", "512", "--attn-backend", "mma", "--no-cuda-graphs",
+                                      "--no-async-scheduling", "--debug-scratch-guard", "16", "--no-chunked-prefill"])
+    cfg = engine_config_from_args(args)
+    assert (cfg.block_size, cfg.num_gpu_blocks, cfg.max_num_seqs, cfg.max_model_len) == (32, 77, 9, 512)
+    assert cfg.attn_backend == "mma" and not cfg.enable_cuda_graphs and not cfg.async_scheduling
+    assert cfg.debug_scratch_guard == 16 and not cfg.enable_chunked_prefill
+    assert cfg.max_num_batched_tokens == 8192  # 2048 with chunked prefill, as in the reference
+    chunked = engine_config_from_args(build_parser().parse_args(["generate", "--model", "m", "--prompt", "x", "--chat"]))
+    assert chunked.enable_chunked_prefill and chunked.max_num_batched_tokens == 2048 and chunked.attn_backend == "auto"
