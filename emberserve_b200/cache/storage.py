@@ -52,10 +52,18 @@ class CacheStorage:
     def paged_group_of(self, entry: int) -> int:
         return self.where[entry][2]
 
-    def zero_slots(self, slots: list[int]) -> None:
-        if not slots:
-            return
-        idx = torch.tensor(slots, dtype=torch.long, device=self.device)
+    def zero_slots(self, slots: "list[int] | torch.Tensor") -> None:
+        """Zero the state of the given slots in every state group.  `slots` may be an int32
+        tensor on the device (the way a step brings them; a slot may appear more than once), so
+        that the fill is an ordinary launch of the step, also inside a CUDA graph."""
+        if isinstance(slots, torch.Tensor):
+            if slots.numel() == 0:
+                return
+            idx = slots.long()
+        else:
+            if not slots:
+                return
+            idx = torch.tensor(slots, dtype=torch.long, device=self.device)
         for g, t in zip(self.groups, self.tensors):
             if not g.paged:
                 t.index_fill_(1, idx, 0)

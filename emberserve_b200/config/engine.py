@@ -9,7 +9,7 @@ derive from free memory), ``gpu_memory_utilization`` (0.90), ``max_num_seqs`` (2
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 
@@ -50,6 +50,7 @@ class EngineConfig:
     # outputs of the step before the one it launched.  Requests whose sampling needs their
     # token history on the host (a repetition penalty) switch the engine to plain stepping.
     async_scheduling: bool = True
+    # Moves the seeds that requests without a seed of their own are given (sampling/sampler.py).
     seed: int = 0
     # Which attention kernels the bfloat16 path may use (the reference's `attn_backend` chooses
     # among its implementations in the same way, emberserve/config.py:258-312): "auto" the
@@ -60,7 +61,6 @@ class EngineConfig:
     # and the engine checks after every step that no kernel wrote there (it waits for the device
     # to do so, so steps no longer overlap).
     debug_scratch_guard: int = 0
-    extra: dict = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         if isinstance(self.dtype, str):

@@ -300,15 +300,6 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nh, int nkv, i
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// dst[i] = float(src[i])   (logits of the bfloat16 path to 32 bits)
-
-template <typename T>
-__global__ void to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dst[i] = to_f32<T>(src[i]);
-}
-
 }  // namespace ems
 
 using namespace ems;
@@ -435,18 +426,6 @@ EMS_EXPORT int ems_rope_kv_write(void* qkv, int dtype, int N, int nh, int nkv, i
         rope_kv_write_kernel<bf16><<<grid, threads, 0, stream>>>(
             (bf16*)qkv, nh, nkv, D, positions, row_of_token, table, rotary_dim, (bf16*)kcache,
             (bf16*)vcache, block_tables, bt_stride, page_size, write_kv);
-    else
-        return EMS_ERR_DTYPE;
-    return launch_status();
-}
-
-EMS_EXPORT int ems_to_f32(const void* src, int dtype, float* dst, long long n, cudaStream_t stream) {
-    if (n <= 0) return EMS_OK;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == EMS_BF16)
-        to_f32_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)src, dst, (size_t)n);
-    else if (dtype == EMS_F32)
-        to_f32_kernel<float><<<blocks, 256, 0, stream>>>((const float*)src, dst, (size_t)n);
     else
         return EMS_ERR_DTYPE;
     return launch_status();

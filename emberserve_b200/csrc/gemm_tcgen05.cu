@@ -404,6 +404,13 @@ EMS_EXPORT int ems_gemm_smallm_status(void) {
     return s ? *s : -1;
 }
 
+// Set the word back to 0 once the host has acted on a code (no kernel of the library may be
+// in flight: the caller has synchronised).
+EMS_EXPORT void ems_tc_status_clear(void) {
+    int* s = status_word();
+    if (s) *s = 0;
+}
+
 // y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias).
 // m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit >= 1 blocks share K: with
 // scratch == null and ksplit <= 8 they form a cluster and reduce on chip; with a

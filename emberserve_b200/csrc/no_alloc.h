@@ -26,6 +26,17 @@
 //    address of the array is taken with cudaGetSymbolAddress (in host code the array's name
 //    is only a stand-in, not a device address) and kept.  Make that first call before any
 //    stream capture.  If taking the address fails the call returns EMS_ERR_LAUNCH (3).
+//    With CUDA's lazy module loading the array itself may only come to exist on a device when
+//    this part of the library is first used there: a caller whose pool takes all free memory
+//    makes the first call on each device BEFORE the pool does, or that call fails with
+//    EMS_ERR_LAUNCH.  The address is kept for the life of the process and is stale after a
+//    cudaDeviceReset: do not reset a device on which this entry point has been called.
+//  * In bfloat16 with head sizes 64 / 128 the kernel is launched as a programmatic dependent
+//    of the kernel before it in the stream: it requests every cached key and value tile
+//    except each row's newest 16-key tile before it waits for that kernel.  A preceding kernel
+//    that signals early (cudaTriggerProgrammaticLaunchCompletion, griddepcontrol.launch_dependents)
+//    may therefore write only each row's newest key and value; one that writes older cache
+//    positions must not signal early (an ordinary kernel never does).
 //  * All calls on a device share the one array, and it keeps what the last call left in
 //    it.  Nothing in it has to start at zero: every partial result that the merge step
 //    reads is written earlier in the same call.  Two calls that may run at the same time on

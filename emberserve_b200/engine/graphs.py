@@ -8,9 +8,13 @@ hundred kernels per step, which is what a decode step at small batch is made of.
 
 Rows that pad a bucket are ordinary rows of a one-token request at position 0 whose block
 table points at a scratch page that the cache manager never hands out, so no kernel needs
-to know about padding.  The split of keys over blocks is fixed per bucket from the
-largest context a graph serves; a block whose share of the keys is empty writes an empty
-partial result, as in the eager path.
+to know about padding (a mixer with state of its own sees a scratch slot for them).  The
+split of keys over blocks is fixed per bucket and layer from the largest context a graph
+serves; a block whose share of the keys is empty writes an empty partial result, as in the
+eager path.
+
+All buckets share ONE arena of scratch buffers: they never run at the same time, so the
+buffers are as large as the largest request any bucket makes of them, not the sum.
 
 (The reference does the same with one graph per batch-size bucket and a scratch block,
 ``emberserve/attn/cuda_graphs.py``; its buckets are over flash-attn / Triton kernels.)
@@ -25,8 +29,7 @@ import numpy as np
 import torch
 
 from emberserve_b200 import kernels as K
-from emberserve_b200.parts.attention import decode_splits
-from emberserve_b200.parts.base import PagedKV, StepContext
+from emberserve_b200.parts.base import StepContext
 
 
 def default_buckets(max_rows: int) -> list[int]:
@@ -67,16 +70,23 @@ class DecodeGraphs:
         self.width = runner.cache.pages_needed(max_ctx_len)
         self.buckets = default_buckets(max_rows)
         self.max_rows = max_rows
-        self._arena_cls = ScratchArena
+        self.arena = ScratchArena(runner.device, guard=runner.scratch.guard)
         self._graphs: dict[int, _Graph] = {}
+        self._statics: dict[int, tuple] = {}
         self._pool = None
         self.npaged = len(runner.cache.pools)
+        self.has_state = runner._has_state
 
     def usable(self, rows) -> bool:
         if len(rows) > self.max_rows:
             return False
+        cache = self.runner.cache
         for r in rows:
             if len(r.tokens) != 1 or r.start + 1 > self.max_ctx_len or len(r.want) > 1:
+                return False
+            # a request that reserved more pages than the widest table a graph reads (it was
+            # admitted for more tokens than max_ctx_len) takes the eager path
+            if any(cache.table_array(r.seq_id, k).size > self.width for k in range(self.npaged)):
                 return False
         return True
 
@@ -88,8 +98,11 @@ class DecodeGraphs:
 
     def _layout(self, bucket: int) -> tuple[dict[str, int], int]:
         offsets, total = {}, 0
-        for name, size in (("tokens", bucket), ("positions", bucket), ("row_of", bucket),
-                           ("cu", bucket + 1), ("starts", bucket), ("want", bucket)):
+        sections = [("tokens", bucket), ("positions", bucket), ("row_of", bucket),
+                    ("cu", bucket + 1), ("starts", bucket), ("want", bucket)]
+        if self.has_state:  # the state slot of each row, and the slots to zero before the step
+            sections += [("slots", bucket), ("fresh", bucket)]
+        for name, size in sections:
             offsets[name] = total
             total += (size + 3) & ~3
         for k in range(self.npaged):
@@ -97,7 +110,12 @@ class DecodeGraphs:
             total += bucket * self.width
         return offsets, total
 
-    def _capture(self, bucket: int) -> _Graph:
+    def _static(self, bucket: int) -> tuple:
+        """The static buffers of a bucket and the context over them, warmed up: two eager
+        passes bring library handles and workspaces to life outside the capture and make the
+        shared scratch buffers as large as this bucket needs them."""
+        if bucket in self._statics:
+            return self._statics[bucket]
         r = self.runner
         dev = r.device
         offsets, total = self._layout(bucket)
@@ -110,32 +128,46 @@ class DecodeGraphs:
             hv[offsets["want"]:offsets["want"] + bucket] = np.arange(bucket)
             for k in range(self.npaged):
                 hv[offsets[f"bt{k}"]:offsets[f"bt{k}"] + bucket * self.width] = r.scratch_page
+            if self.has_state:
+                hv[offsets["slots"]:offsets["slots"] + bucket] = r.scratch_slot
+                hv[offsets["fresh"]:offsets["fresh"] + bucket] = r.scratch_slot
         meta.copy_(host[0])
 
         def view(name: str, size: int) -> torch.Tensor:
             return meta[offsets[name]:offsets[name] + size]
 
-        kv_heads = max((g.need.num_kv_heads for g in r.groups if isinstance(g.need, PagedKV)), default=1)
-        arena = self._arena_cls(dev, guard=r.scratch.guard)
         ctx = StepContext(
             num_tokens=bucket, num_rows=bucket, dtype=r.dtype, device=dev,
             tokens=view("tokens", bucket), positions=view("positions", bucket),
             row_of_token=view("row_of", bucket), cu_q=view("cu", bucket + 1), starts=view("starts", bucket),
             q_lens=[1] * bucket, start_list=[0] * bucket, max_q_len=1, max_ctx_len=self.max_ctx_len,
-            scratch=arena, extra={"decode_splits": decode_splits(bucket, kv_heads, self.max_ctx_len),
-                                    "attn_kernel": r.attn_kernel},
-            deferred=r.token_feedback)
+            scratch=self.arena, extra={"attn_kernel": r.attn_kernel}, deferred=r.token_feedback)
         bts = [view(f"bt{k}", bucket * self.width).view(bucket, self.width) for k in range(self.npaged)]
-        handles = [None if call.cache is None else r.storage.handle(call.cache, call.write, bts, None)
+        slots = view("slots", bucket) if self.has_state else None
+        fresh = view("fresh", bucket) if self.has_state else None
+        handles = [None if call.cache is None else r.storage.handle(call.cache, call.write, bts, slots)
                    for call in r.decoder.spec.order]
         want = view("want", bucket)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):  # library handles and workspaces come to life outside the capture
+        with torch.cuda.stream(side):
             for _ in range(2):
-                r.decoder.forward(ctx, handles, want, bucket)
+                self._forward(ctx, handles, want, bucket, fresh)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
+        self._statics[bucket] = (offsets, meta, host, ctx, bts, handles, want, fresh)
+        return self._statics[bucket]
+
+    def _forward(self, ctx, handles, want, bucket: int, fresh) -> torch.Tensor:
+        r = self.runner
+        if fresh is not None:
+            r.storage.zero_slots(fresh)  # slots handed out since the last step (else the scratch slot)
+        return r.decoder.forward(ctx, handles, want, bucket)
+
+    def _capture(self, bucket: int) -> _Graph:
+        r = self.runner
+        offsets, meta, host, ctx, bts, handles, want, fresh = self._static(bucket)
+        self.arena.frozen = True  # from here on a buffer that grows leaves its old memory to the graphs
         graph = torch.cuda.CUDAGraph()
         before = K.launch_count()
         # cuBLAS keeps one workspace per stream for as long as the process lives.  One that was
@@ -151,7 +183,7 @@ class DecodeGraphs:
         gc.disable()
         try:
             with torch.cuda.graph(graph, pool=self._pool):
-                logits = r.decoder.forward(ctx, handles, want, bucket)
+                logits = self._forward(ctx, handles, want, bucket, fresh)
         finally:
             if gc_was_on:
                 gc.enable()
@@ -159,24 +191,23 @@ class DecodeGraphs:
         if self._pool is None:
             self._pool = graph.pool()
         return _Graph(bucket, graph, meta, host, [None, None], offsets, logits, K.launch_count() - before,
-                      keep=(arena, ctx, handles, bts, want))
+                      keep=(self.arena, ctx, handles, bts, want, fresh))
 
     def capture_all(self) -> int:
         """Capture every bucket now (largest first), so that no step of a served request pays for
         a capture; returns how many graphs were captured (``emberserve/engine.py:322-334`` captures
         at boot as well)."""
-        done = 0
-        for bucket in sorted(self.buckets, reverse=True):
-            if bucket not in self._graphs:
-                self._graphs[bucket] = self._capture(bucket)
-                done += 1
-        return done
+        todo = [b for b in sorted(self.buckets, reverse=True) if b not in self._graphs]
+        for bucket in todo:  # every bucket's warm-up first: the shared buffers reach their final sizes
+            self._static(bucket)
+        for bucket in todo:
+            self._graphs[bucket] = self._capture(bucket)
+        return len(todo)
 
     def verify_scratch(self) -> None:
-        for g in self._graphs.values():
-            g.keep[0].verify()
+        self.arena.verify()
 
-    def run(self, rows) -> torch.Tensor:
+    def run(self, rows, fresh: list[int] = ()) -> torch.Tensor:
         r = self.runner
         n = len(rows)
         bucket = self._bucket(n)
@@ -206,6 +237,15 @@ class DecodeGraphs:
                 bt[i, :t.size] = t
             if n < bucket:
                 bt[n:, 0] = r.scratch_page
+        if self.has_state:
+            hv[o["slots"]:o["slots"] + n] = [r.cache.state_slot(row.seq_id) for row in rows]
+            hv[o["slots"] + n:o["slots"] + bucket] = r.scratch_slot
+            fresh = list(fresh)
+            if len(fresh) > bucket:  # more than the graph's list holds: the rest at once
+                r.storage.zero_slots(fresh[bucket:])
+                fresh = fresh[:bucket]
+            hv[o["fresh"]:o["fresh"] + len(fresh)] = fresh
+            hv[o["fresh"] + len(fresh):o["fresh"] + bucket] = r.scratch_slot
         g.meta_dev.copy_(g.host[turn], non_blocking=True)
         g.events[turn] = K.record_event()
         g.graph.replay()

@@ -21,6 +21,7 @@ follow ``emberserve/engine.py``: ``from_pretrained`` (``:383-426``), ``add_reque
 
 from __future__ import annotations
 
+import contextlib
 import dataclasses
 import json
 import os
@@ -60,6 +61,7 @@ class _InFlight:
     """A launched step whose tokens the host has not read yet."""
 
     requests: list[Request]  # the rows that sample, in order
+    scheduled: list[Request]  # every request that had a row in the step
     places: list[int]  # where in each request's output its placeholder stands
     length_stop: list[bool]  # the token ends the request by count, whatever it is
     host: torch.Tensor | None  # pinned int32 copy of the tokens, valid after `event`
@@ -75,7 +77,7 @@ class LLMEngine:
         self.tokenizer = tokenizer
         self.detokenizer = Detokenizer(tokenizer)
         self.scheduler = Scheduler(config, runner.cache)
-        self.sampler = Sampler(runner.device)
+        self.sampler = Sampler(runner.device, seed=config.seed)
         # every id that ends a request: the configuration's, and the tokenizer's own end-of-sequence
         # id where there is a tokenizer (emberserve/engine.py:220-222)
         eos = set(getattr(self.model_config, "eos_token_ids", ()))
@@ -96,28 +98,48 @@ class LLMEngine:
         self._token_host: list[torch.Tensor | None] = [None, None]
         self._token_turn = 0
         runner.attn_kernel = config.attn_backend
+        if config.max_num_seqs > runner.token_feedback.numel():
+            raise ValueError(f"max_num_seqs={config.max_num_seqs} exceeds the {runner.token_feedback.numel()} "
+                             f"sampled tokens a step may leave on the device for the next one")
         if config.enable_cuda_graphs:
-            runner.enable_graphs(config.max_model_len, config.max_num_seqs)
-            if config.eager_graph_capture and runner.graphs is not None:
-                runner.graphs.capture_all()
+            with self._on_device():
+                runner.enable_graphs(config.max_model_len, config.max_num_seqs)
+                if config.eager_graph_capture and runner.graphs is not None:
+                    runner.graphs.capture_all()
+
+    def _on_device(self):
+        """The runner's GPU made the current device for what the engine launches itself (graph
+        capture, the sampler, events): the kernels launch on the current device's stream."""
+        if self.runner.device.type == "cuda":
+            return torch.cuda.device(self.runner.device)
+        return contextlib.nullcontext()
 
     @classmethod
     def from_pretrained(cls, model_dir: str | os.PathLike, engine_config: EngineConfig | None = None,
                         **overrides) -> "LLMEngine":
-        cfg = engine_config or EngineConfig()
-        for key, value in overrides.items():
-            if not hasattr(cfg, key):
-                raise TypeError(f"EngineConfig has no field {key!r}")
-            setattr(cfg, key, value)
-        cfg.__post_init__()
-        cfg.model_dir = str(model_dir)
+        unknown = [k for k in overrides if k not in {f.name for f in dataclasses.fields(EngineConfig)}]
+        if unknown:
+            raise TypeError(f"EngineConfig has no field {unknown[0]!r}")
+        # a copy with the overrides: the caller's object is left as it is (replace() validates again)
+        cfg = dataclasses.replace(engine_config or EngineConfig(), **overrides, model_dir=str(model_dir))
+        runner = ModelRunner.from_dir(model_dir, cfg.dtype, device=cfg.device, **cls.runner_options(cfg))
+        return cls(runner, cfg, tokenizer=load_tokenizer(model_dir))
+
+    @staticmethod
+    def runner_options(cfg: EngineConfig) -> dict:
+        """What the model runner is built with under `cfg`: the page size and count, and the sizes
+        of the largest steps, for which memory is kept free when the cache is sized from free
+        memory (``emberserve/engine.py:121-139``: without chunked prefill a preempted request
+        comes back with its whole history in one step, up to max_model_len tokens)."""
+        chunk = cfg.max_num_batched_tokens
+        if not cfg.enable_chunked_prefill:
+            chunk = max(chunk, cfg.max_model_len)
         # More pages than max_num_seqs requests of max_model_len tokens can never be used.
         useful = cfg.max_num_seqs * (-(-cfg.max_model_len // cfg.block_size))
-        runner = ModelRunner.from_dir(
-            model_dir, cfg.dtype, device=cfg.device, page_size=cfg.block_size,
-            num_pages=cfg.num_gpu_blocks, max_pages=useful, num_state_slots=cfg.max_num_seqs,
-            gpu_memory_utilization=cfg.gpu_memory_utilization, scratch_guard=cfg.debug_scratch_guard)
-        return cls(runner, cfg, tokenizer=load_tokenizer(model_dir))
+        return dict(page_size=cfg.block_size, num_pages=cfg.num_gpu_blocks, max_pages=useful,
+                    num_state_slots=cfg.max_num_seqs, gpu_memory_utilization=cfg.gpu_memory_utilization,
+                    max_step_tokens=chunk, max_graph_rows=cfg.max_num_seqs if cfg.enable_cuda_graphs else 0,
+                    max_logit_rows=cfg.max_num_seqs, scratch_guard=cfg.debug_scratch_guard)
 
     @classmethod
     def from_runner(cls, runner: ModelRunner, engine_config: EngineConfig | None = None) -> "LLMEngine":
@@ -134,11 +156,12 @@ class LLMEngine:
                 self._final_text.pop(next(iter(self._final_text)))
         self.detokenizer.drop(request_id)
 
-    def output_text(self, request_id: str) -> str:
-        """Text so far of a live request, or the whole text of one that has ended (handed out once;
-        the last FINAL_TEXT_KEEP ended requests are kept; emberserve/engine.py:1102-1107)."""
+    def output_text(self, request_id: str, take: bool = True) -> str:
+        """Text so far of a live request, or the whole text of one that has ended (handed out once
+        unless `take` is false; the last FINAL_TEXT_KEEP ended requests are kept;
+        emberserve/engine.py:1102-1107)."""
         if request_id in self._final_text:
-            return self._final_text.pop(request_id)
+            return self._final_text.pop(request_id) if take else self._final_text[request_id]
         return self.detokenizer.text(request_id)
 
     def release_graphs(self) -> None:
@@ -228,6 +251,14 @@ class LLMEngine:
         self.runner.verify_scratch()  # (does nothing unless the scratch buffers are guarded)
         return self._finalize(before)
 
+    def drain(self):
+        """Run steps until no request is left; yields the final ``RequestOutput`` of each request
+        as it ends (its text is then to be had from ``output_text``)."""
+        while self.has_unfinished_requests():
+            for out in self.step():
+                if out.finished:
+                    yield out
+
     def _history_needed(self) -> bool:
         """Whether some live request samples with its token history (kept on the host)."""
         if not self._penalties_seen:
@@ -264,13 +295,35 @@ class LLMEngine:
         logits = self.runner.step(self.build_rows(so))
         t1 = time.perf_counter()
         sampling = [r for r, done in zip(so.scheduled, so.prefill_complete) if done]
-        tokens = self.sampler.sample(logits, sampling) if sampling else []
+        with self._on_device():
+            tokens = self.sampler.sample(logits, sampling) if sampling else []  # (reading them waits for the step)
         t2 = time.perf_counter()
         for req, qlen in zip(so.scheduled, so.query_lens):
             req.num_computed_tokens += qlen
+        if sampling:
+            self._check_kernels(so.scheduled)
         outputs = self._postprocess(sampling, tokens)
         self._record(so, (t1 - t0) * 1e3, (t2 - t1) * 1e3)
         return outputs
+
+    def _check_kernels(self, scheduled: list[Request]) -> None:
+        """Called once the host has waited for a step: if a bounded wait inside one of the
+        tcgen05 kernels ran out, what the step computed is invalid (its logits, and the keys and
+        values it cached).  No token of it is handed out: the step's requests, and those of a step
+        launched behind it from its tokens, end with ABORT, their pages go back, the status word is
+        cleared and the error is raised."""
+        try:
+            K.check_status()
+        except K.KernelError:
+            behind, self._inflight = self._inflight, None
+            for req in list(scheduled) + (list(behind.scheduled) if behind is not None else []):
+                if not req.is_finished:
+                    req.hold = False
+                    while req.output_token_ids and req.output_token_ids[-1] < 0:
+                        req.output_token_ids.pop()  # placeholders of tokens that never arrive
+                    self.scheduler.finish_request(req, FinishReason.ABORT)
+                    self.detokenizer.drop(req.request_id)
+            raise
 
     def _record(self, so: SchedulerOutput, forward_ms: float, sample_ms: float) -> None:
         if not self.keep_stats and self._trace_file is None:
@@ -300,17 +353,18 @@ class LLMEngine:
         tokens: list[int] = []
         if sampling:
             n = len(sampling)
-            dev_tokens = self.sampler.sample_tensor(logits, sampling, out=self.runner.token_feedback[:n])
-            if dev_tokens.is_cuda:
-                turn = self._token_turn
-                self._token_turn ^= 1
-                if self._token_host[turn] is None or self._token_host[turn].numel() < n:
-                    self._token_host[turn] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
-                host = self._token_host[turn]
-                host[:n].copy_(dev_tokens, non_blocking=True)
-                event = K.record_event()
-            else:
-                tokens = dev_tokens.tolist()
+            with self._on_device():
+                dev_tokens = self.sampler.sample_tensor(logits, sampling, out=self.runner.token_feedback[:n])
+                if dev_tokens.is_cuda:
+                    turn = self._token_turn
+                    self._token_turn ^= 1
+                    if self._token_host[turn] is None or self._token_host[turn].numel() < n:
+                        self._token_host[turn] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+                    host = self._token_host[turn]
+                    host[:n].copy_(dev_tokens, non_blocking=True)
+                    event = K.record_event()
+                else:
+                    tokens = dev_tokens.tolist()
         t2 = time.perf_counter()
         for req, qlen in zip(so.scheduled, so.query_lens):
             req.num_computed_tokens += qlen
@@ -323,7 +377,7 @@ class LLMEngine:
             length_stop.append(by_count)
             req.hold = by_count
         self._record(so, (t1 - t0) * 1e3, (t2 - t1) * 1e3)
-        return _InFlight(sampling, places, length_stop, host, event, tokens)
+        return _InFlight(sampling, list(so.scheduled), places, length_stop, host, event, tokens)
 
     def _finalize(self, inflight: "_InFlight | None") -> list[RequestOutput]:
         """Read the tokens of a launched step and do what follows from them."""
@@ -331,6 +385,8 @@ class LLMEngine:
             return []
         if inflight.event is not None:
             inflight.event.synchronize()
+        self._check_kernels(inflight.scheduled)  # the step has run: did all of its kernels?
+        if inflight.event is not None:
             tokens = inflight.host[:len(inflight.requests)].tolist()
         else:
             tokens = inflight.tokens

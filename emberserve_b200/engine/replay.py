@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import numpy as np
 
+from emberserve_b200 import kernels as K
 from emberserve_b200.engine.runner import ModelRunner, StepRow
 
 
@@ -59,6 +60,7 @@ class TraceReplayer:
         out = None
         if logits is not None and logits.shape[0] > 0:
             out = logits.detach().to("cpu").numpy().astype("<f4", copy=True)
+            K.check_status()  # the copy waited for the step: no logits of a kernel that gave up
         for rid in step.get("end", []):
             rid = str(rid)
             if rid in self._ids:

@@ -29,15 +29,13 @@ from emberserve_b200 import kernels as K
 from emberserve_b200.cache.manager import CacheManager, plan_groups
 from emberserve_b200.cache.storage import CacheStorage
 from emberserve_b200.config.model import ModelConfig
+from emberserve_b200.engine.memory import MemoryPlan, plan_memory
 from emberserve_b200.parts.base import PagedKV, StepContext
 from emberserve_b200.parts.decoder import Decoder
 from emberserve_b200.parts.linear import strict_matmul_precision
 from emberserve_b200.registry import build_decoder, load_config
 from emberserve_b200.weights.loader import init_random_on_device, load_weights
 
-# Memory kept free for everything that is not the cache when its size is derived from
-# free memory (``emberserve/engine.py:117-138``: workspace, activations, logits).
-_WORKSPACE_BYTES = 1 << 30
 _MIN_PAGES = 64
 # How many tokens of one step may wait on the device for the step after it.
 MAX_DEFERRED_TOKENS = 8192
@@ -67,7 +65,10 @@ class ScratchArena:
         self.guard = guard
         self._bufs: dict[tuple[str, torch.dtype], torch.Tensor] = {}
         self._whole: dict[tuple[str, torch.dtype], torch.Tensor] = {}
-        self.frozen = False  # set while CUDA graphs hold pointers into the buffers
+        # Set while CUDA graphs hold pointers into the buffers: a buffer that has to grow then
+        # leaves its old memory alive (in `_retired`) for the graphs that were captured over it.
+        self.frozen = False
+        self._retired: list[torch.Tensor] = []
 
     def __call__(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         numel = 1
@@ -77,7 +78,7 @@ class ScratchArena:
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < numel:
             if self.frozen and buf is not None:
-                raise RuntimeError(f"scratch buffer {name!r} would move while graphs hold it")
+                self._retired.append(self._whole.get(key, buf))
             if self.guard:
                 # guards of a multiple of 16 bytes keep the buffer as aligned as the allocation
                 g = -(-self.guard * dtype.itemsize // 16) * 16 // dtype.itemsize
@@ -104,7 +105,8 @@ class ScratchArena:
                                        f"(byte {where} of the guard)")
 
     def bytes(self) -> int:
-        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+        return (sum(b.numel() * b.element_size() for b in self._bufs.values())
+                + sum(b.numel() * b.element_size() for b in self._retired))
 
 
 def _align4(n: int) -> int:
@@ -119,8 +121,9 @@ class ModelRunner:
     def __init__(self, config: ModelConfig, decoder: Decoder, dtype: torch.dtype,
                  device: str | torch.device = "cuda:0", page_size: int = 16,
                  num_pages: int | None = None, max_pages: int | None = None,
-                 num_state_slots: int = 256, gpu_memory_utilization: float = 0.90, reserve_bytes: int = _WORKSPACE_BYTES,
-                 scratch_guard: int = 0) -> None:
+                 num_state_slots: int = 256, gpu_memory_utilization: float = 0.90,
+                 reserve_bytes: int | None = None, max_step_tokens: int = 8192, max_graph_rows: int = 256,
+                 max_logit_rows: int = 256, scratch_guard: int = 0) -> None:
         self.device = torch.device(device)
         if self._require_cuda and (self.device.type != "cuda" or not torch.cuda.is_available()):
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path "
@@ -139,18 +142,23 @@ class ModelRunner:
         self.max_positions = decoder.spec.max_positions
         self.groups = plan_groups(decoder.cache_entries())
         paged = [g for g in self.groups if g.paged]
+        has_state = any(not g.paged for g in self.groups)
+        self.memory_plan: MemoryPlan | None = None
         if num_pages is None:
-            num_pages = self._pages_from_free_memory(paged, gpu_memory_utilization, reserve_bytes)
+            num_pages = self._pages_from_free_memory(paged, gpu_memory_utilization, reserve_bytes,
+                                                     max_step_tokens, max_graph_rows, max_logit_rows,
+                                                     num_state_slots if has_state else 0)
             if max_pages is not None:
                 num_pages = max(_MIN_PAGES, min(num_pages, max_pages))
         self.num_pages = num_pages
-        has_state = any(not g.paged for g in self.groups)
         self.cache = CacheManager(self.groups, num_pages, page_size,
                                   num_state_slots if has_state else 0)
-        # One page more than the manager hands out: rows that pad a CUDA-graph bucket write there.
+        # One page (and one state slot) more than the manager hands out: rows that pad a
+        # CUDA-graph bucket write there.
         self.scratch_page = num_pages
+        self.scratch_slot = num_state_slots if has_state else 0
         self.storage = CacheStorage(self.groups, [num_pages + 1] * len(paged), page_size,
-                                    num_state_slots if has_state else 0, dtype, self.device)
+                                    num_state_slots + 1 if has_state else 0, dtype, self.device)
         self.scratch = ScratchArena(self.device, guard=scratch_guard)
         self.attn_kernel = "auto"  # "auto", "mma" or "generic": handed to the mixers with every step
         self._meta_dev = torch.empty(1 << 12, dtype=torch.int32, device=self.device)
@@ -169,11 +177,13 @@ class ModelRunner:
 
     def enable_graphs(self, max_ctx_len: int, max_rows: int) -> bool:
         """Replay pure-decode steps of up to `max_rows` rows and contexts up to `max_ctx_len`
-        from CUDA graphs (captured per row-count bucket at first use).  Models with
-        fixed-size state per request run eagerly."""
+        from CUDA graphs (captured per row-count bucket at first use).  A mixer with state of
+        its own is captured like any other: the slot of each row and the slots to be zeroed
+        travel with the step's integers, so its forward must not read them on the host in a
+        step of single tokens."""
         from emberserve_b200.engine.graphs import DecodeGraphs
 
-        if not self._on_cuda or self._has_state:
+        if not self._on_cuda:
             return False
         self.graphs = DecodeGraphs(self, min(max_ctx_len, self.max_positions), max_rows)
         self.use_graphs = True
@@ -207,15 +217,29 @@ class ModelRunner:
             total += len(g.entries) * 2 * need.num_kv_heads * self.page_size * need.head_dim * esize
         return total
 
-    def _pages_from_free_memory(self, paged, utilization: float, reserve: int) -> int:
-        """``emberserve/engine.py:141-153``: (free * utilization - reserve) // bytes per page."""
+    def _pages_from_free_memory(self, paged, utilization: float, reserve: int | None, max_step_tokens: int,
+                                max_graph_rows: int, max_logit_rows: int, state_slots: int) -> int:
+        """``emberserve/engine.py:141-153``: (free * utilization - reserve) // bytes per page, the
+        reserve being what the steps will allocate AFTER the cache exists (`plan_memory`)."""
         if not paged:
             return _MIN_PAGES
         if not self._on_cuda:
             return 2048  # the reference's fixed page count off the GPU (emberserve/engine.py:194-207)
         free, _ = torch.cuda.mem_get_info(self.device)
-        usable = int(free * utilization) - reserve
-        return max(_MIN_PAGES, usable // self._bytes_per_page(paged))
+        esize = torch.empty((), dtype=self.dtype).element_size()
+        state_bytes = 0
+        for g in self.groups:
+            if not g.paged:
+                per_slot = 4
+                for d in g.need.shape:
+                    per_slot *= d
+                state_bytes += len(g.entries) * (state_slots + 1) * per_slot
+        self.memory_plan = plan_memory(
+            free_bytes=free, utilization=utilization, bytes_per_page=self._bytes_per_page(paged),
+            scratch_bytes_per_token=self.decoder.scratch_bytes_per_token(esize), vocab_size=self.vocab_size,
+            max_step_tokens=max_step_tokens, max_logit_rows=max_logit_rows, graph_rows=max_graph_rows,
+            state_bytes=state_bytes, reserve_override=reserve)
+        return max(_MIN_PAGES, self.memory_plan.num_pages)
 
     # ---- one step ----------------------------------------------------------------------------
     def _check_rows(self, rows: list[StepRow]) -> None:
@@ -246,8 +270,8 @@ class ModelRunner:
                     raise ValueError(f"request {r.seq_id}: wanted place {w} outside its "
                                      f"{len(r.tokens)} tokens")
 
-    def _pack(self, rows: list[StepRow]) -> tuple[StepContext, list[torch.Tensor], torch.Tensor | None,
-                                                  torch.Tensor, int]:
+    def _pack(self, rows: list[StepRow], fresh: list[int] = ()) -> tuple[
+            StepContext, list[torch.Tensor], torch.Tensor | None, torch.Tensor, int, torch.Tensor]:
         b = len(rows)
         q_lens = [len(r.tokens) for r in rows]
         starts = [r.start for r in rows]
@@ -270,7 +294,8 @@ class ModelRunner:
             tables.append(arr)
         slots = np.asarray([max(0, self.cache.state_slot(r.seq_id)) for r in rows], dtype=np.int32)
 
-        sections = [tokens, positions, row_of, cu, np.asarray(starts, dtype=np.int32), want, slots]
+        sections = [tokens, positions, row_of, cu, np.asarray(starts, dtype=np.int32), want, slots,
+                    np.asarray(list(fresh), dtype=np.int32)]
         sections += [t.reshape(-1) for t in tables]
         offsets, total = [], 0
         for s in sections:
@@ -307,8 +332,8 @@ class ModelRunner:
             q_lens=q_lens, start_list=starts, max_q_len=max(q_lens),
             max_ctx_len=max(s + q for s, q in zip(starts, q_lens)), scratch=self.scratch,
             deferred=self.token_feedback, extra={"attn_kernel": self.attn_kernel})
-        bt = [dev(7 + k).view(b, tables[k].shape[1]) for k in range(npaged)]
-        return ctx, bt, dev(6), dev(5), num_want
+        bt = [dev(8 + k).view(b, tables[k].shape[1]) for k in range(npaged)]
+        return ctx, bt, dev(6), dev(5), num_want, dev(7)
 
     def verify_scratch(self) -> None:
         """With guarded scratch buffers (scratch_guard > 0): wait for the device and raise if a
@@ -330,16 +355,18 @@ class ModelRunner:
             return torch.empty(0, self.vocab_size, dtype=torch.float32, device=self.device)
         self._check_rows(rows)
         with (torch.cuda.device(self.device) if self._on_cuda else contextlib.nullcontext()):
+            # state slots handed out since the last step are zeroed on the device before any
+            # mixer reads them; their numbers travel with the step's other integers
+            fresh = self.cache.take_fresh_slots() if self._has_state else []
             if self.use_graphs and self.graphs.usable(rows):
-                logits = self.graphs.run(rows)
+                logits = self.graphs.run(rows, fresh)
                 for r in rows:
                     self.cache.commit(r.seq_id, r.start + 1)
                 self.steps_run += 1
                 return logits
-            fresh = self.cache.take_fresh_slots()
+            ctx, block_tables, slots, want_rows, num_want, fresh_dev = self._pack(rows, fresh)
             if fresh:
-                self.storage.zero_slots(fresh)
-            ctx, block_tables, slots, want_rows, num_want = self._pack(rows)
+                self.storage.zero_slots(fresh_dev)
             handles = [None if call.cache is None else
                        self.storage.handle(call.cache, call.write, block_tables, slots)
                        for call in self.decoder.spec.order]

@@ -61,7 +61,6 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_silu_mul": [P, P, I, I, I, P],
         "ems_rope_table": [P, P, I, I, P],
         "ems_rope_kv_write": [P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, P],
-        "ems_to_f32": [P, I, P, L, P],
         "ems_decode_attention_fused": [P, L, P, P, P, P, I, I, P, P, I, I, I, I, I, F, P, I, I, I, P, L, P],
         "ems_paged_attention": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I, P, L, I, P],
         "ems_argmax": [P, P, I, I, P, P],
@@ -80,12 +79,32 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ems_gemm_large_gated_supported.restype = c_int
     lib.ems_gemm_smallm_status.argtypes = []
     lib.ems_gemm_smallm_status.restype = c_int
+    lib.ems_tc_status_clear.argtypes = []
+    lib.ems_tc_status_clear.restype = None
     lib.ems_gemm_smallm_scratch_bytes.argtypes = [I, I, I]
     lib.ems_gemm_smallm_scratch_bytes.restype = c_longlong
     lib.ems_argmax_slices.argtypes = [I, I]
     lib.ems_argmax_slices.restype = c_int
     lib.ems_paged_attention_scratch_bytes.argtypes = [I, I, I, I]
     lib.ems_paged_attention_scratch_bytes.restype = c_longlong
+
+
+_sm_counts: dict[int, int] = {}
+# What a helper assumes where there is no device to ask (the host-logic tests): a B200.
+B200_SMS = 148
+
+
+def sm_count(device: "torch.device | str | None" = None) -> int:
+    """Streaming multiprocessors of `device` (asked once per device); the grid-shaping helpers
+    (how keys or K are split over blocks) take it from here instead of a constant."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch._C._cuda_getDevice())
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        return B200_SMS
+    idx = dev.index if dev.index is not None else torch._C._cuda_getDevice()
+    n = _sm_counts.get(idx)
+    if n is None:
+        n = _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return n
 
 
 _launches = 0
@@ -226,12 +245,6 @@ def rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
         rotary_dim, _ptr(kcache, "kcache"), _ptr(vcache, "vcache"),
         _i32(block_tables, "block_tables"), bt_stride, page_size, 1 if write_kv else 0, _stream()),
         "rope_kv_write")
-
-
-def to_f32(src: torch.Tensor, dst: torch.Tensor) -> None:
-    assert dst.dtype == torch.float32 and dst.numel() >= src.numel()
-    _check(library().ems_to_f32(_ptr(src, "src"), _dt(src), _ptr(dst, "dst"), src.numel(), _stream()),
-           "to_f32")
 
 
 def attention_scratch_bytes(num_tokens: int, num_heads: int, head_dim: int, splits: int) -> int:
@@ -400,7 +413,20 @@ def gemm_smallm_status() -> int:
     return int(library().ems_gemm_smallm_status())
 
 
-def check_status() -> None:
+def clear_status() -> None:
+    """Set the status word of the tcgen05 kernels back to 0 (after the device has been waited for)."""
+    library().ems_tc_status_clear()
+
+
+def check_status(clear: bool = True) -> None:
+    """Raise if a bounded wait inside a tcgen05 kernel (a GEMM or the prompt attention) ran out
+    since the word was last cleared: what that kernel wrote is invalid, and so is everything
+    computed from it.  The word lives in host-mapped memory, so the check costs no CUDA call; it
+    means something only after a synchronisation point behind the kernels in question.  With
+    `clear` the word is reset, so that the next step starts clean."""
     code = gemm_smallm_status()
     if code != 0:
-        raise KernelError(f"a wait inside a tcgen05 GEMM kernel ran out (code {code}); its results are invalid")
+        if clear:
+            clear_status()
+        raise KernelError(f"a wait inside a tcgen05 kernel ran out (code {code}); the results of the "
+                          f"step are invalid")

@@ -13,6 +13,7 @@ hands the block tables to the kernels (``attn/base.py:79-91`` is the same contra
 
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass
 from typing import Any
 
@@ -24,10 +25,26 @@ from emberserve_b200.parts.base import (Mixer, PagedKV, PagedKVHandle, ParamSpec
 from emberserve_b200.parts.linear import linear
 
 # Blocks wanted in flight before keys are split among several blocks of a decode step:
-# two per SM of a B200.
-_TARGET_BLOCKS = 2 * 148
+# this many per SM of the device.
+_BLOCKS_PER_SM = 2
 _MAX_SPLITS = 64
 _MIN_KEYS_PER_SPLIT = 128
+
+
+_log = logging.getLogger("emberserve_b200")
+_slow_path_told: set[tuple[int, int]] = set()
+
+
+def _tell_slow_path_once(head_dim: int, group: int) -> None:
+    """One line, once per geometry, when bfloat16 attention cannot run on the tensor-core
+    kernels (head sizes 64 and 128; at most 16 query heads per KV head in decode steps) and
+    takes the 32-bit CUDA-core kernel instead: right, but several times slower."""
+    key = (head_dim, group)
+    if key not in _slow_path_told:
+        _slow_path_told.add(key)
+        _log.warning("bfloat16 attention with head_dim=%d and %d query heads per KV head runs on the generic "
+                     "CUDA-core kernel: the tensor-core kernels take head sizes 64 and 128 (and up to 16 heads "
+                     "per KV head when decoding)", head_dim, group)
 
 
 @dataclass(frozen=True)
@@ -48,11 +65,13 @@ class AttentionSpec:
     kind: str = "gqa_attention"
 
 
-def decode_splits(num_rows: int, num_kv_heads: int, max_ctx: int) -> int:
+def decode_splits(num_rows: int, num_kv_heads: int, max_ctx: int, sms: int | None = None) -> int:
     """How many blocks share the keys of one (request, KV head) in a decode step.  A
-    function of shapes only (``emberserve/attn/paged_triton.py:259-281`` has the same idea)."""
+    function of shapes and of the device's SM count `sms` only
+    (``emberserve/attn/paged_triton.py:259-281`` has the same idea)."""
     blocks = max(1, num_rows * num_kv_heads)
-    want = _TARGET_BLOCKS // blocks  # rounded down: all blocks of the step run in one wave
+    target = _BLOCKS_PER_SM * (sms if sms is not None else K.sm_count())
+    want = target // blocks  # rounded down: all blocks of the step run in one wave
     cap = max(1, max_ctx // _MIN_KEYS_PER_SPLIT)
     return max(1, min(_MAX_SPLITS, want, cap))
 
@@ -92,6 +111,10 @@ class GQAttention(Mixer):
                                       init="bias")
         return specs
 
+    def scratch_elements_per_token(self) -> int:
+        # qkv, attn_out, mixer_out
+        return self.q_size + 2 * self.kv_size + self.q_size + self.spec.hidden
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVHandle) -> torch.Tensor:
         s: AttentionSpec = self.spec
         n = ctx.num_tokens
@@ -104,11 +127,16 @@ class GQAttention(Mixer):
                 table, rot = r
         b = ctx.num_rows
         kern = ctx.extra.get("attn_kernel", "auto")  # the engine's choice of attention kernels
+        if (ctx.dtype == torch.bfloat16 and kern != "generic"
+                and (s.head_dim not in (64, 128) or s.num_heads // s.num_kv_heads > 16)):
+            _tell_slow_path_once(s.head_dim, s.num_heads // s.num_kv_heads)
         if (kern != "generic" and ctx.all_decode and n == b and x.is_cuda
                 and K.decode_attention_fused_supported(ctx.dtype, s.num_heads, s.num_kv_heads, s.head_dim, rot)):
             # a decode step in bfloat16: rotation, cache write and attention in one kernel
             out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
-            splits = ctx.extra.get("decode_splits") or decode_splits(b, s.num_kv_heads, ctx.max_ctx_len)
+            # (in a captured step ctx.max_ctx_len is the longest context its graph serves, so
+            # the split is fixed per bucket and per layer)
+            splits = decode_splits(b, s.num_kv_heads, ctx.max_ctx_len, K.sm_count(ctx.device))
             scratch = None
             if splits > 1:
                 nbytes = K.attention_scratch_bytes(b, s.num_heads, s.head_dim, splits)
@@ -131,7 +159,7 @@ class GQAttention(Mixer):
         if nd > 0:
             splits, scratch = 1, None
             max_ctx = ctx.max_ctx_len if nd == b else max(st + 1 for st in ctx.start_list[:nd])
-            splits = ctx.extra.get("decode_splits") or decode_splits(nd, s.num_kv_heads, max_ctx)
+            splits = decode_splits(nd, s.num_kv_heads, max_ctx, K.sm_count(ctx.device))
             if splits > 1:
                 nbytes = K.attention_scratch_bytes(nd, s.num_heads, s.head_dim, splits)
                 scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)

@@ -173,13 +173,22 @@ class Part:
     def children(self) -> dict[str, "Part"]:
         return {}
 
+    def scratch_elements_per_token(self) -> int:
+        """Elements of the activation dtype that `forward` asks of ``ctx.scratch`` per token of a
+        step, children not counted.  Only used to keep memory free for the steps when the
+        cache is sized; a part that allocates by other means may leave it at 0 (small
+        allocations are covered by a fixed workspace)."""
+        return 0
+
 
 class Norm(Part):
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor,
                 ctx: StepContext, rows: torch.Tensor | None = None) -> torch.Tensor:
         """residual += delta (32-bit sum); return norm(residual) in the activation dtype.
-        With `rows` (int32 packed token indices) only those rows are normalised and
-        returned, compactly, and the residual is left unchanged."""
+        With `rows` (int32 packed token indices on the device; their count is ``rows.numel()``)
+        only the rows ``residual[rows] + delta[rows]`` are normalised and returned, compactly,
+        and the residual is left unchanged: that is how the decoder calls the final norm, on
+        the rows whose logits are wanted."""
         raise NotImplementedError
 
 

@@ -118,6 +118,18 @@ class Decoder:
                 table[f"{path}.{local}"] = ps
         return table
 
+    def scratch_bytes_per_token(self, esize: int) -> int:
+        """Bytes of step scratch per token of a step, for an activation type of `esize` bytes:
+        the 32-bit residual, and every named buffer once (all blocks share the buffers by name,
+        so the widest of each kind counts: the sum over the kinds of part of their largest
+        request)."""
+        widest: dict[type, int] = {}
+        for _, part in self._walk():
+            n = part.scratch_elements_per_token()
+            if n:
+                widest[type(part)] = max(widest.get(type(part), 0), n)
+        return 4 * self.spec.hidden + esize * sum(widest.values())
+
     def ignorable(self, name: str) -> bool:
         return any(name == pat or name.endswith(pat) for pat in self.spec.ignorable)
 
@@ -157,7 +169,7 @@ class Decoder:
         if num_want == 0:
             # still fold the last delta in?  Nothing reads the residual after the step.
             return logits
-        normed = self.final_norm.forward(delta, residual, ctx, rows=want_rows, num_rows=num_want,
-                                         out_name="final_normed")
+        assert want_rows is not None and want_rows.numel() == num_want
+        normed = self.final_norm.forward(delta, residual, ctx, rows=want_rows)
         linear_f32_out(normed, self.head, logits)
         return logits

@@ -28,9 +28,6 @@ def strict_matmul_precision() -> None:
     torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 
-# Blocks of the small-row kernel that a B200 runs at once: 148 SMs, two blocks each while the
-# token tile is narrow (their shared-memory rings then fit twice), else one.
-_SMS = 148
 _MIN_K_TILES_PER_SPLIT = 8
 # Up to this many rows the hand-written kernel is used; with more, cuBLAS is as fast or faster
 # (measured at the projection shapes of a 7B model).
@@ -41,11 +38,12 @@ _SMALLM_ROWS = 16
 _GATED_ROWS = 64
 
 
-def smallm_ksplit(m_tok: int, n_out: int, k: int) -> int:
+def smallm_ksplit(m_tok: int, n_out: int, k: int, sms: int | None = None) -> int:
     """Over how many blocks (one thread-block cluster, at most 8) the small-row kernel splits
-    K so that the blocks of the product fill the SMs: the smallest split that keeps at least
-    nine tenths of them busy, a function of the shape alone (a result never depends on the
-    batch)."""
+    K so that the blocks of the product fill the `sms` SMs of the device: the smallest split
+    that keeps at least nine tenths of them busy, a function of the shape and the device alone
+    (a result never depends on the batch)."""
+    sms = sms if sms is not None else K.sm_count()
     tiles = -(-n_out // 128)
     k_tiles = -(-k // 64)
     best, best_fill = 1, 0.0
@@ -53,7 +51,7 @@ def smallm_ksplit(m_tok: int, n_out: int, k: int) -> int:
         if split > 1 and k_tiles // split < _MIN_K_TILES_PER_SPLIT:
             break
         blocks = tiles * split
-        fill = blocks / (-(-blocks // _SMS) * _SMS)
+        fill = blocks / (-(-blocks // sms) * sms)
         if fill > best_fill + 1e-9:
             best, best_fill = split, fill
         if fill >= 0.9:
@@ -97,7 +95,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
     if scratch is not None and _use_smallm(x, weight, bias, out):
         m, k = x.shape
         n = weight.shape[0]
-        K.gemm_smallm(x, weight, bias, out, ksplit=smallm_ksplit(m, n, k))
+        K.gemm_smallm(x, weight, bias, out, ksplit=smallm_ksplit(m, n, k, K.sm_count(x.device)))
         return out
     same = weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
     if same and out.dtype == x.dtype:

@@ -41,6 +41,10 @@ class SwiGLU(FeedForward):
             "wdown": ParamSpec((s.hidden, i), [Source(s.down_name + ".weight")]),
         }
 
+    def scratch_elements_per_token(self) -> int:
+        # ffn_act, ffn_out, and gate_up for the steps in which no fused kernel takes the sizes
+        return 3 * self.spec.intermediate + self.spec.hidden
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s: SwiGLUSpec = self.spec
         n = x.shape[0]

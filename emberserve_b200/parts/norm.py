@@ -31,11 +31,13 @@ class RMSNorm(Norm):
         s: RMSNormSpec = self.spec
         return {"weight": ParamSpec((s.dim,), [Source(s.weight_name)], init="ones")}
 
+    def scratch_elements_per_token(self) -> int:
+        return self.spec.dim  # "normed" (the rows before the head are fewer)
+
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
-                rows: torch.Tensor | None = None, num_rows: int | None = None,
-                out_name: str = "normed") -> torch.Tensor:
+                rows: torch.Tensor | None = None) -> torch.Tensor:
         s: RMSNormSpec = self.spec
-        n = residual.shape[0] if rows is None else (rows.numel() if num_rows is None else num_rows)
-        out = ctx.scratch(out_name, (n, s.dim), ctx.dtype)
-        K.add_rmsnorm(delta, residual, self.weight, out, s.eps, rows=rows, num_rows=num_rows)
+        n = residual.shape[0] if rows is None else rows.numel()
+        out = ctx.scratch("normed" if rows is None else "normed_rows", (n, s.dim), ctx.dtype)
+        K.add_rmsnorm(delta, residual, self.weight, out, s.eps, rows=rows)
         return out

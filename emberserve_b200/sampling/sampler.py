@@ -10,7 +10,8 @@ The draw is counter-based: row i uses the uniform number Philox(seed_i, n_i) whe
 how many tokens the request has produced so far.  Its tokens therefore depend on its seed
 and its logits only: not on the batch, not on how its prompt was cut, and they survive a
 preemption.  Requests without a seed get ``0x5EED0000 + k`` for the k-th such request of
-the process (``sampling.py:22-39``).
+the engine (``sampling.py:22-39``), moved by ``EngineConfig.seed * 2**32``: two engines with
+the same seed draw the same tokens for the same requests in the same order.
 """
 
 from __future__ import annotations
@@ -23,29 +24,30 @@ from emberserve_b200 import kernels as K
 from emberserve_b200.engine.request import Request
 
 _UNSEEDED_BASE = 0x5EED_0000
-_unseeded = itertools.count()
 _SEED_KEY = "_sampling_seed"
 
 
-def seed_of(request: Request) -> int:
-    seed = request.metadata.get(_SEED_KEY)
-    if seed is None:
-        seed = request.sampling_params.seed
-        if seed is None:
-            seed = _UNSEEDED_BASE + next(_unseeded)
-        request.metadata[_SEED_KEY] = int(seed)
-    return request.metadata[_SEED_KEY]
-
-
 class Sampler:
-    def __init__(self, device: torch.device | str) -> None:
+    def __init__(self, device: torch.device | str, seed: int = 0) -> None:
         self.device = torch.device(device)
+        self._unseeded_base = _UNSEEDED_BASE + (int(seed) << 32)
+        self._unseeded = itertools.count()
         # the per-row parameters of a step travel in one pinned buffer and one copy (two buffers
         # in turn, each guarded by the event of the copy that last read it)
         self._host: list[torch.Tensor | None] = [None, None]
         self._events: list["torch.cuda.Event | None"] = [None, None]
         self._dev: torch.Tensor | None = None
         self._turn = 0
+
+    def seed_of(self, request: Request) -> int:
+        """The request's own seed, or the next one of the engine's; kept with the request."""
+        seed = request.metadata.get(_SEED_KEY)
+        if seed is None:
+            seed = request.sampling_params.seed
+            if seed is None:
+                seed = self._unseeded_base + next(self._unseeded)
+            request.metadata[_SEED_KEY] = int(seed)
+        return request.metadata[_SEED_KEY]
 
     def _upload(self, sections: list[tuple[torch.dtype, list]]) -> list[torch.Tensor]:
         """Device tensors of the given (dtype, values) lists: one host-to-device copy for all of
@@ -102,7 +104,7 @@ class Sampler:
             sections += [(torch.float32, [p.temperature for p in params]),
                          (torch.int32, [p.top_k for p in params]),
                          (torch.float32, [p.top_p for p in params]),
-                         (torch.int64, [_signed64(seed_of(q)) for q in requests]),
+                         (torch.int64, [_signed64(self.seed_of(q)) for q in requests]),
                          (torch.int64, [q.num_output_tokens for q in requests])]
         dev = self._upload(sections)
         if penalised:

@@ -8,8 +8,10 @@ For Tiny A and Tiny B it draws weights with this package's random-weights mode (
 float32), copies the tensors into the reference's ``Qwen2ForCausalLM`` through its
 ``load_hf_state_dict`` (emberserve/model/weights.py:202-209), runs its
 ``forward_logits_all`` with its naive attention backend (emberserve/attn/naive.py) on one
-sequence, and stores the float32 logits with a checksum of the weights.  The weights are
-copied, never re-drawn: the reference's own random initialisation draws in another order.
+sequence, and stores the float32 logits together with the weights themselves
+(``<name>_weights.safetensors``, float32, a few hundred KB), so that the comparison never
+depends on what a later torch draws from the same seed.  The weights are copied into the
+reference's model, never re-drawn: its own random initialisation draws in another order.
 """
 
 from __future__ import annotations
@@ -30,6 +32,7 @@ from tiny_configs import ALL, SEEDS  # noqa: E402
 
 from emberserve_b200.registry import build_decoder  # noqa: E402
 from emberserve_b200.weights.loader import random_checkpoint  # noqa: E402
+from emberserve_b200.weights.safetensors_io import write_safetensors  # noqa: E402
 
 CASES = {"tiny_a": 17, "tiny_b": 40}  # sequence lengths
 
@@ -77,6 +80,7 @@ def main() -> None:
         with torch.no_grad():
             logits = model.forward_logits_all(torch.tensor(ids, dtype=torch.long), backend, meta)
         np.save(HERE / f"{name}_logits.npy", logits.float().numpy())
+        write_safetensors(HERE / f"{name}_weights.safetensors", tensors)
         meta_out[name] = {"tokens": ids, "weights_sha256": checksum(tensors), "seed": SEEDS[name],
                           "torch": torch.__version__}
         print(name, tuple(logits.shape), float(logits.abs().max()))

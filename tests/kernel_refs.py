@@ -78,10 +78,6 @@ def rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, positions, row_of_toke
     vcache[page, :, slot, :] = v.to(vcache.dtype)
 
 
-def to_f32(src, dst):
-    dst.view(-1)[: src.numel()].copy_(src.reshape(-1).float())
-
-
 def attention_scratch_bytes(num_tokens, num_heads, head_dim, splits):
     return 0 if splits <= 1 else num_tokens * num_heads * splits * (head_dim + 2) * 4
 
@@ -218,11 +214,11 @@ def gemm_smallm_gated(x, weight, out):
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 
-def check_status():
+def check_status(clear=True):
     return None
 
 
-ALL = ["gemm_smallm_scratch_bytes", "gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write", "to_f32",
+ALL = ["gemm_smallm_scratch_bytes", "gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write",
        "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample"]
 
 

@@ -72,7 +72,7 @@ def rope_angles(positions: torch.Tensor, head_dim: int, theta: float) -> torch.T
     emb = cat(freqs, freqs)  (emberserve/model/rope.py:68-82)."""
     exponent = torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim
     inv_freq = 1.0 / (float(theta) ** exponent)
-    freqs = torch.outer(positions.to(torch.float32), inv_freq)
+    freqs = torch.outer(positions.to(torch.float32), inv_freq.to(positions.device))
     return torch.cat((freqs, freqs), dim=-1)
 
 
@@ -101,8 +101,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     kf = k.repeat_interleave(groups, dim=1).transpose(0, 1)  # [H, T, D]
     vf = v.repeat_interleave(groups, dim=1).transpose(0, 1)
     scores = torch.matmul(qf, kf.transpose(-1, -2)) / math.sqrt(d)
-    i = torch.arange(t)[:, None]
-    j = torch.arange(t)[None, :]
+    i = torch.arange(t, device=q.device)[:, None]
+    j = torch.arange(t, device=q.device)[None, :]
     hidden = j > i
     if window is not None:
         hidden = hidden | (j <= i - window)
@@ -151,13 +151,14 @@ def decoder_layer(h: torch.Tensor, w: dict[str, torch.Tensor], i: int, g: dict,
 
 
 def forward_logits(cfg: dict, weights: dict[str, torch.Tensor], token_ids: list[int],
-                   dtype: torch.dtype = torch.float64) -> torch.Tensor:
+                   dtype: torch.dtype = torch.float64, device: str = "cpu") -> torch.Tensor:
     """Logits [T, vocab] of every position of one whole sequence
-    (emberserve/model/qwen2.py:180-187,214-230)."""
+    (emberserve/model/qwen2.py:180-187,214-230).  `device`: where the same plain arithmetic
+    runs (sequences of thousands of tokens need more memory than a host may have)."""
     g = geometry(cfg)
-    w = {k: v.to(dtype) for k, v in weights.items()}
-    ids = torch.tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(len(token_ids))
+    w = {k: v.to(device=device, dtype=dtype) for k, v in weights.items()}
+    ids = torch.tensor(token_ids, dtype=torch.long, device=device)
+    positions = torch.arange(len(token_ids), device=device)
     h = embedding(w["model.embed_tokens.weight"], ids)
     for i in range(g["layers"]):
         h = decoder_layer(h, w, i, g, positions)

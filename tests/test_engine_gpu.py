@@ -21,7 +21,11 @@ from tiny_configs import ALL, PAGE_SIZES, SEEDS
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
-TOL = {torch.float32: 3e-5, torch.bfloat16: 3e-2}
+# Largest |logit difference| allowed, as a fraction of the model's largest |logit|: with the
+# ordinary random weights N(0, 0.02) (bfloat16 measured at 5e-3), and with the "sharp" weights of
+# five times the deviation or scaled q/k projections, whose logits bfloat16 rounding moves more.
+TOL = {torch.float32: 3e-5, torch.bfloat16: 1.5e-2}
+TOL_SHARP = {torch.float32: 3e-5, torch.bfloat16: 3e-2}
 
 
 def _runner(model_dir, dtype, page_size, pages):
@@ -75,7 +79,7 @@ def test_greedy_generation_equals_plain(sharp_dirs, name):
         for i, (x, y) in enumerate(zip(a, b)):
             if x != y:
                 logits = plain.forward_logits(cfg, w, p + b[:i])[-1]
-                assert abs(float(logits[x] - logits[y])) <= 2 * TOL[torch.bfloat16] * float(logits.abs().max())
+                assert abs(float(logits[x] - logits[y])) <= 2 * TOL_SHARP[torch.bfloat16] * float(logits.abs().max())
                 break
 
 
@@ -273,7 +277,7 @@ def test_long_decoding_token_by_token(sharp_dirs, name, dtype):
     outs = {s["step"]: rp.run_step(s) for s in steps}
     got = rc.collect(steps, outs)
     err = max(float(np.abs(got[("r0", p)] - want[p]).max()) for p in range(n))
-    assert err <= TOL[dtype] * float(np.abs(want).max()), err
+    assert err <= TOL_SHARP[dtype] * float(np.abs(want).max()), err
     if name == "tiny_c":
         assert runner.cache.stats().num_free[1] == runner.cache.stats().num_pages[1]
 
@@ -298,7 +302,7 @@ def test_first_tokens_of_a_sequence(sharp_dirs, dtype):
     for rid, toks in reqs + [("w", reqs[2][1])]:
         want = plain.forward_logits(cfgd, w, toks).numpy()
         for p in range(len(toks)):
-            assert np.abs(got[(rid, p)] - want[p]).max() <= TOL[dtype] * np.abs(want).max()
+            assert np.abs(got[(rid, p)] - want[p]).max() <= TOL_SHARP[dtype] * np.abs(want).max()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
@@ -379,7 +383,7 @@ def test_peaked_attention_far_keys_window_edge_page_edge(model_dirs, tmp_path, n
         rp = TraceReplayer(runner)
         got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
         err = max(float(np.abs(got[("r0", p)] - want[p]).max()) for p in range(n))
-        assert err <= TOL[dtype] * float(np.abs(want).max()), (dtype, err)
+        assert err <= TOL_SHARP[dtype] * float(np.abs(want).max()), (dtype, err)
 
 
 def test_stale_page_contents_do_not_leak(sharp_dirs):
@@ -545,17 +549,16 @@ def test_block_part_alone():
 
 # ---- a toy architecture with a mixer that keeps state of its own ----------------------------------
 
-def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
-    """A recurrent toy mixer (s_t = decay * s_{t-1} + x_t W_in ; y_t = s_t W_out) defined
-    HERE is registered as a part, used by a toy architecture registered HERE, written as a
-    random model folder, loaded, and stepped in portions, token by token and beside another
-    request; layers alternate between the toy mixer and attention.  Nothing in the package
-    is edited for it."""
+def _toy_decay_architecture(tmp_path):
+    """Registers a toy architecture whose layers alternate between a recurrent toy mixer with
+    state of its own (s_t = decay * s_{t-1} + x_t W_in ; y_t = s_t W_out) and attention, with a
+    toy norm before the toy mixers and the head; writes a random model folder.  Returns
+    (config, folder, plain float64 restatement)."""
     from emberserve_b200.config.model import ModelConfig
     from emberserve_b200.engine.replay import TraceReplayer
     from emberserve_b200.engine.runner import ModelRunner
     from emberserve_b200.parts.attention import AttentionSpec
-    from emberserve_b200.parts.base import FixedState, Mixer, ParamSpec, Source, register_part
+    from emberserve_b200.parts.base import FixedState, Mixer, Norm, ParamSpec, Source, register_part
     from emberserve_b200.parts.block import PreNormBlockSpec
     from emberserve_b200.parts.decoder import DecoderSpec, LayerCall
     from emberserve_b200.parts.mlp import SwiGLUSpec
@@ -584,6 +587,13 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
 
         def forward(self, x, ctx, cache):
             u = x.float() @ self.w_in.float().t()
+            if ctx.all_decode:
+                # a step of single tokens: nothing is read on the host, so that the step can be
+                # captured in a CUDA graph (rows that pad a graph share a scratch slot)
+                idx = cache.slots.long()
+                s = self.spec.decay * cache.state.index_select(0, idx) + u
+                cache.state.index_copy_(0, idx, s)
+                return (s @ self.w_out.float().t()).to(x.dtype)
             y = torch.empty_like(u)
             slots = cache.slots.tolist()
             n0 = 0
@@ -595,6 +605,40 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                 cache.state[slots[row]] = s
                 n0 += q
             return (y @ self.w_out.float().t()).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class ToyLayerNormSpec:
+        dim: int
+        eps: float
+        name: str
+        kind: str = "toy_layernorm"
+
+    @register_part("norm", "toy_layernorm")
+    class ToyLayerNorm(Norm):
+        """Mean-centred norm with gain and bias, written to the documented Norm interface only
+        (delta, residual, ctx, rows): it stands before the toy mixers and before the head."""
+
+        def param_specs(self):
+            s = self.spec
+            return {"gain": ParamSpec((s.dim,), [Source(s.name + ".weight")], init="ones"),
+                    "bias": ParamSpec((s.dim,), [Source(s.name + ".bias")], init="bias")}
+
+        def forward(self, delta, residual, ctx, rows=None):
+            if rows is None:
+                if delta is not None:
+                    residual += delta.float()
+                r = residual
+            else:
+                r = residual[rows.long()]
+                if delta is not None:
+                    r = r + delta[rows.long()].float()
+            r = r - r.mean(-1, keepdim=True)
+            y = r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + self.spec.eps)
+            return (y * self.gain.float() + self.bias.float()).to(ctx.dtype)
+
+    def plain_layer_norm(h, gain, bias, eps):
+        r = h - h.mean(-1, keepdim=True)
+        return r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + eps) * gain + bias
 
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
@@ -621,11 +665,12 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                                    f"{p}.v", f"{p}.o"))
             layers.append(PreNormBlockSpec(
                 mixer=mixer, feed_forward=SwiGLUSpec(cfg.hidden_size, 64, f"{p}.g", f"{p}.u", f"{p}.d"),
-                mixer_norm=RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n1"),
+                mixer_norm=(ToyLayerNormSpec(cfg.hidden_size, 1e-4, f"{p}.n1") if i % 2 == 0 else
+                            RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n1")),
                 ffn_norm=RMSNormSpec(cfg.hidden_size, 1e-5, f"{p}.n2")))
         return DecoderSpec(vocab_size=cfg.vocab_size, hidden=cfg.hidden_size, embed_name="toy.embed",
                            layers=layers, order=[LayerCall(i, i) for i in range(cfg.num_layers)],
-                           final_norm=RMSNormSpec(cfg.hidden_size, 1e-5, "toy.norm"), head_name=None,
+                           final_norm=ToyLayerNormSpec(cfg.hidden_size, 1e-4, "toy.norm"), head_name=None,
                            max_positions=128)
 
     register_architecture("ToyDecayForCausalLM", ToyConfig, build)
@@ -640,8 +685,8 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         t = len(tokens)
         for i in range(cfg.num_layers):
             p = f"toy.{i}"
-            x = plain.rms_norm(h, w[f"{p}.n1"], 1e-5)
             if i % 2 == 0:
+                x = plain_layer_norm(h, w[f"{p}.n1.weight"], w[f"{p}.n1.bias"], 1e-4)
                 u = x @ w[f"{p}.rec.in.weight"].T
                 s = torch.zeros(cfg.state_size, dtype=torch.float64)
                 ys = []
@@ -650,6 +695,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                     ys.append(s)
                 a = torch.stack(ys) @ w[f"{p}.rec.out.weight"].T
             else:
+                x = plain.rms_norm(h, w[f"{p}.n1"], 1e-5)
                 q = (x @ w[f"{p}.q.weight"].T).view(t, 3, 16)
                 k = (x @ w[f"{p}.k.weight"].T).view(t, 1, 16)
                 v = (x @ w[f"{p}.v.weight"].T).view(t, 1, 16)
@@ -660,8 +706,19 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
             y = plain.rms_norm(h, w[f"{p}.n2"], 1e-5)
             gate, up = y @ w[f"{p}.g.weight"].T, y @ w[f"{p}.u.weight"].T
             h = h + (torch.nn.functional.silu(gate) * up) @ w[f"{p}.d.weight"].T
-        return (plain.rms_norm(h, w["toy.norm"], 1e-5) @ w["toy.embed"].T).numpy()
+        return (plain_layer_norm(h, w["toy.norm.weight"], w["toy.norm.bias"], 1e-4) @ w["toy.embed"].T).numpy()
+    return cfg, folder, plain_toy
 
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A recurrent toy mixer and a toy norm defined HERE are registered as parts, used by a toy
+    architecture registered HERE, written as a random model folder, loaded, and stepped in
+    portions, token by token and beside another request.  Nothing in the package is edited
+    for it."""
+    from emberserve_b200.engine.replay import TraceReplayer
+    from emberserve_b200.engine.runner import ModelRunner
+
+    cfg, folder, plain_toy = _toy_decay_architecture(tmp_path)
     runner = ModelRunner.from_dir(folder, torch.float32, device=DEV, page_size=8, num_pages=24,
                                   num_state_slots=2)
     kinds = [type(g.need).__name__ for g in runner.groups]
@@ -676,6 +733,32 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                 assert np.abs(got[(rid, p)] - want[rid][p]).max() <= 3e-5 * np.abs(want[rid]).max()
         runner.cache.check()
         assert runner.cache.stats().free_state_slots == 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_toy_mixer_with_state_decodes_from_cuda_graphs(tmp_path, dtype):
+    """The same toy architecture with CUDA graphs on: the state slot of each row and the slots
+    to be zeroed reach the captured step through its static integers, padded rows use a scratch
+    slot, and a slot that goes from a finished request to a new one starts from zero."""
+    from emberserve_b200.engine.replay import TraceReplayer
+    from emberserve_b200.engine.runner import ModelRunner
+
+    cfg, folder, plain_toy = _toy_decay_architecture(tmp_path)
+    reqs = rc.make_requests(cfg.vocab_size, [21, 30, 17, 26, 1, 19], seed=5)
+    steps = rc.mixed(reqs, max_live=3, seed=4, decode_tail=12)
+    runner = ModelRunner.from_dir(folder, dtype, device=DEV, page_size=8,
+                                  num_pages=TraceReplayer.pages_for(rc.max_live_tokens(steps), 8), num_state_slots=3)
+    assert runner.enable_graphs(128, 4)
+    rp = TraceReplayer(runner)
+    got = rc.collect(steps, {s["step"]: rp.run_step(s) for s in steps})
+    assert {1, 2, 4} & set(runner.graphs._graphs), "no step went through a graph"
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+    for rid, toks in reqs:
+        want = plain_toy(toks)
+        err = max(float(np.abs(got[(rid, p)] - want[p]).max()) for p in range(len(toks)))
+        assert err <= tol * float(np.abs(want).max()), (rid, err)
+    runner.cache.check()
+    assert runner.cache.stats().free_state_slots == 3
 
 
 # ---- a toy architecture with routed experts, learned positions and a shared cache entry -----------

@@ -3,6 +3,8 @@ restatements: what the scheduler cuts and batches must not change a request's to
 
 from __future__ import annotations
 
+import dataclasses
+
 import pytest
 import torch
 
@@ -179,6 +181,79 @@ def test_request_that_outgrows_the_pool_is_dropped(model_dirs, async_on):
     assert res[1].finish_reason == FinishReason.LENGTH and len(res[1].output_token_ids) == 3
     st = llm.engine.runner.cache.stats()
     assert st.num_free == st.num_pages and st.num_sequences == 0
+
+
+@pytest.mark.parametrize("async_on", [False, True])
+def test_a_step_whose_kernel_gave_up_hands_out_no_token(model_dirs, async_on, monkeypatch):
+    """A bounded wait of a tcgen05 kernel that runs out leaves a code in the status word.  The
+    engine reads the word once it has waited for the step: no token of that step is returned,
+    its requests end with ABORT, their pages go back, the word is cleared and the next
+    requests are served as if nothing had happened.  (The code is set on the host here; no
+    kernel is made to time out.)"""
+    import emberserve_b200.kernels as K
+
+    name = "tiny_a"
+    word = {"code": 0, "cleared": 0}
+
+    def check_status(clear=True):
+        if word["code"]:
+            code, word["code"] = word["code"], 0
+            word["cleared"] += 1
+            raise K.KernelError(f"a wait inside a tcgen05 kernel ran out (code {code})")
+
+    monkeypatch.setattr(K, "check_status", check_status)
+    llm = make_llm(model_dirs[name], name, async_scheduling=async_on)
+    eng = llm.engine
+    prompts = prompts_for(name, [5, 11], seed=3)
+    for i, p in enumerate(prompts):
+        eng.add_request(f"r{i}", p, SamplingParams.greedy(6, ignore_eos=True))
+    seen = []
+    for _ in range(2 + async_on):
+        seen += eng.step()
+    tokens_before = {o.request_id: list(o.output_token_ids) for o in seen}
+    word["code"] = 2
+    with pytest.raises(K.KernelError, match="ran out"):
+        eng.step()
+    assert word["cleared"] == 1
+    assert not eng.has_unfinished_requests()
+    assert eng.step() == []
+    for req_id, toks in tokens_before.items():
+        assert all(t >= 0 for t in toks)
+    eng.runner.cache.check()
+    assert eng.runner.cache.num_free_pages(0) == eng.runner.num_pages
+    # the engine goes on: the same prompts again give the tokens of an undisturbed run
+    again = llm.generate(prompts, SamplingParams.greedy(6, ignore_eos=True))
+    clean = make_llm(model_dirs[name], name, async_scheduling=async_on).generate(
+        prompts, SamplingParams.greedy(6, ignore_eos=True))
+    assert [r.output_token_ids for r in again] == [r.output_token_ids for r in clean]
+    assert all(r.finish_reason == FinishReason.LENGTH for r in again)
+
+
+def test_engine_seed_moves_the_seeds_of_unseeded_requests(model_dirs):
+    name = "tiny_b"
+    prompts = prompts_for(name, [9, 23], seed=5)
+    params = SamplingParams(max_tokens=10, temperature=1.0, ignore_eos=True)  # no seed of its own
+
+    def run(seed):
+        return [r.output_token_ids for r in make_llm(model_dirs[name], name, seed=seed).generate(prompts, params)]
+
+    assert run(0) == run(0) and run(7) == run(7)
+    assert run(0) != run(7)
+
+
+def test_from_pretrained_leaves_the_callers_configuration_alone(model_dirs, monkeypatch):
+    from emberserve_b200.engine.runner import ModelRunner
+
+    monkeypatch.setattr(ModelRunner, "_require_cuda", False)
+    name = "tiny_a"
+    cfg = EngineConfig(device="cpu", dtype=torch.float32, block_size=PAGE_SIZES[name], num_gpu_blocks=32,
+                       max_model_len=64, enable_cuda_graphs=False)
+    before = dataclasses.asdict(cfg)
+    eng = LLMEngine.from_pretrained(model_dirs[name], cfg, max_num_seqs=3, dtype="float32")
+    assert dataclasses.asdict(cfg) == before
+    assert eng.config.max_num_seqs == 3 and eng.config.model_dir == str(model_dirs[name])
+    with pytest.raises(TypeError, match="no field"):
+        LLMEngine.from_pretrained(model_dirs[name], cfg, no_such_knob=1)
 
 
 def test_repetition_penalty_steps_without_lag(model_dirs):

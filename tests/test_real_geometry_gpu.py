@@ -24,7 +24,7 @@ SHAPES = {
     "qwen2.5-32b": (5120, 40, 8, 128, 27648, 1, 1e-5, False),
 }
 LENGTHS = [70, 150, 40, 97]
-TOL = {torch.float32: 3e-5, torch.bfloat16: 3e-2}
+TOL = {torch.float32: 3e-5, torch.bfloat16: 1.5e-2}
 
 
 def config_of(name: str) -> Qwen2Config:

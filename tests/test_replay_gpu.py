@@ -26,7 +26,7 @@ ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"tiny_a": [5, 11, 17, 40, 23, 64, 100], "tiny_b": [1, 9, 23, 40, 70, 33, 130],
            "tiny_c": [3, 48, 90, 61, 35, 77, 200], "tiny_d": [2, 70, 141, 64, 33, 90, 260]}
 # Largest |logit difference| allowed, as a fraction of the largest |logit| of the model.
-TOL = {torch.float32: 3e-5, torch.bfloat16: 3e-2}
+TOL = {torch.float32: 3e-5, torch.bfloat16: 1.5e-2}
 
 
 def _oracle(model_dir, reqs):
@@ -114,16 +114,17 @@ def test_page_size_16_and_engine_default(model_dirs, cases):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(model_dirs, cases, tmp_path, dtype):
+@pytest.mark.parametrize("name,block_size", [("tiny_b", None), ("tiny_a", 4)])
+def test_trace_run_program(model_dirs, cases, tmp_path, dtype, name, block_size):
     """bin/trace_run as a user runs it: steps on standard input, `done <step>` lines and
-    .f32 files back."""
-    name = "tiny_b"
+    .f32 files back; with its own page size of 16, and with Tiny A's pages of 4 tokens."""
     reqs, want, scale = cases[name]
     steps = rc.mixed(reqs, seed=4)
     out_dir = tmp_path / "out"
     proc = subprocess.run(
         [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dirs[name]), "--dtype", dtype,
-         "--out", str(out_dir), "--max-tokens", str(rc.max_live_tokens(steps))],
+         "--out", str(out_dir), "--max-tokens", str(rc.max_live_tokens(steps))]
+        + (["--block-size", str(block_size)] if block_size else []),
         input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
     done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
