@@ -15,6 +15,13 @@ requests) by its time and by the measured copy bandwidth.
 A decode step reads far more than the 126 MB of L2 (14 GB of weights), so consecutive
 timed steps never find their inputs cached: "inputs larger than L2" in ``config``.
 
+The same line carries, under ``points``, every other measurement of the engine: decode and
+prefill of the true 32-bit path, prefill at 128 / 256 / 512 tokens, a mixed step (32 decoding
+rows beside a 512-token prompt portion), the hot kernels alone as fractions of the measured
+peaks, continuous batching of 256 requests at the 0.5B shape and chunked prefill beside decode
+at the 32B shape (the last three models are built in child processes of their own, one after
+the other, once this process has freed the GPU; ``--no-extras`` leaves them out).
+
 ``--impl reference`` runs the unmodified reference from ``baseline/_ref`` through its own
 ``LLMEngine`` for the same metric and shape, or prints why it cannot.
 """
@@ -203,7 +210,7 @@ def run_ours(args) -> dict:
                 "launches": K.launch_count() - launches0,
                 "clocks": clocks.summary() if clocks else None}
 
-    def prefill(iters: int = 3, portions: int = 1) -> dict:
+    def prefill(iters: int = 3, portions: int = 1, ptoks: int = ptoks) -> dict:
         """One prompt of `ptoks` tokens, in one step or in `portions` equal steps."""
         times = []
         part = ptoks // portions
@@ -226,6 +233,36 @@ def run_ours(args) -> dict:
                  + m["head_flops"])
         return {"value": ptoks * 1e3 / ms, "tokens": ptoks, "ms": ms,
                 "frac": flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / ms / 1e9}
+
+    def mixed_step(decoding: int = 32, portion: int = 512, iters: int = 5) -> dict:
+        """One step of `decoding` rows that bring one token each (contexts of CONTEXT tokens)
+        beside the first `portion` tokens of a new prompt."""
+        seqs = list(range(7000, 7000 + decoding))
+        for s in seqs:
+            runner.cache.admit(s, CONTEXT - iters - 2)
+            runner.cache.commit(s, CONTEXT - iters - 2)
+        times = []
+        for it in range(iters + 1):
+            rows = []
+            for s in seqs:
+                at = CONTEXT - iters - 2 + it
+                runner.cache.extend(s, at + 1)
+                rows.append(StepRow(s, rand_tokens(1), at, [0]))
+            runner.cache.admit(7900 + it, portion)
+            rows.append(StepRow(7900 + it, rand_tokens(portion), 0, [portion - 1]))
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            runner.step(rows)
+            ev1.record()
+            torch.cuda.synchronize()
+            runner.cache.release(7900 + it)
+            if it:
+                times.append(ev0.elapsed_time(ev1))
+        for s in seqs:
+            runner.cache.release(s)
+        ms = statistics.mean(times)
+        return {"ms": ms, "tok_s": (decoding + portion) * 1e3 / ms}
 
     def end_to_end(batch: int, steps: int, warmup: int) -> dict:
         """The same decode steps through LLMEngine.step(): schedule, pack, copy in, run,
@@ -290,6 +327,7 @@ def run_ours(args) -> dict:
         if args.kernel_times:
             out["kernels"] = kernel_times(lambda: prefill(1))
         return out
+    used_graphs = bool(runner.use_graphs)
     main = decode(args.batch, args.steps, args.warmup, sample_clocks=True)
     pre = prefill()
     b1 = decode(1, min(args.steps, 32), 3)
@@ -297,6 +335,28 @@ def run_ours(args) -> dict:
     half = decode(args.batch, min(args.steps, 32), 3, context=CONTEXT // 2)
     pre4 = prefill(2, portions=4)
     e2e = end_to_end(args.batch, args.steps, args.warmup)
+    points = {"decode_b1": b1["tok_s"], "decode_b64": b64["tok_s"],
+              f"decode_b{args.batch}_ctx{CONTEXT // 2}": half["tok_s"], "prefill_4x512": pre4["value"],
+              "decode_b1_hbm_frac": b1["gbs"] / peaks["hbm_gbs"],
+              "decode_b64_hbm_frac": b64["gbs"] / peaks["hbm_gbs"]}
+    for t in (128, 256, 512):
+        short = prefill(3, ptoks=t)
+        points[f"prefill_{t}"] = short["value"]
+        # a short prompt step is bound by the weights it reads, not by arithmetic
+        points[f"prefill_{t}_hbm_frac"] = m["weight_bytes"] / short["ms"] / 1e6 / peaks["hbm_gbs"]
+    mixed = mixed_step()
+    points["mixed_32dec_512prefill_tok_s"] = mixed["tok_s"]
+    points["mixed_32dec_512prefill_ms"] = mixed["ms"]
+    if not args.no_extras:
+        # free this model before others are built (the child processes need the memory)
+        runner.graphs = None
+        del runner
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        points.update(kernel_points(args))
+        points.update(extra_points(args))
     return {
         "metric": "decode tok/s at batch 8, context 4096 (Qwen2.5-7B shape)",
         "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -309,18 +369,106 @@ def run_ours(args) -> dict:
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE,
                    "prefill_tokens": PREFILL_TOKENS, "parallelism": "1gpu",
-                   "l2": "inputs larger than L2", "cuda_graphs": bool(runner.use_graphs),
+                   "l2": "inputs larger than L2", "cuda_graphs": used_graphs,
                    "peaks": peaks["source"]},
         "clocks": main["clocks"], "gpu_launches": main["launches"], "e2e": e2e,
         "prefill": pre,
         "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": main["gbs"] / peaks["hbm_gbs"]},
-        "points": {"decode_b1": b1["tok_s"], "decode_b64": b64["tok_s"],
-                   f"decode_b{args.batch}_ctx{CONTEXT // 2}": half["tok_s"], "prefill_4x512": pre4["value"],
-                   "decode_b1_hbm_frac": b1["gbs"] / peaks["hbm_gbs"],
-                   "decode_b64_hbm_frac": b64["gbs"] / peaks["hbm_gbs"]},
+        "points": points,
         "reference_a100_fp16_b8_tok_s": A100_FP16_B8_TOK_S,
     }
+
+
+def kernel_points(args) -> dict:
+    """The kernels that a step's time goes to, each alone at the 7B geometry (`run_kernel`), as
+    fractions of the measured peaks: the four projections at 8 rows, the decode attention at
+    batch 8 and 64, the prompt attention of 2,048 tokens."""
+    import copy
+
+    out = {}
+
+    def one(**kw):
+        a = copy.copy(args)
+        a.model_shape, a.splits, a.start, a.attn_kernel, a.steps = "7b", 0, 0, "auto", 5
+        for key, value in kw.items():
+            setattr(a, key, value)
+        return run_kernel(a)
+
+    for shape in ("qkv", "o", "gate_up", "down"):
+        r = one(kernel="gemm", shape=shape, batch=8)
+        out[f"kernel_{shape}_m8_hbm_frac"] = r["frac_hbm"]
+        out[f"kernel_{shape}_m8_us"] = r["ms"] * 1e3
+    for b in (8, 64):
+        r = one(kernel="decode_attention", batch=b, context=CONTEXT, fused=True)
+        out[f"kernel_decode_attention_b{b}_hbm_frac"] = r["frac_hbm"]
+        out[f"kernel_decode_attention_b{b}_us"] = r["ms"] * 1e3
+    r = one(kernel="prefill_attention", context=PREFILL_TOKENS)
+    out["kernel_prefill_attention_2048_bf16_frac"] = r["frac_bf16"]
+    out["kernel_prefill_attention_2048_us"] = r["ms"] * 1e3
+    return out
+
+
+def extra_points(args) -> dict:
+    """The measurements that need another model: each in a child process of this script (its own
+    CUDA context, freed when it exits), one after the other.  A child that fails leaves a note
+    instead of its numbers; the headline does not depend on them."""
+    out = {}
+
+    def child(*flags, timeout=600):
+        cmd = [sys.executable, str(ROOT / "bench.py"), "--steps", "32", "--warmup", "3", *flags]
+        try:
+            proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+            lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+            if proc.returncode != 0 or not lines:
+                return {"error": (proc.stderr or proc.stdout)[-200:].replace("\n", " ")}
+            return json.loads(lines[-1])
+        except Exception as e:  # a time-out, or output that is no JSON
+            return {"error": f"{type(e).__name__}: {e}"[:200]}
+
+    r = child("--workload", "fp32-7b")
+    if "error" in r:
+        out["fp32_error"] = r["error"]
+    else:
+        out.update({k: v for k, v in r.items() if k.startswith("fp32_")})
+    r = child("--workload", "serve-0.5b")
+    out["serve_0.5b_tok_s" if "value" in r else "serve_0.5b_error"] = r.get("value", r.get("error"))
+    if "value" in r:
+        out["serve_0.5b_requests"] = r["requests"]
+    r = child("--workload", "mixed-32b", timeout=900)
+    out["mixed_32b_tok_s" if "value" in r else "mixed_32b_error"] = r.get("value", r.get("error"))
+    if "value" in r:
+        out["mixed_32b_ms_per_step"] = r["ms_per_step_wall"]
+    return out
+
+
+def run_fp32(args) -> dict:
+    """The true 32-bit path at the 7B shape (float32 weights, cache and activations, SGEMM with
+    TF32 off, CUDA-core attention): decode at batch 1 and 8, and the 2,048-token prefill, with
+    the fractions of the measured copy bandwidth (the prefill as a rate: the denominator that
+    would apply, SGEMM's own peak, is not measured here)."""
+    import copy
+
+    a = copy.copy(args)
+    a.dtype, a.model_shape, a.only, a.kernel_times, a.layers = "float32", "7b", "decode", False, None
+    import gc
+
+    import torch
+
+    out = {}
+    for b in (1, 8):
+        a.batch, a.decode_context = b, CONTEXT
+        r = run_ours(a)
+        out[f"fp32_decode_b{b}"] = r["tok_s"]
+        out[f"fp32_decode_b{b}_hbm_frac"] = r["hbm_frac"]
+        gc.collect()  # (the 30 GB of the model that has just been timed)
+        torch.cuda.empty_cache()
+    a.only, a.prefill_tokens, a.steps = "prefill", PREFILL_TOKENS, 2
+    r = run_ours(a)
+    out["fp32_prefill_2048"] = r["value"]
+    out["fp32_prefill_2048_tflops"] = r["tflops"]
+    out["fp32_prefill_2048_frac_of_bf16_peak"] = r["frac"]
+    return out
 
 
 def run_kernel(args) -> dict:
@@ -700,9 +848,12 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b"], default="decode-7b",
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b"], default="decode-7b",
                     help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests; "
-                         "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape")
+                         "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape; fp32-7b: "
+                         "the true 32-bit path (the headline line runs the last three as child processes)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
     ap.add_argument("--only", choices=["decode", "prefill", "kernel"], default=None,
@@ -757,6 +908,9 @@ def main() -> int:
         return 0
     if args.workload == "mixed-32b":
         print(json.dumps(run_mixed_32b(args)))
+        return 0
+    if args.workload == "fp32-7b":
+        print(json.dumps(run_fp32(args)))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
