@@ -332,6 +332,58 @@ def test_decode_steps_replayed_from_cuda_graphs(model_dirs, name, dtype):
     runner.cache.check()
 
 
+# ---- the cache sized from free memory ---------------------------------------------------------------
+
+def test_cache_from_free_memory_leaves_room_for_the_graphs_and_the_largest_steps():
+    """The 7B shape with 97 % of the free memory in use, 256 sequences and a step budget of 8,192
+    tokens: the cache is sized first, the graphs of all row buckets are captured after it, then the
+    largest prompt portion and the largest decode step run.  A reserve that forgot the graphs'
+    scratch and logits, or the activations of a full portion, runs out of memory here."""
+    import gc
+
+    from emberserve_b200.config.engine import EngineConfig
+    from emberserve_b200.config.model import Qwen2Config
+    from emberserve_b200.engine.llm_engine import LLMEngine
+    from emberserve_b200.engine.runner import ModelRunner, StepRow
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    cfg = Qwen2Config(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                      num_attention_heads=28, num_key_value_heads=4, head_dim=128, max_position_embeddings=32768,
+                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False, attention_bias=True,
+                      eos_token_ids=(151645,))
+    ecfg = EngineConfig(dtype=torch.bfloat16, gpu_memory_utilization=0.97, max_num_seqs=256, max_model_len=32768,
+                        max_num_batched_tokens=8192)
+    runner = ModelRunner.from_random(cfg, seed=0, dtype=torch.bfloat16, device=DEV,
+                                     **LLMEngine.runner_options(ecfg))
+    plan = runner.memory_plan
+    assert plan is not None and runner.num_pages == plan.num_pages > 100_000
+    assert plan.step_scratch == 8192 * runner.decoder.scratch_bytes_per_token(2) and plan.graph_logits == 256 * 152064 * 4
+    assert runner.storage.bytes() == (runner.num_pages + 1) * plan.bytes_per_page
+    free_after_cache = torch.cuda.mem_get_info(DEV)[0]
+    assert free_after_cache >= plan.reserve  # what was kept for the steps is still there
+    engine = LLMEngine.from_runner(runner, ecfg)  # captures the graphs of all 14 buckets
+    assert sorted(runner.graphs._graphs) == [1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256]
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (8192 + 256,), generator=g).tolist()
+    runner.cache.admit(0, 8192)
+    logits = runner.step([StepRow(0, toks[:8192], 0, [8191])])  # the largest prompt portion
+    assert torch.isfinite(logits).all()
+    for s in range(1, 256):
+        runner.cache.admit(s, 1)
+    runner.cache.extend(0, 8193)
+    rows = [StepRow(0, [toks[8192]], 8192, [0])] + [StepRow(s, [toks[8192 + s]], 0, [0]) for s in range(1, 256)]
+    logits = runner.step(rows)  # the largest decode step, from the graph of 256 rows
+    assert logits.shape == (256, cfg.vocab_size) and torch.isfinite(logits).all()
+    torch.cuda.synchronize()
+    # the steps stayed inside what was kept for them (the utilization's own 3 % is never touched)
+    used_by_steps = free_after_cache - torch.cuda.mem_get_info(DEV)[0]
+    assert used_by_steps <= plan.reserve, (used_by_steps, plan.reserve)
+    del engine, runner, logits
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
 # ---- faults that random weights would hide ------------------------------------------------------
 
 def _with_attention_pointing_at(model_dir, out_dir, gain=5.0):
