@@ -608,8 +608,6 @@ def run_kernel(args) -> dict:
         from emberserve_b200.parts.linear import smallm_ksplit
 
         ksplit = args.splits or smallm_ksplit(m, n_out, k)
-        on_chip = ksplit <= 8  # the blocks of a split reduce as a cluster, as in the engine
-        scratch = None if on_chip else torch.empty(K.gemm_smallm_scratch_bytes(m, n_out, ksplit) // 4, device=dev)
         act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
         state = {"i": 0}
 
@@ -617,7 +615,7 @@ def run_kernel(args) -> dict:
             if args.shape == "gate_up":  # as the engine runs it: both halves and SiLU in one kernel
                 K.gemm_smallm_gated(x, ws[state["i"] % copies], act)
             else:
-                K.gemm_smallm(x, ws[state["i"] % copies], None, out, ksplit=ksplit, scratch=scratch)
+                K.gemm_smallm(x, ws[state["i"] % copies], None, out, ksplit=ksplit)
             state["i"] += 1
 
         def cublas():

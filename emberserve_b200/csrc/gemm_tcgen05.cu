@@ -9,9 +9,12 @@
 // tcgen05.mma (kind::f16, bfloat16 inputs, float32 accumulators in tensor memory) on the
 // stages as they land; tcgen05.commit hands each stage back to the TMA producer.  When the
 // block's K range is done the four warps read their 32 accumulator lanes from tensor
-// memory (tcgen05.ld) and store them: as the result, or as a float32 partial when K is
-// split over several blocks so that all SMs stream (a small second kernel adds the
-// partials in a fixed order, adds the bias, and rounds once).
+// memory (tcgen05.ld) and store them.  When K is split over several blocks so that all SMs
+// stream, those blocks are one thread-block cluster: every block PUSHES its float32 partial
+// rows into the shared memory of the block that owns them (st.async, counted by that block's
+// mbarrier), and each owner adds what arrived in rank order, adds the bias and rounds once.
+// A push is one trip through the cluster's network; no block waits at a cluster barrier
+// after its K loop, and none pulls.
 //
 // The reference's engine calls cuBLAS for these products (emberserve/model/qwen2.py:57-58,
 // 77-79,203); this kernel replaces the library where the row count is small.
@@ -31,49 +34,78 @@ namespace ems {
 
 constexpr int G5_BM = 128;      // output features per block (MMA M)
 constexpr int G5_BK = 64;       // K per stage: 64 bf16 = one 128-byte swizzle span
-// Stages of the ring: as many as let two blocks share an SM (the blocks of the next kernel must
-// be able to move in while this one drains, and two rings in flight feed the memory better).
-template <int NT, bool DUAL> constexpr int g5_stages() { return DUAL ? 5 : (NT <= 16 ? 6 : (NT <= 32 ? 5 : 4)); }
+// Stages of the ring: as many as let two blocks share an SM beside the inbox of the split-K
+// reduction (the blocks of the next kernel must be able to move in while this one drains, and two
+// rings in flight feed the memory better).
+#ifndef G5_DUAL_STAGES
+#define G5_DUAL_STAGES 5
+#endif
+template <int NT, int COLS, bool DUAL> constexpr int g5_stages() {
+    return DUAL ? G5_DUAL_STAGES : (NT <= 16 ? (COLS <= 8 ? 6 : 5) : (NT <= 32 ? 4 : 3));
+}
 constexpr int G5_THREADS = 128;
+// Rows of the inbox: `ksplit` senders times the rows a block owns (128 / ksplit, rounded up to 4).
+constexpr int G5_INBOX_ROWS = 128 + 4 * 8;
+template <int COLS, bool DUAL> constexpr int g5_inbox_bytes() { return DUAL ? 0 : G5_INBOX_ROWS * COLS * 4; }
 
 struct Gemm5Params {
-    float* partial;      // [ksplit, M_tok, N_out] float32 (ksplit > 1) or unused
-    void* y;             // [M_tok, N_out] bf16 (ksplit == 1)
-    const bf16* bias;    // [N_out] or null (applied here only when ksplit == 1)
+    void* y;             // [M_tok, N_out] bf16
+    const bf16* bias;    // [N_out] or null
     int* status;         // device-visible status word
-    int m_tok, n_out, k_tiles, ksplit;
-    int cluster_reduce;  // 1: the ksplit blocks of a row tile are a cluster and reduce on chip
+    int m_tok, n_out, k_tiles;
+    int ksplit;          // > 1: the ksplit blocks of a row tile are a cluster and reduce on chip
     int dual_offset;     // DUAL kernels: row distance between the two weight tiles
 };
 
-// NT: token columns of the MMA (16, 32 or 64).
+// 16 bytes into the shared memory of the block with rank `rank` of this cluster, at the address
+// that `addr` has in this block; the store completes 16 bytes on that block's mbarrier `bar`.
+__device__ __forceinline__ void push_f32x4(uint32_t addr, uint32_t bar, uint32_t rank, float a, float b, float c,
+                                           float d) {
+    uint32_t raddr, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar), "r"(rank));
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(raddr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(rbar) : "memory");
+}
+
+template <int N> __device__ __forceinline__ void tc_ld_cols(uint32_t taddr, float (&v)[N]);
+template <> __device__ __forceinline__ void tc_ld_cols<16>(uint32_t taddr, float (&v)[16]) { tc_ld16(taddr, v); }
+
+// NT: token columns of the MMA (16, 32 or 64; with 128 weight rows per MMA, multiples of 16).
+// COLS: how many of them hold tokens, NT or, for up to 8 tokens, 8: then a stage holds only 8
+// activation rows (one 1 KB swizzle atom), the MMA's upper 8 columns read whatever lies behind
+// them in shared memory, and their accumulators are never looked at.  The kilobytes saved buy
+// a sixth stage beside the inbox.
 // DUAL: the block owns TWO weight tiles, rows [tile*128, +128) and the same rows `dual_offset`
 // further down (gate and up projections of a gated feed-forward), accumulates both, and
 // stores silu(first) * second: the activation never goes to memory unfused.
-// Split K (ksplit > 1) in one of two ways: the ksplit blocks of a row tile form a thread-block
-// cluster and add their accumulators through distributed shared memory, in rank order
-// (p.cluster_reduce); or each block writes a float32 partial for a second kernel to add.
-template <int NT, bool DUAL>
+// Split K (ksplit > 1): the ksplit blocks of a row tile form a thread-block cluster and add
+// their accumulators through distributed shared memory, in rank order.
+template <int NT, int COLS, bool DUAL>
 __global__ void __launch_bounds__(G5_THREADS)
 gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            const Gemm5Params p) {
-    constexpr int STAGES = g5_stages<NT, DUAL>();
+    constexpr int STAGES = g5_stages<NT, COLS, DUAL>();
     constexpr uint32_t W_BYTES = G5_BM * G5_BK * 2;               // 16 KB per weight tile
     constexpr uint32_t A_BYTES = (DUAL ? 2 : 1) * W_BYTES;
-    constexpr uint32_t B_BYTES = NT * G5_BK * 2;                  // 2..8 KB
+    constexpr uint32_t B_BYTES = COLS * G5_BK * 2;                // 1..8 KB
     constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * NT;
     constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
+    constexpr uint32_t INBOX_BYTES = g5_inbox_bytes<COLS, DUAL>();
+    constexpr int LD = 16;  // accumulator columns per tensor-memory load
     // instruction descriptor: D float32, A and B bfloat16, both K-major, N = NT, M = 128
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) |
                                ((uint32_t)(G5_BM >> 4) << 24);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    // carve: [A stages][B stages][barriers][tmem pointer]; the base is rounded up to 1024 bytes
+    // carve: [A stages][B stages][inbox][barriers][tmem pointer]; the base is rounded up to 1024 bytes
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t a_s = base, b_s = base + STAGES * A_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * (A_BYTES + B_BYTES));
+    float* inbox = reinterpret_cast<float*>(base_ptr + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * (A_BYTES + B_BYTES) + INBOX_BYTES);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, done_bar = empty0 + 8 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const uint32_t inbox_bar = done_bar + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, ks = blockIdx.y;
@@ -81,10 +113,18 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int per = (p.k_tiles + p.ksplit - 1) / p.ksplit;
     const int kt_begin = ks * per, kt_end = min(p.k_tiles, kt_begin + per);
     const int nk = max(0, kt_end - kt_begin);
+    // split K: rank `me` of the cluster owns output rows [me * owned, +owned) of the tile
+    const bool split = !DUAL && p.ksplit > 1;
+    const int me = split ? (int)cluster_rank() : 0;
+    const int owned = (((G5_BM + p.ksplit - 1) / p.ksplit) + 3) & ~3;
+    const int my_rows = max(0, min(owned, G5_BM - me * owned));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done_bar, 1);
+        mbar_init(inbox_bar, 1);
+        // what the blocks of the cluster (this one included) will push here: COLS floats per owned row each
+        if (split && my_rows > 0) mbar_expect_tx(inbox_bar, (uint32_t)(p.ksplit * my_rows * COLS * 4));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // The weights do not depend on the kernel before this one: the first ring of weight tiles
         // is requested at once, before the block has even set up its tensor memory (this thread
@@ -105,6 +145,9 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // no block pushes into a peer before that peer's inbox barrier exists (the only cluster
+    // barrier of the kernel; it is passed while the blocks still wait for the kernel before)
+    if (split) cluster_sync_all();
     const uint32_t tmem_d = *tmem_slot;
     bool ok = true;
 
@@ -171,94 +214,83 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     if (DUAL) {
         if (have) {
 #pragma unroll
-            for (int c0 = 0; c0 < NT; c0 += 16) {
-                float g[16], u[16];
-                tc_ld16(taddr + c0, g);
-                tc_ld16(taddr + NT + c0, u);
+            for (int c0 = 0; c0 < COLS; c0 += LD) {
+                float g[LD], u[LD];
+                tc_ld_cols<LD>(taddr + c0, g);
+                tc_ld_cols<LD>(taddr + NT + c0, u);
                 if (row < p.n_out) {
                     bf16* y = reinterpret_cast<bf16*>(p.y);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
+                    for (int i = 0; i < LD; ++i)
                         if (c0 + i < p.m_tok)
                             y[(size_t)(c0 + i) * p.n_out + row] =
                                 __float2bfloat16_rn(g[i] / (1.0f + expf(-g[i])) * u[i]);
                 }
             }
         }
-    } else if (p.cluster_reduce) {
-        // every block of the cluster leaves its accumulator in its own shared memory (the
-        // stage ring is idle now); each block then adds up its share of the rows
-        // layout red[column][row]: neighbouring threads write neighbouring words
-        float* red = reinterpret_cast<float*>(base_ptr);
+    } else if (split) {
+        // push: this thread's accumulator row goes to the block that owns it, into the slot of
+        // this block's rank; inbox layout [sender][owned row][token]
+        const uint32_t dst_rank = (uint32_t)(row_local / owned);
+        const uint32_t slot = smem_u32(inbox) + (uint32_t)((me * owned + row_local % owned) * COLS) * 4u;
 #pragma unroll
-        for (int c0 = 0; c0 < NT; c0 += 16) {
-            float v[16];
-            if (have) tc_ld16(taddr + c0, v);
+        for (int c0 = 0; c0 < COLS; c0 += LD) {
+            float v[LD];
+            if (have) tc_ld_cols<LD>(taddr + c0, v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) red[(c0 + i) * G5_BM + row_local] = have ? v[i] : 0.f;
-        }
-        cluster_sync_all();
-        const int me = (int)cluster_rank();
-        // this block adds rows [me * owned, +owned), four neighbouring rows to a thread
-        const int owned = (((G5_BM + p.ksplit - 1) / p.ksplit) + 3) & ~3;
-        const int quads = owned >> 2;
-        bf16* y = reinterpret_cast<bf16*>(p.y);
-        for (int idx = threadIdx.x; idx < quads * p.m_tok; idx += G5_THREADS) {
-            const int n = idx / quads, rl = me * owned + (idx % quads) * 4;
-            const int orow = tile * G5_BM + rl;
-            if (rl >= G5_BM || orow >= p.n_out) continue;
-            const uint32_t addr = a_s + (uint32_t)(n * G5_BM + rl) * 4u;
-            float4 part[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-                part[r] = r < p.ksplit ? ld_cluster_f32x4(addr, (uint32_t)r) : make_float4(0.f, 0.f, 0.f, 0.f);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {  // rank order, the same for every batch
-                acc[0] += part[r].x; acc[1] += part[r].y; acc[2] += part[r].z; acc[3] += part[r].w;
+            for (int i = 0; i < LD && c0 + i < COLS; i += 4) {
+                const bool z = !have;  // a block without K (or whose waits ran out) pushes zeros: nobody waits in vain
+                push_f32x4(slot + (uint32_t)(c0 + i) * 4u, inbox_bar, dst_rank, z ? 0.f : v[i], z ? 0.f : v[i + 1],
+                           z ? 0.f : v[i + 2], z ? 0.f : v[i + 3]);
             }
-            bf16* dst = y + (size_t)n * p.n_out + orow;
+        }
+        // own: add what the ksplit blocks pushed for my rows, in rank order (the same for every batch)
+        if (my_rows > 0) {
+            bool arrived = true;
+            if (lane == 0) arrived = mbar_wait(inbox_bar, 0, p.status, 5);
+            arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
+            if (arrived) mbar_try_wait(inbox_bar, 0);  // (every thread observes the completed phase itself)
+            const int quads = owned >> 2;
+            bf16* y = reinterpret_cast<bf16*>(p.y);
+            for (int idx = threadIdx.x; idx < quads * p.m_tok && arrived; idx += G5_THREADS) {
+                const int n = idx / quads, rl = (idx % quads) * 4;
+                const int orow = tile * G5_BM + me * owned + rl;
+                if (me * owned + rl >= G5_BM || orow >= p.n_out) continue;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int r = 0; r < p.ksplit; ++r) {
+                    const float* src = inbox + (size_t)((r * owned + rl) * COLS + n);
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (orow + e < p.n_out) {
-                    const float b = p.bias ? __bfloat162float(p.bias[orow + e]) : 0.f;
-                    acc[e] += b;
+                    for (int e = 0; e < 4; ++e) acc[e] += src[e * COLS];
                 }
-            if (orow + 3 < p.n_out && ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0)) {
-                uint2 o;
-                __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
-                o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(dst) = o;
-            } else {
+                bf16* dst = y + (size_t)n * p.n_out + orow;
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (orow + e < p.n_out) dst[e] = __float2bfloat16_rn(acc[e]);
-            }
-        }
-        cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
-    } else if (have) {
-#pragma unroll
-        for (int c0 = 0; c0 < NT; c0 += 16) {
-            float v[16];
-            tc_ld16(taddr + c0, v);
-            if (row < p.n_out) {
-                if (p.ksplit == 1) {
-                    const float bias = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
-                    bf16* y = reinterpret_cast<bf16*>(p.y);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (c0 + i < p.m_tok) y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(v[i] + bias);
+                    if (orow + e < p.n_out && p.bias) acc[e] += __bfloat162float(p.bias[orow + e]);
+                if (me * owned + rl + 3 < G5_BM && orow + 3 < p.n_out && ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0)) {
+                    uint2 o;
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
+                    o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst) = o;
                 } else {
-                    float* dst = p.partial + (size_t)ks * p.m_tok * p.n_out;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (c0 + i < p.m_tok) dst[(size_t)(c0 + i) * p.n_out + row] = v[i];
+                    for (int e = 0; e < 4; ++e)
+                        if (me * owned + rl + e < G5_BM && orow + e < p.n_out) dst[e] = __float2bfloat16_rn(acc[e]);
                 }
             }
         }
-    } else if (done && p.ksplit > 1) {  // a split with no K: its partial is zero
-        if (row < p.n_out)
-            for (int n = 0; n < p.m_tok; ++n) p.partial[((size_t)ks * p.m_tok + n) * p.n_out + row] = 0.f;
+    } else if (have) {
+#pragma unroll
+        for (int c0 = 0; c0 < COLS; c0 += LD) {
+            float v[LD];
+            tc_ld_cols<LD>(taddr + c0, v);
+            if (row < p.n_out) {
+                const float bias = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+                bf16* y = reinterpret_cast<bf16*>(p.y);
+#pragma unroll
+                for (int i = 0; i < LD; ++i)
+                    if (c0 + i < p.m_tok) y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(v[i] + bias);
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -266,18 +298,6 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
     }
-}
-
-// out[n, j] = round(sum_s partial[s, n, j] + bias[j]), splits added in index order
-__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ partial, const bf16* __restrict__ bias,
-                                          bf16* __restrict__ y, int ksplit, int m_tok, int n_out) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t total = (size_t)m_tok * n_out;
-    if (idx >= total) return;
-    float acc = 0.f;
-    for (int s = 0; s < ksplit; ++s) acc += partial[(size_t)s * total + idx];
-    if (bias) acc += __bfloat162float(bias[idx % n_out]);
-    y[idx] = __float2bfloat16_rn(acc);
 }
 
 // ---- host side: tensor maps and launch ---------------------------------------------------
@@ -352,35 +372,45 @@ bool tc_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_r
     return tensor_map_2d(ptr, rows, cols, box_rows, out);
 }
 
-template <int NT, bool DUAL>
-static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
-                        cudaStream_t stream) {
-    constexpr int stages = g5_stages<NT, DUAL>();
-    constexpr int smem = stages * ((DUAL ? 2 : 1) * G5_BM * G5_BK * 2 + NT * G5_BK * 2) + (2 * stages + 1) * 8 +
-                         16 + 1024;
-    auto kernel = gemm_smallm_tcgen05_kernel<NT, DUAL>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return EMS_ERR_LAUNCH;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles, p.ksplit);
+template <int NT, int COLS, bool DUAL> constexpr int g5_smem_bytes() {
+    // (the last stage's MMA reads NT activation rows where only COLS were loaded: room for them)
+    return g5_stages<NT, COLS, DUAL>() * ((DUAL ? 2 : 1) * G5_BM * G5_BK * 2 + COLS * G5_BK * 2) +
+           (NT - COLS) * G5_BK * 2 * (DUAL ? 1 : 0) + g5_inbox_bytes<COLS, DUAL>() +
+           (2 * g5_stages<NT, COLS, DUAL>() + 2) * 8 + 16 + 1024;
+}
+
+template <int NT, int COLS, bool DUAL>
+static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int tiles, int ksplit, cudaStream_t stream) {
+    cfg = {};
+    cfg.gridDim = dim3(tiles, ksplit);
     cfg.blockDim = dim3(G5_THREADS);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = g5_smem_bytes<NT, COLS, DUAL>();
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
     int nattr = 0;
     // may start while the kernel before it still runs (see grid_dependency_wait)
     attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[nattr].val.programmaticStreamSerializationAllowed = 1;
     ++nattr;
-    if (p.cluster_reduce) {
+    if (ksplit > 1) {
         attr[nattr].id = cudaLaunchAttributeClusterDimension;
         attr[nattr].val.clusterDim.x = 1;
-        attr[nattr].val.clusterDim.y = p.ksplit;
+        attr[nattr].val.clusterDim.y = ksplit;
         attr[nattr].val.clusterDim.z = 1;
         ++nattr;
     }
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
+}
+
+template <int NT, int COLS, bool DUAL>
+static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
+                        cudaStream_t stream) {
+    auto kernel = gemm_smallm_tcgen05_kernel<NT, COLS, DUAL>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g5_smem_bytes<NT, COLS, DUAL>()) != cudaSuccess)
+        return EMS_ERR_LAUNCH;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    fill_launch<NT, COLS, DUAL>(cfg, attr, tiles, p.ksplit, stream);
     if (cudaLaunchKernelEx(&cfg, kernel, mw, mx, p) != cudaSuccess) {
         cudaGetLastError();
         return EMS_ERR_LAUNCH;
@@ -388,17 +418,14 @@ static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm
     return launch_status();
 }
 
+static inline int nt_for(int m_tok) { return m_tok <= 16 ? 16 : (m_tok <= 32 ? 32 : 64); }
+
 }  // namespace ems
 
 using namespace ems;
 
-// Bytes of float32 scratch for `ksplit` > 1.
-EMS_EXPORT long long ems_gemm_smallm_scratch_bytes(int m_tok, int n_out, int ksplit) {
-    return ksplit > 1 ? (long long)ksplit * m_tok * n_out * 4 : 0;
-}
-
 // 0 while no kernel of this file has recorded a failed wait; else the code of the first one
-// (1 producer, 2 MMA issuer, 3 epilogue, 4 drain).
+// (1 producer, 2 MMA issuer, 3 epilogue, 4 drain, 5 arrival of the split-K partials).
 EMS_EXPORT int ems_gemm_smallm_status(void) {
     int* s = status_word();
     return s ? *s : -1;
@@ -412,39 +439,29 @@ EMS_EXPORT void ems_tc_status_clear(void) {
 }
 
 // y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias).
-// m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit >= 1 blocks share K: with
-// scratch == null and ksplit <= 8 they form a cluster and reduce on chip; with a
-// scratch buffer they leave float32 partials for a second kernel.
+// m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit in 1..8 blocks share K: they
+// form a thread-block cluster and add their accumulators on chip.
 EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
-                               int k, int ksplit, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+                               int k, int ksplit, cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;
-    if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 64) return EMS_ERR_SHAPE;
+    if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 8) return EMS_ERR_SHAPE;  // 8: the portable cluster size
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2)) return EMS_ERR_ALIGN;
-    const bool cluster = ksplit > 1 && scratch == nullptr;
-    if (cluster && ksplit > 8) return EMS_ERR_SHAPE;  // the portable cluster size
-    if (ksplit > 1 && !cluster && scratch_bytes < ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit))
-        return EMS_ERR_SCRATCH;
     int* status = status_word();
     if (!status) return EMS_ERR_LAUNCH;
     int* status_dev = nullptr;
     if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
-    const int nt = m_tok <= 16 ? 16 : (m_tok <= 32 ? 32 : 64);
+    const int nt = nt_for(m_tok);
     CUtensorMap mw, mx;
-    if (!tensor_map_2d(w, n_out, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, nt, &mx)) return EMS_ERR_LAUNCH;
+    if (!tensor_map_2d(w, n_out, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm5Params p;
-    p.partial = reinterpret_cast<float*>(scratch); p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
+    p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
     p.status = status_dev; p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = ksplit;
-    p.cluster_reduce = cluster ? 1 : 0; p.dual_offset = 0;
+    p.dual_offset = 0;
     const int tiles = (n_out + G5_BM - 1) / G5_BM;
-    int rc;
-    if (nt == 16) rc = launch_gemm5<16, false>(mw, mx, p, tiles, stream);
-    else if (nt == 32) rc = launch_gemm5<32, false>(mw, mx, p, tiles, stream);
-    else rc = launch_gemm5<64, false>(mw, mx, p, tiles, stream);
-    if (rc != EMS_OK || ksplit == 1 || cluster) return rc;
-    const size_t total = (size_t)m_tok * n_out;
-    gemm_splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        p.partial, p.bias, reinterpret_cast<bf16*>(y), ksplit, m_tok, n_out);
-    return launch_status();
+    if (m_tok <= 8) return launch_gemm5<16, 8, false>(mw, mx, p, tiles, stream);
+    if (nt == 16) return launch_gemm5<16, 16, false>(mw, mx, p, tiles, stream);
+    if (nt == 32) return launch_gemm5<32, 32, false>(mw, mx, p, tiles, stream);
+    return launch_gemm5<64, 64, false>(mw, mx, p, tiles, stream);
 }
 
 // act[m_tok, inter] (bf16) = silu(x . w[0:inter]^T) * (x . w[inter:2*inter]^T): the gated
@@ -458,14 +475,15 @@ EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, in
     if (!status) return EMS_ERR_LAUNCH;
     int* status_dev = nullptr;
     if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
-    const int nt = m_tok <= 16 ? 16 : (m_tok <= 32 ? 32 : 64);
+    const int nt = nt_for(m_tok);
     CUtensorMap mw, mx;
-    if (!tensor_map_2d(w, 2LL * inter, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, nt, &mx)) return EMS_ERR_LAUNCH;
+    if (!tensor_map_2d(w, 2LL * inter, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm5Params p;
-    p.partial = nullptr; p.y = act; p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
-    p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = 1; p.cluster_reduce = 0; p.dual_offset = inter;
+    p.y = act; p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
+    p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = 1; p.dual_offset = inter;
     const int tiles = (inter + G5_BM - 1) / G5_BM;
-    if (nt == 16) return launch_gemm5<16, true>(mw, mx, p, tiles, stream);
-    if (nt == 32) return launch_gemm5<32, true>(mw, mx, p, tiles, stream);
-    return launch_gemm5<64, true>(mw, mx, p, tiles, stream);
+    if (m_tok <= 8) return launch_gemm5<16, 8, true>(mw, mx, p, tiles, stream);
+    if (nt == 16) return launch_gemm5<16, 16, true>(mw, mx, p, tiles, stream);
+    if (nt == 32) return launch_gemm5<32, 32, true>(mw, mx, p, tiles, stream);
+    return launch_gemm5<64, 64, true>(mw, mx, p, tiles, stream);
 }

@@ -66,7 +66,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_argmax": [P, P, I, I, P, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
-        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, L, P],
+        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P],
         "ems_gemm_smallm_gated": [P, P, P, I, I, I, P],
         "ems_gemm_large_gated": [P, P, P, I, I, I, P],
         "ems_gemm_large": [P, P, P, P, I, I, I, P],
@@ -81,8 +81,6 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ems_gemm_smallm_status.restype = c_int
     lib.ems_tc_status_clear.argtypes = []
     lib.ems_tc_status_clear.restype = None
-    lib.ems_gemm_smallm_scratch_bytes.argtypes = [I, I, I]
-    lib.ems_gemm_smallm_scratch_bytes.restype = c_longlong
     lib.ems_argmax_slices.argtypes = [I, I]
     lib.ems_argmax_slices.restype = c_int
     lib.ems_paged_attention_scratch_bytes.argtypes = [I, I, I, I]
@@ -344,17 +342,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 GEMM_SMALLM_MAX_ROWS = 64
 
 
-def gemm_smallm_scratch_bytes(m_tok: int, n_out: int, ksplit: int) -> int:
-    return int(library().ems_gemm_smallm_scratch_bytes(m_tok, n_out, ksplit))
-
-
 def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
-                ksplit: int = 1, scratch: torch.Tensor | None = None) -> None:
+                ksplit: int = 1) -> None:
     """out[m, n] = x[m, :] . weight[n, :] (+ bias[n]) in bfloat16 with float32 accumulation, for
-    m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks share K: without
-    `scratch` (ksplit up to 8) they form a thread-block cluster and add their accumulators
-    on chip, in rank order; with `scratch` they leave float32 partials there that a second
-    kernel adds in a fixed order."""
+    m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks (up to 8) share K: they
+    form a thread-block cluster and add their accumulators on chip, in rank order."""
     m, k = x.shape
     n = weight.shape[0]
     assert weight.shape[1] == k and out.shape == (m, n)
@@ -362,8 +354,7 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     assert bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == n)
     _check(library().ems_gemm_smallm(
         _ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
-        _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
-        _stream()), "gemm_smallm", 2 if (ksplit > 1 and scratch is not None) else 1)
+        _stream()), "gemm_smallm")
 
 
 def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -408,7 +399,8 @@ def gemm_large(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
 
 def gemm_smallm_status() -> int:
     """0, or the code of the first bounded wait that ran out in the tcgen05 kernel (after a
-    synchronisation point): 1 producer, 2 MMA issuer, 3 epilogue, 4 drain of the small-row kernel;
+    synchronisation point): 1 producer, 2 MMA issuer, 3 epilogue, 4 drain, 5 arrival of the split-K
+    partials of the small-row kernel;
     11 producer, 12 and 13 MMA issuer, 14 epilogue of the two-SM kernel."""
     return int(library().ems_gemm_smallm_status())
 

@@ -196,11 +196,7 @@ def sample(logits, temperature, top_k, top_p, seeds, counters, out):
 GEMM_SMALLM_MAX_ROWS = 64
 
 
-def gemm_smallm_scratch_bytes(m_tok, n_out, ksplit):
-    return ksplit * m_tok * n_out * 4 if ksplit > 1 else 0
-
-
-def gemm_smallm(x, weight, bias, out, ksplit=1, scratch=None):
+def gemm_smallm(x, weight, bias, out, ksplit=1):
     y = x.float() @ weight.float().t()
     if bias is not None:
         y = y + bias.float()
@@ -218,7 +214,7 @@ def check_status(clear=True):
     return None
 
 
-ALL = ["gemm_smallm_scratch_bytes", "gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write",
+ALL = ["gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write",
        "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample"]
 
 
