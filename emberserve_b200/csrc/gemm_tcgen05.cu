@@ -55,7 +55,23 @@ struct Gemm5Params {
     int m_tok, n_out, k_tiles;
     int ksplit;          // > 1: the ksplit blocks of a row tile are a cluster and reduce on chip
     int dual_offset;     // DUAL kernels: row distance between the two weight tiles
+    // The norm that stands BEHIND this product, begun in its epilogue (plain kernels, at most 16
+    // rows): the product is added into the float32 residual stream `res` [m_tok, n_out] instead
+    // of being stored, `scaled` gets bf16(res * gain), and every block leaves the sum of res^2
+    // over its share of the columns, per row, in sumsq_out[(tile * ksplit + rank) * 16 + row].
+    float* res;
+    const bf16* gain;
+    bf16* scaled;
+    float* sumsq_out;
+    // The norm that stands BEFORE this product, finished in its epilogue: the activations it was
+    // given are res * gain of such a producer, and row n of the result is multiplied by
+    // 1 / sqrt(sum_parts sumsq_in[part * 16 + n] * in_inv_width + in_eps) before the bias is added.
+    const float* sumsq_in;
+    int in_parts;
+    float in_inv_width, in_eps;
 };
+
+constexpr int G5_NORM_ROWS = 16;  // rows (tokens) of a step up to which the norms are fused into the products
 
 // 16 bytes into the shared memory of the block with rank `rank` of this cluster, at the address
 // that `addr` has in this block; the store completes 16 bytes on that block's mbarrier `bar`.
@@ -106,6 +122,8 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, done_bar = empty0 + 8 * STAGES;
     const uint32_t inbox_bar = done_bar + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+    float* rstd_s = reinterpret_cast<float*>(bars + 2 * STAGES + 4);  // [16] scale of each row (norm before)
+    float* ssq_s = rstd_s + G5_NORM_ROWS;                             // [16][32] partial sums (norm behind)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, ks = blockIdx.y;
@@ -203,10 +221,23 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     // ---- epilogue: all four warps, 32 accumulator lanes (= output features) each -------
     grid_dependency_wait();  // (the producer has passed it already; this orders the stores below)
     allow_dependent_launch();  // a GEMM that follows may set up and fetch weights as blocks retire
+    if (p.sumsq_in != nullptr && warp >= 2) {
+        // the scale of each row, by the two warps that had nothing to do so far (they get here as
+        // soon as the kernel before has completed): four threads per row add the partial sums
+        // in a fixed pattern
+        const int t = threadIdx.x - 64, n = t >> 2, j = t & 3;
+        float sum = 0.f;
+        for (int part = j; part < p.in_parts; part += 4) sum += p.sumsq_in[(size_t)part * G5_NORM_ROWS + n];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (j == 0) rstd_s[n] = 1.0f / sqrtf(sum * p.in_inv_width + p.in_eps);
+    }
     bool done = true;
     if (lane == 0) done = mbar_wait(done_bar, 0, p.status, 3);
     done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
     tc_fence_after();
+    const bool scale_rows = p.sumsq_in != nullptr;
+    if (scale_rows) __syncthreads();  // rstd_s is written
     const int row_local = warp * 32 + lane;
     const int row = tile * G5_BM + row_local;  // output feature of this thread
     const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
@@ -222,9 +253,11 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     bf16* y = reinterpret_cast<bf16*>(p.y);
 #pragma unroll
                     for (int i = 0; i < LD; ++i)
-                        if (c0 + i < p.m_tok)
-                            y[(size_t)(c0 + i) * p.n_out + row] =
-                                __float2bfloat16_rn(g[i] / (1.0f + expf(-g[i])) * u[i]);
+                        if (c0 + i < p.m_tok) {
+                            const float sc = scale_rows ? rstd_s[c0 + i] : 1.0f;
+                            const float gi = g[i] * sc, ui = u[i] * sc;
+                            y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(gi / (1.0f + expf(-gi)) * ui);
+                        }
                 }
             }
         }
@@ -246,15 +279,30 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
         // own: add what the ksplit blocks pushed for my rows, in rank order (the same for every batch)
         if (my_rows > 0) {
+            // (norm behind) what this thread's first four outputs join, asked for while the pushes travel
+            const bool norm_behind = p.res != nullptr;
+            const int quads = owned >> 2;
+            float4 res_pre = make_float4(0.f, 0.f, 0.f, 0.f);
+            uint2 gain_pre = make_uint2(0u, 0u);
+            bool pre = false;
+            if (norm_behind && (int)threadIdx.x < quads * p.m_tok && (p.n_out & 3) == 0) {
+                const int n = threadIdx.x / quads, rl = (threadIdx.x % quads) * 4;
+                const int orow = tile * G5_BM + me * owned + rl;
+                if (me * owned + rl + 3 < G5_BM && orow + 3 < p.n_out) {
+                    res_pre = *reinterpret_cast<const float4*>(p.res + (size_t)n * p.n_out + orow);
+                    gain_pre = *reinterpret_cast<const uint2*>(p.gain + orow);
+                    pre = true;
+                }
+            }
             bool arrived = true;
             if (lane == 0) arrived = mbar_wait(inbox_bar, 0, p.status, 5);
             arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
             if (arrived) mbar_try_wait(inbox_bar, 0);  // (every thread observes the completed phase itself)
-            const int quads = owned >> 2;
             bf16* y = reinterpret_cast<bf16*>(p.y);
             for (int idx = threadIdx.x; idx < quads * p.m_tok && arrived; idx += G5_THREADS) {
                 const int n = idx / quads, rl = (idx % quads) * 4;
                 const int orow = tile * G5_BM + me * owned + rl;
+                if (norm_behind) ssq_s[n * 32 + idx % quads] = 0.f;
                 if (me * owned + rl >= G5_BM || orow >= p.n_out) continue;
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 for (int r = 0; r < p.ksplit; ++r) {
@@ -262,10 +310,58 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[e] += src[e * COLS];
                 }
-                bf16* dst = y + (size_t)n * p.n_out + orow;
+                const float sc = scale_rows ? rstd_s[n] : 1.0f;
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
+                for (int e = 0; e < 4; ++e) {
+                    acc[e] *= sc;
                     if (orow + e < p.n_out && p.bias) acc[e] += __bfloat162float(p.bias[orow + e]);
+                }
+                if (norm_behind) {
+                    // the product joins the residual stream here; the norm behind it gets its gain
+                    // applied and its statistic begun
+                    const size_t at = (size_t)n * p.n_out + orow;
+                    float r[4], gn[4];
+                    bool valid[4];
+                    if (pre && idx == (int)threadIdx.x) {
+                        r[0] = res_pre.x; r[1] = res_pre.y; r[2] = res_pre.z; r[3] = res_pre.w;
+                        const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gain_pre.x));
+                        const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gain_pre.y));
+                        gn[0] = g01.x; gn[1] = g01.y; gn[2] = g23.x; gn[3] = g23.y;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) valid[e] = true;
+                    } else {  // every load before the first store (the stores may alias them for all the compiler knows)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            valid[e] = me * owned + rl + e < G5_BM && orow + e < p.n_out;
+                            r[e] = valid[e] ? p.res[at + e] : 0.f;
+                            gn[e] = valid[e] ? __bfloat162float(p.gain[orow + e]) : 0.f;
+                        }
+                    }
+                    float ss = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        r[e] += acc[e];
+                        if (valid[e]) ss += r[e] * r[e];
+                    }
+                    if (pre && idx == (int)threadIdx.x) {
+                        *reinterpret_cast<float4*>(p.res + at) = make_float4(r[0], r[1], r[2], r[3]);
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(r[0] * gn[0], r[1] * gn[1]);
+                        const __nv_bfloat162 hi = __floats2bfloat162_rn(r[2] * gn[2], r[3] * gn[3]);
+                        uint2 o;
+                        o.x = *reinterpret_cast<const uint32_t*>(&lo); o.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(p.scaled + at) = o;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (valid[e]) {
+                                p.res[at + e] = r[e];
+                                p.scaled[at + e] = __float2bfloat16_rn(r[e] * gn[e]);
+                            }
+                    }
+                    ssq_s[n * 32 + idx % quads] = ss;
+                    continue;
+                }
+                bf16* dst = y + (size_t)n * p.n_out + orow;
                 if (me * owned + rl + 3 < G5_BM && orow + 3 < p.n_out && ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0)) {
                     uint2 o;
                     __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
@@ -277,18 +373,57 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                         if (me * owned + rl + e < G5_BM && orow + e < p.n_out) dst[e] = __float2bfloat16_rn(acc[e]);
                 }
             }
+            if (norm_behind) {  // this block's share of each row's sum of squares, added in a fixed order
+                __syncthreads();
+                if (threadIdx.x < p.m_tok) {
+                    float sum = 0.f;
+                    for (int q = 0; q < quads; ++q) sum += ssq_s[threadIdx.x * 32 + q];
+                    p.sumsq_out[(size_t)(tile * p.ksplit + me) * G5_NORM_ROWS + threadIdx.x] = arrived ? sum : 0.f;
+                }
+            }
         }
-    } else if (have) {
+    } else {
+        const bool norm_behind = p.res != nullptr;
+        if (have) {
 #pragma unroll
-        for (int c0 = 0; c0 < COLS; c0 += LD) {
-            float v[LD];
-            tc_ld_cols<LD>(taddr + c0, v);
-            if (row < p.n_out) {
-                const float bias = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+            for (int c0 = 0; c0 < COLS; c0 += LD) {
+                float v[LD], r[LD];
+                tc_ld_cols<LD>(taddr + c0, v);
+                const float bias = (row < p.n_out && p.bias) ? __bfloat162float(p.bias[row]) : 0.f;
                 bf16* y = reinterpret_cast<bf16*>(p.y);
+                const float gn = (norm_behind && row < p.n_out) ? __bfloat162float(p.gain[row]) : 0.f;
+                if (norm_behind) {  // every load before the first store
 #pragma unroll
-                for (int i = 0; i < LD; ++i)
-                    if (c0 + i < p.m_tok) y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(v[i] + bias);
+                    for (int i = 0; i < LD; ++i)
+                        r[i] = (c0 + i < p.m_tok && row < p.n_out) ? p.res[(size_t)(c0 + i) * p.n_out + row] : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < LD; ++i) {
+                    if (c0 + i >= p.m_tok) continue;
+                    const float out = v[i] * (scale_rows ? rstd_s[c0 + i] : 1.0f) + bias;
+                    if (!norm_behind) {
+                        if (row < p.n_out) y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(out);
+                        continue;
+                    }
+                    float sq = 0.f;
+                    if (row < p.n_out) {
+                        const size_t at = (size_t)(c0 + i) * p.n_out + row;
+                        const float sum = r[i] + out;
+                        p.res[at] = sum;
+                        p.scaled[at] = __float2bfloat16_rn(sum * gn);
+                        sq = sum * sum;
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0) ssq_s[(c0 + i) * 32 + warp] = sq;
+                }
+            }
+        }
+        if (norm_behind) {  // (p.m_tok <= 16 = COLS or less: one pass of the loop above)
+            __syncthreads();
+            if (threadIdx.x < p.m_tok) {
+                float sum = 0.f;
+                for (int w = 0; w < G5_THREADS / 32; ++w) sum += ssq_s[threadIdx.x * 32 + w];
+                p.sumsq_out[(size_t)tile * G5_NORM_ROWS + threadIdx.x] = have ? sum : 0.f;
             }
         }
     }
@@ -376,7 +511,7 @@ template <int NT, int COLS, bool DUAL> constexpr int g5_smem_bytes() {
     // (the last stage's MMA reads NT activation rows where only COLS were loaded: room for them)
     return g5_stages<NT, COLS, DUAL>() * ((DUAL ? 2 : 1) * G5_BM * G5_BK * 2 + COLS * G5_BK * 2) +
            (NT - COLS) * G5_BK * 2 * (DUAL ? 1 : 0) + g5_inbox_bytes<COLS, DUAL>() +
-           (2 * g5_stages<NT, COLS, DUAL>() + 2) * 8 + 16 + 1024;
+           (2 * g5_stages<NT, COLS, DUAL>() + 2) * 8 + 16 + (G5_NORM_ROWS + G5_NORM_ROWS * 32) * 4 + 1024;
 }
 
 template <int NT, int COLS, bool DUAL>
@@ -406,7 +541,9 @@ template <int NT, int COLS, bool DUAL>
 static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
                         cudaStream_t stream) {
     auto kernel = gemm_smallm_tcgen05_kernel<NT, COLS, DUAL>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g5_smem_bytes<NT, COLS, DUAL>()) != cudaSuccess)
+    // (all of the SM's memory as shared memory: two blocks of the plain kernel then share an SM)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g5_smem_bytes<NT, COLS, DUAL>()) != cudaSuccess ||
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return EMS_ERR_LAUNCH;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
@@ -438,14 +575,32 @@ EMS_EXPORT void ems_tc_status_clear(void) {
     if (s) *s = 0;
 }
 
+// The norm before a product, to be finished in its epilogue (Gemm5Params::sumsq_in); false if the
+// arguments do not make sense.
+static bool fill_norm_before(Gemm5Params& p, const float* sumsq_in, int in_parts, int in_width, float in_eps) {
+    p.sumsq_in = sumsq_in; p.in_parts = in_parts; p.in_eps = in_eps;
+    p.in_inv_width = in_width > 0 ? 1.0f / (float)in_width : 0.f;
+    return sumsq_in == nullptr || (p.m_tok <= G5_NORM_ROWS && in_parts > 0 && in_width > 0);
+}
+
 // y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias).
 // m_tok <= 64; k a multiple of 8; 16-byte aligned pointers.  ksplit in 1..8 blocks share K: they
 // form a thread-block cluster and add their accumulators on chip.
+// With `res` (m_tok <= 16): the product is added into the float32 stream res[m_tok, n_out] instead of
+// being stored in y, scaled[m_tok, n_out] = bf16(res * gain), and sumsq_out[tiles * ksplit, 16] gets
+// every block's share of each row's sum of squares (the norm behind the product).  With `sumsq_in`
+// (m_tok <= 16): row n of the product is multiplied by 1 / sqrt(sum over in_parts of
+// sumsq_in[part, n] / in_width + in_eps) before the bias is added (the norm before it).
 EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
-                               int k, int ksplit, cudaStream_t stream) {
+                               int k, int ksplit, float* res, const void* gain, void* scaled, float* sumsq_out,
+                               const float* sumsq_in, int in_parts, int in_width, float in_eps,
+                               cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;
     if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 8) return EMS_ERR_SHAPE;  // 8: the portable cluster size
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2)) return EMS_ERR_ALIGN;
+    if (res != nullptr && (m_tok > G5_NORM_ROWS || gain == nullptr || scaled == nullptr || sumsq_out == nullptr))
+        return EMS_ERR_SHAPE;
+    if (res == nullptr && y == nullptr) return EMS_ERR_SHAPE;
     int* status = status_word();
     if (!status) return EMS_ERR_LAUNCH;
     int* status_dev = nullptr;
@@ -457,6 +612,9 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
     p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
     p.status = status_dev; p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = ksplit;
     p.dual_offset = 0;
+    p.res = res; p.gain = reinterpret_cast<const bf16*>(gain); p.scaled = reinterpret_cast<bf16*>(scaled);
+    p.sumsq_out = sumsq_out;
+    if (!fill_norm_before(p, sumsq_in, in_parts, in_width, in_eps)) return EMS_ERR_SHAPE;
     const int tiles = (n_out + G5_BM - 1) / G5_BM;
     if (m_tok <= 8) return launch_gemm5<16, 8, false>(mw, mx, p, tiles, stream);
     if (nt == 16) return launch_gemm5<16, 16, false>(mw, mx, p, tiles, stream);
@@ -466,7 +624,9 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
 
 // act[m_tok, inter] (bf16) = silu(x . w[0:inter]^T) * (x . w[inter:2*inter]^T): the gated
 // feed-forward's first two projections and its activation in one kernel.  w: [2*inter, k].
+// `sumsq_in` ...: the norm before the product, as for ems_gemm_smallm (both halves are scaled).
 EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, int m_tok, int inter, int k,
+                                     const float* sumsq_in, int in_parts, int in_width, float in_eps,
                                      cudaStream_t stream) {
     if (m_tok <= 0 || inter <= 0) return EMS_OK;
     if (m_tok > 64 || k <= 0 || k % 8) return EMS_ERR_SHAPE;
@@ -481,6 +641,8 @@ EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, in
     Gemm5Params p;
     p.y = act; p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
     p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = 1; p.dual_offset = inter;
+    p.res = nullptr; p.gain = nullptr; p.scaled = nullptr; p.sumsq_out = nullptr;
+    if (!fill_norm_before(p, sumsq_in, in_parts, in_width, in_eps)) return EMS_ERR_SHAPE;
     const int tiles = (inter + G5_BM - 1) / G5_BM;
     if (m_tok <= 8) return launch_gemm5<16, 8, true>(mw, mx, p, tiles, stream);
     if (nt == 16) return launch_gemm5<16, 16, true>(mw, mx, p, tiles, stream);

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
+from dataclasses import dataclass
 
 import torch
 
@@ -66,8 +67,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_argmax": [P, P, I, I, P, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
-        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P],
-        "ems_gemm_smallm_gated": [P, P, P, I, I, I, P],
+        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, P],
+        "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, P],
         "ems_gemm_large_gated": [P, P, P, I, I, I, P],
         "ems_gemm_large": [P, P, P, P, I, I, I, P],
     }
@@ -342,30 +343,83 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 GEMM_SMALLM_MAX_ROWS = 64
 
 
-def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
-                ksplit: int = 1) -> None:
+# Rows of a step up to which the small-row products can take a norm into their epilogues.
+GEMM_NORM_ROWS = 16
+
+
+@dataclass
+class NormBehind:
+    """The norm that stands behind a small-row product, begun in the product's epilogue: the
+    product is added into `residual` (float32 [m, n], in place) instead of being stored,
+    `scaled` (bfloat16 [m, n]) receives residual * gain, and `sumsq` (float32 [parts, 16],
+    parts = row tiles * ksplit of the product) every block's share of each row's sum of squares."""
+
+    residual: torch.Tensor
+    gain: torch.Tensor
+    scaled: torch.Tensor
+    sumsq: torch.Tensor
+
+
+@dataclass
+class NormBefore:
+    """The norm that stands before a small-row product, finished in its epilogue: the product
+    was given residual * gain, and row n of its result is multiplied by
+    1 / sqrt(sumsq[:parts, n].sum() / width + eps) before the bias is added."""
+
+    sumsq: torch.Tensor
+    parts: int
+    width: int
+    eps: float
+
+
+def _norm_before_args(nb: "NormBefore | None", m: int) -> tuple:
+    if nb is None:
+        return (None, 0, 0, 0.0)
+    assert nb.sumsq.dtype == torch.float32 and nb.sumsq.numel() >= nb.parts * GEMM_NORM_ROWS and m <= GEMM_NORM_ROWS
+    return (_ptr(nb.sumsq, "sumsq"), nb.parts, nb.width, float(nb.eps))
+
+
+def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor | None,
+                ksplit: int = 1, norm_behind: NormBehind | None = None,
+                norm_before: NormBefore | None = None) -> None:
     """out[m, n] = x[m, :] . weight[n, :] (+ bias[n]) in bfloat16 with float32 accumulation, for
     m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks (up to 8) share K: they
-    form a thread-block cluster and add their accumulators on chip, in rank order."""
+    form a thread-block cluster and add their accumulators on chip, in rank order.  With
+    `norm_behind` the product joins the residual stream in the epilogue (`out` is not written and
+    may be None); with `norm_before` its rows are scaled there (m <= 16 for both)."""
     m, k = x.shape
     n = weight.shape[0]
-    assert weight.shape[1] == k and out.shape == (m, n)
-    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    assert weight.shape[1] == k and (out is None or out.shape == (m, n))
+    assert x.dtype == weight.dtype == torch.bfloat16 and (out is None or out.dtype == torch.bfloat16)
     assert bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == n)
+    behind = (None, None, None, None)
+    if norm_behind is not None:
+        nb = norm_behind
+        parts = -(-n // 128) * ksplit
+        assert m <= GEMM_NORM_ROWS and nb.residual.dtype == torch.float32 and nb.residual.shape == (m, n)
+        assert nb.gain.dtype == torch.bfloat16 and nb.gain.numel() == n
+        assert nb.scaled.dtype == torch.bfloat16 and nb.scaled.shape == (m, n)
+        assert nb.sumsq.dtype == torch.float32 and nb.sumsq.numel() >= parts * GEMM_NORM_ROWS
+        behind = (_ptr(nb.residual, "residual"), _ptr(nb.gain, "gain"), _ptr(nb.scaled, "scaled"),
+                  _ptr(nb.sumsq, "sumsq"))
+    else:
+        assert out is not None
     _check(library().ems_gemm_smallm(
         _ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
-        _stream()), "gemm_smallm")
+        *behind, *_norm_before_args(norm_before, m), _stream()), "gemm_smallm")
 
 
-def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                      norm_before: NormBefore | None = None) -> None:
     """out[m, i] = silu(x . weight[i]) * (x . weight[I + i]) for weight [2 I, K]: gate and up
-    projections of a gated feed-forward and its activation in one tcgen05 kernel, m <= 64."""
+    projections of a gated feed-forward and its activation in one tcgen05 kernel, m <= 64.  With
+    `norm_before` (m <= 16) both projections' rows are scaled first, as in `gemm_smallm`."""
     m, k = x.shape
     inter = out.shape[1]
     assert weight.shape == (2 * inter, k) and out.shape[0] == m
     assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
     _check(library().ems_gemm_smallm_gated(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(out, "out"), m, inter, k,
-                                           _stream()), "gemm_smallm_gated")
+                                           *_norm_before_args(norm_before, m), _stream()), "gemm_smallm_gated")
 
 
 def gemm_large_gated_supported(m: int, inter: int, k: int) -> bool:

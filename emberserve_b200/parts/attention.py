@@ -78,6 +78,7 @@ def decode_splits(num_rows: int, num_kv_heads: int, max_ctx: int, sms: int | Non
 
 @register_part("mixer", "gqa_attention")
 class GQAttention(Mixer):
+    splits_norms = True
     wqkv: torch.Tensor
     wo: torch.Tensor
     bqkv: torch.Tensor | None = None
@@ -120,6 +121,7 @@ class GQAttention(Mixer):
         n = ctx.num_tokens
         qkv = ctx.scratch("qkv", (n, self.q_size + 2 * self.kv_size), ctx.dtype)
         linear(x, self.wqkv, self.bqkv, qkv, ctx.scratch)
+        behind = ctx.extra.get("norm_behind")  # the norm behind this mixer, if wo's product may begin it
         table, rot = (None, 0)
         if self.position is not None:
             r = self.position.rotary(ctx.device)
@@ -145,8 +147,7 @@ class GQAttention(Mixer):
                                      s.num_heads, s.num_kv_heads, s.head_dim, self.scale, table, rot,
                                      cache.write, window=cache.window, splits=splits, scratch=scratch)
             y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
-            linear(out, self.wo, None, y, ctx.scratch)
-            return y
+            return linear(out, self.wo, None, y, ctx.scratch, behind)
         K.rope_kv_write(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions,
                         ctx.row_of_token, table, rot, cache.k, cache.v, cache.block_tables,
                         cache.page_size, write_kv=cache.write)
@@ -171,5 +172,4 @@ class GQAttention(Mixer):
                               ctx.starts[nd:], b - nd, n, s.num_heads, s.num_kv_heads, s.head_dim,
                               self.scale, max(ctx.q_lens[nd:]), window=cache.window, kernel=kern)
         y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
-        linear(out, self.wo, None, y, ctx.scratch)
-        return y
+        return linear(out, self.wo, None, y, ctx.scratch, behind)

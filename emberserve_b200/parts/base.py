@@ -132,6 +132,54 @@ class StepContext:
 
 
 # ---------------------------------------------------------------------------------------
+# a norm split between the products on either side of it
+
+
+@dataclass
+class NormRequest:
+    """What a block asks of the LAST product of a sub-layer when the norm behind the sub-layer
+    can be begun there (steps of few rows, where every kernel saved is microseconds): add the
+    product into `residual` instead of returning it, and hand back `ScaledRows` for the norm
+    with this `gain` and `eps`.  A sub-layer that does not know about this ignores it."""
+
+    residual: torch.Tensor  # [num_tokens, width] float32, updated in place
+    gain: torch.Tensor  # [width]
+    eps: float
+
+
+@dataclass
+class ScaledRows:
+    """Activations of a norm that is not finished yet: `x` holds residual * gain (activation
+    dtype); row n still has to be multiplied by rsqrt(sumsq[:parts, n].sum() / width + eps).
+    That factor is one number per row, so it commutes with a product x W^T: the product that
+    reads `x` applies it to its result (`parts.linear`), and the norm costs no kernel of its own.
+    `materialize()` finishes the norm the plain way for a reader that cannot."""
+
+    x: torch.Tensor  # [num_tokens, width]
+    sumsq: torch.Tensor  # [parts, 16] float32: shares of each row's sum of squares
+    parts: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.x.is_cuda
+
+    def materialize(self) -> torch.Tensor:
+        n, width = self.x.shape
+        total = self.sumsq[:self.parts, :n].sum(0)
+        rstd = torch.rsqrt(total / width + self.eps)
+        return (self.x.float() * rstd[:, None]).to(self.x.dtype)
+
+
+# ---------------------------------------------------------------------------------------
 # parts
 
 
@@ -182,6 +230,12 @@ class Part:
 
 
 class Norm(Part):
+    def split_request(self, residual: torch.Tensor, ctx: StepContext) -> "NormRequest | None":
+        """A `NormRequest` if, in this step, the norm can be begun by the product before it and
+        finished by the product behind it (then `forward` will be handed the `ScaledRows` that
+        came of it as `delta`, and passes them on); None (the default) if it is a kernel of its own."""
+        return None
+
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor,
                 ctx: StepContext, rows: torch.Tensor | None = None) -> torch.Tensor:
         """residual += delta (32-bit sum); return norm(residual) in the activation dtype.
@@ -209,6 +263,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if `forward` takes `ScaledRows` for x (its first product finishes the norm) and looks
+    # for a `NormRequest` in ctx.extra["norm_behind"] (its last product begins the next norm,
+    # and `forward` then returns `ScaledRows`).  False: plain tensors in and out.
+    splits_norms = False
+
     def cache_need(self) -> CacheNeed | None:
         return None
 
@@ -217,6 +276,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    splits_norms = False  # as for Mixer
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
@@ -228,6 +289,12 @@ class Block(Part):
 
     def cache_need(self) -> CacheNeed | None:
         raise NotImplementedError
+
+    def entry_norm(self) -> "Norm | None":
+        """The norm that receives what the block is given, if the sub-layer behind that norm takes
+        `ScaledRows`: the block BEFORE this one may then let its last product begin that norm
+        (the decoder tells it through ctx.extra["next_norm"]).  None: hand me a plain delta."""
+        return None
 
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
                 cache: Any) -> torch.Tensor:

@@ -41,9 +41,21 @@ class PreNormBlock(Block):
     def cache_need(self) -> CacheNeed | None:
         return self.mixer.cache_need()
 
+    def entry_norm(self):
+        return self.mixer_norm if self.mixer.splits_norms else None
+
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
                 cache: Any) -> torch.Tensor:
+        # A sub-layer whose successor takes `ScaledRows` is asked to begin the norm that follows
+        # it in its last product (ctx.extra["norm_behind"]); what it returns says whether it did.
+        after_ffn = ctx.extra.pop("next_norm", None)  # the next block's entry norm, from the decoder
         x = self.mixer_norm.forward(delta, residual, ctx)
+        ctx.extra["norm_behind"] = (self.ffn_norm.split_request(residual, ctx)
+                                    if self.mixer.splits_norms and self.ffn.splits_norms else None)
         a = self.mixer.forward(x, ctx, cache)
         y = self.ffn_norm.forward(a, residual, ctx)
-        return self.ffn.forward(y, ctx)
+        ctx.extra["norm_behind"] = (after_ffn.split_request(residual, ctx)
+                                    if after_ffn is not None and self.ffn.splits_norms else None)
+        out = self.ffn.forward(y, ctx)
+        ctx.extra["norm_behind"] = None
+        return out

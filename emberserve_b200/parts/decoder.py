@@ -163,7 +163,11 @@ class Decoder:
         if self.embed_position is not None:
             self.embed_position.on_embedding(residual, ctx)
         delta = None
-        for call, handle in zip(s.order, handles, strict=True):
+        for i, (call, handle) in enumerate(zip(s.order, handles, strict=True)):
+            # the norm that will receive this block's output, if it can be begun by the block's
+            # last product (`Block.entry_norm`); the final norm is always a kernel of its own
+            ctx.extra["next_norm"] = (self.blocks[s.order[i + 1].layer].entry_norm()
+                                      if i + 1 < len(s.order) else None)
             delta = self.blocks[call.layer].forward(delta, residual, ctx, handle)
         logits = ctx.scratch("logits", (num_want, s.vocab_size), torch.float32)
         if num_want == 0:

@@ -17,6 +17,7 @@ from __future__ import annotations
 import torch
 
 from emberserve_b200 import kernels as K
+from emberserve_b200.parts.base import NormRequest, ScaledRows
 
 
 def strict_matmul_precision() -> None:
@@ -28,7 +29,8 @@ def strict_matmul_precision() -> None:
     torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 
-_MIN_K_TILES_PER_SPLIT = 8
+_MIN_K_TILES_PER_SPLIT = 4
+_MAX_KSPLIT = 8  # the portable size of a thread-block cluster
 # Up to this many rows the hand-written kernel is used; with more, cuBLAS is as fast or faster
 # (measured at the projection shapes of a 7B model).
 _SMALLM_ROWS = 16
@@ -39,23 +41,24 @@ _GATED_ROWS = 64
 
 
 def smallm_ksplit(m_tok: int, n_out: int, k: int, sms: int | None = None) -> int:
-    """Over how many blocks (one thread-block cluster, at most 8) the small-row kernel splits
-    K so that the blocks of the product fill the `sms` SMs of the device: the smallest split
-    that keeps at least nine tenths of them busy, a function of the shape and the device alone
-    (a result never depends on the batch)."""
+    """Over how many blocks (one thread-block cluster, at most 8) the small-row kernel splits K:
+    the LARGEST split whose blocks all start at once on the `sms` SMs of the device.  These
+    products are chains of short waits (fill the ring, multiply, push the partial sums, store)
+    as much as streams, so the shortest K range per block wins as long as no cluster has to wait
+    for a second wave; a K range keeps at least four 64-column tiles.  Two blocks share an SM, but
+    a cluster has to fit into one of the GPU's processing clusters, so not every slot can be
+    filled: 6/7 of them is what starts in one wave on a B200 (36 clusters of 7 do, 36 of 8 do
+    not).  A function of the shape and the device alone: a result never depends on the batch."""
     sms = sms if sms is not None else K.sm_count()
     tiles = -(-n_out // 128)
     k_tiles = -(-k // 64)
-    best, best_fill = 1, 0.0
-    for split in range(1, 9):
-        if split > 1 and k_tiles // split < _MIN_K_TILES_PER_SPLIT:
+    slots = (2 * sms * 6) // 7
+    best = 1
+    for split in range(2, _MAX_KSPLIT + 1):
+        if k_tiles // split < _MIN_K_TILES_PER_SPLIT:
             break
-        blocks = tiles * split
-        fill = blocks / (-(-blocks // sms) * sms)
-        if fill > best_fill + 1e-9:
-            best, best_fill = split, fill
-        if fill >= 0.9:
-            break
+        if tiles * split <= slots:
+            best = split
     return best
 
 
@@ -67,7 +70,11 @@ def _use_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
             and x.is_contiguous() and weight.is_contiguous() and out.is_contiguous())
 
 
-def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+def _norm_before(x: ScaledRows) -> K.NormBefore:
+    return K.NormBefore(x.sumsq, x.parts, x.x.shape[1], x.eps)
+
+
+def gated_linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, out: torch.Tensor) -> bool:
     """out = silu(x Wg^T) * (x Wu^T) with weight = [Wg; Wu], in one kernel, where a hand-written
     kernel takes the case: the weight-streaming one up to 64 rows, the two-SM one (256 x 256
     tiles, persistent) above; False if the caller has to do it in steps.  At the 7B shape the
@@ -76,6 +83,11 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bo
     step of the 0.5B shape at 256 rows (38 tiles of the 9728 x 896 weight) takes 1.53 ms with it and
     1.57 with the library and the activation kernel, although alone the library is ahead there
     (9.7 us against 11.9): inside a graph one launch less weighs more than the kernel's fixed cost."""
+    if isinstance(x, ScaledRows):  # a norm that this product has to finish
+        if _use_smallm(x.x, weight, None, out, K.GEMM_NORM_ROWS):
+            K.gemm_smallm_gated(x.x, weight, out, norm_before=_norm_before(x))
+            return True
+        x = x.materialize()
     if _use_smallm(x, weight, None, out, _GATED_ROWS):
         K.gemm_smallm_gated(x, weight, out)
         return True
@@ -87,15 +99,36 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bo
 
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
-           out: torch.Tensor, scratch=None) -> torch.Tensor:
+def linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, bias: torch.Tensor | None,
+           out: torch.Tensor, scratch=None, behind: NormRequest | None = None) -> "torch.Tensor | ScaledRows":
     """out = x @ weight.T (+ bias).  x: [N, K], weight: [M, K], out: [N, M].  With few rows
     in bfloat16 the product runs on the hand-written tcgen05 kernel (`scratch` is the step's
-    scratch allocator, for its split-K partials); otherwise in cuBLAS."""
+    scratch allocator); otherwise in cuBLAS.
+
+    `x` may be `ScaledRows`, the input of a norm still to be finished: the kernel scales the
+    rows of the product (or the norm is finished the plain way first).  With `behind`, a
+    `NormRequest`, the kernel adds the product into the residual stream, begins that norm and
+    `ScaledRows` come back instead of `out` (which is then not written); where the kernel does
+    not take the case the request is ignored and `out` comes back as always."""
+    before = None
+    if isinstance(x, ScaledRows):
+        if scratch is not None and _use_smallm(x.x, weight, bias, out, K.GEMM_NORM_ROWS):
+            before, x = _norm_before(x), x.x
+        else:
+            x = x.materialize()
     if scratch is not None and _use_smallm(x, weight, bias, out):
         m, k = x.shape
         n = weight.shape[0]
-        K.gemm_smallm(x, weight, bias, out, ksplit=smallm_ksplit(m, n, k, K.sm_count(x.device)))
+        ksplit = smallm_ksplit(m, n, k, K.sm_count(x.device))
+        if (behind is not None and m <= K.GEMM_NORM_ROWS and behind.residual.shape == (m, n)
+                and behind.gain.dtype == torch.bfloat16):
+            parts = -(-n // 128) * ksplit
+            rows = ScaledRows(scratch("normed", (m, n), torch.bfloat16),
+                              scratch("norm_sumsq", (parts, K.GEMM_NORM_ROWS), torch.float32), parts, behind.eps)
+            K.gemm_smallm(x, weight, bias, None, ksplit=ksplit, norm_before=before,
+                          norm_behind=K.NormBehind(behind.residual, behind.gain, rows.x, rows.sumsq))
+            return rows
+        K.gemm_smallm(x, weight, bias, out, ksplit=ksplit, norm_before=before)
         return out
     same = weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
     if same and out.dtype == x.dtype:

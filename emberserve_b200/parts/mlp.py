@@ -29,6 +29,7 @@ class SwiGLUSpec:
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
+    splits_norms = True
     wgu: torch.Tensor
     wdown: torch.Tensor
 
@@ -54,5 +55,5 @@ class SwiGLU(FeedForward):
             linear(x, self.wgu, None, gu, ctx.scratch)
             K.silu_mul(gu, act)
         y = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
-        linear(act, self.wdown, None, y, ctx.scratch)
-        return y
+        # (the norm behind this feed-forward, if the down projection's product may begin it)
+        return linear(act, self.wdown, None, y, ctx.scratch, ctx.extra.get("norm_behind"))

@@ -7,12 +7,14 @@ stream is held in 32 bits; the sum and the statistics are 32-bit.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
 
 from emberserve_b200 import kernels as K
-from emberserve_b200.parts.base import Norm, ParamSpec, Source, StepContext, register_part
+from emberserve_b200.parts.base import (Norm, NormRequest, ParamSpec, ScaledRows, Source, StepContext,
+                                        register_part)
 
 
 @dataclass(frozen=True)
@@ -34,8 +36,21 @@ class RMSNorm(Norm):
     def scratch_elements_per_token(self) -> int:
         return self.spec.dim  # "normed" (the rows before the head are fewer)
 
+    def split_request(self, residual: torch.Tensor, ctx: StepContext) -> NormRequest | None:
+        # In bfloat16 steps of few rows the norm is split between the products around it: the one
+        # before adds into the residual, applies the gain and begins the sum of squares, the one
+        # behind multiplies its rows by rsqrt(mean + eps).  (Roundings then differ from the
+        # kernel's: residual * gain is rounded once, the scale is applied to a float32 result.)
+        if (ctx.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and residual.is_cuda
+                and ctx.num_tokens <= K.GEMM_NORM_ROWS and os.environ.get("EMBERSERVE_SPLIT_NORMS", "1") != "0"):
+            return NormRequest(residual, self.weight, self.spec.eps)
+        return None
+
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
+        if isinstance(delta, ScaledRows):  # begun by the product before: the product behind finishes it
+            assert rows is None
+            return delta
         s: RMSNormSpec = self.spec
         n = residual.shape[0] if rows is None else rows.numel()
         out = ctx.scratch("normed" if rows is None else "normed_rows", (n, s.dim), ctx.dtype)

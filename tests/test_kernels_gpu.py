@@ -602,6 +602,74 @@ def test_gemm_smallm_cluster_split(m, n, k, ksplit):
     assert torch.equal(out, again)  # fixed order of additions
 
 
+@pytest.mark.parametrize("m,n,k,ksplit", [(8, 3584, 3584, 5), (1, 896, 4864, 8), (16, 3584, 18944, 5), (5, 200, 640, 1),
+                                          (8, 5120, 1024, 2), (13, 130, 512, 3)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_smallm_begins_the_norm_behind_it(m, n, k, ksplit, with_bias):
+    """The product added into the float32 residual stream in the kernel's epilogue, with the gain
+    of the norm behind it applied to a bfloat16 copy and the rows' sums of squares left in
+    per-block shares: against the same done in float64."""
+    g = torch.Generator(device="cuda").manual_seed(m * 13 + n)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16) if with_bias else None
+    gain = (1 + 0.3 * torch.randn(n, device=dev(), generator=g)).to(torch.bfloat16)
+    res0 = torch.randn(m, n, device=dev(), generator=g) * 2
+    res = res0.clone()
+    parts = -(-n // 128) * ksplit
+    scaled = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev())
+    sumsq = torch.full((parts, 16), float("nan"), device=dev())
+    K().gemm_smallm(x, w, bias, None, ksplit=ksplit, norm_behind=K().NormBehind(res, gain, scaled, sumsq))
+    torch.cuda.synchronize()
+    K().check_status()
+    y = x.double() @ w.double().t() + (bias.double() if with_bias else 0)
+    want = res0.double() + y
+    tol_y = 8e-3 * float(y.abs().max()) + 1e-3  # (the product itself is bfloat16 x bfloat16 in float32)
+    assert float((res.double() - want).abs().max()) <= tol_y
+    torch.testing.assert_close(scaled.float(), (res * gain.float()).to(torch.bfloat16).float(), rtol=8e-3, atol=1e-6)
+    got_sq = sumsq[:, :m].double().sum(0)
+    torch.testing.assert_close(got_sq, res.double().pow(2).sum(1), rtol=1e-5, atol=1e-5)
+    again_res, again_sq = res0.clone(), torch.empty_like(sumsq)
+    K().gemm_smallm(x, w, bias, None, ksplit=ksplit, norm_behind=K().NormBehind(again_res, gain, torch.empty_like(scaled), again_sq))
+    assert torch.equal(again_res, res) and torch.equal(again_sq[:, :m], sumsq[:, :m])  # fixed order of additions
+
+
+@pytest.mark.parametrize("m,n,k,ksplit,parts", [(8, 4608, 3584, 4, 140), (1, 1152, 896, 1, 7), (16, 640, 1024, 2, 33),
+                                                (5, 130, 512, 3, 1)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_smallm_finishes_the_norm_before_it(m, n, k, ksplit, parts, gated):
+    """Rows of the product multiplied by rsqrt(mean square + eps), the mean square coming from
+    per-block shares, before the bias (plain product) or before SiLU (gated product): against
+    the norm applied to the activations first, in float64."""
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n + parts)
+    r = torch.randn(m, k, device=dev(), generator=g) * 3  # the residual rows that the norm is about
+    gain = (1 + 0.3 * torch.randn(k, device=dev(), generator=g)).to(torch.bfloat16)
+    xg = (r * gain.float()).to(torch.bfloat16)
+    # their sums of squares, cut into `parts` shares (and rubbish in the rows beyond m)
+    cut = torch.rand(parts, m, device=dev(), generator=g) + 0.1
+    shares = torch.full((parts, 16), float("nan"), device=dev())
+    shares[:, :m] = cut / cut.sum(0) * r.pow(2).sum(1)
+    eps = 1e-5
+    before = K().NormBefore(shares, parts, k, eps)
+    rstd = torch.rsqrt(r.double().pow(2).mean(1) + eps)
+    if gated:
+        inter = n // 2
+        w = (torch.randn(2 * inter, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+        out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=dev())
+        K().gemm_smallm_gated(xg, w, out, norm_before=before)
+        y = (xg.double() * rstd[:, None]) @ w.double().t()
+        want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    else:
+        w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+        bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16)
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev())
+        K().gemm_smallm(xg, w, bias, out, ksplit=ksplit, norm_before=before)
+        want = (xg.double() * rstd[:, None]) @ w.double().t() + bias.double()
+    torch.cuda.synchronize()
+    K().check_status()
+    assert float((out.double() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
+
+
 @pytest.mark.parametrize("m,inter,k", [(300, 256, 128), (2048, 1152, 896), (513, 4864, 896), (65, 128, 72),
                                        (1000, 2560, 3584), (256, 128, 64), (129, 384, 200)])
 def test_gemm_large_gated(m, inter, k):
