@@ -169,6 +169,24 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const uint32_t tmem_d = *tmem_slot;
     bool ok = true;
 
+    // What the epilogue of a split product will need from global memory for this thread's first
+    // four outputs, asked for now, while the block waits and streams: bias and gain are weights
+    // and are loaded; the residual row may still be written by a kernel before this one, so it is
+    // only asked into L2 (a step has read hundreds of megabytes since it was last touched).
+    const int quads = owned >> 2;
+    const int my_n = threadIdx.x / quads, my_rl = (threadIdx.x % quads) * 4;
+    const int my_orow = tile * G5_BM + me * owned + my_rl;
+    const bool my_quad = split && (int)threadIdx.x < quads * p.m_tok && me * owned + my_rl + 3 < G5_BM &&
+                         my_orow + 3 < p.n_out && (p.n_out & 3) == 0;
+    uint2 gain_pre = make_uint2(0u, 0u), bias_pre = make_uint2(0u, 0u);
+    if (my_quad) {
+        if (p.bias) bias_pre = *reinterpret_cast<const uint2*>(p.bias + my_orow);
+        if (p.res) {
+            gain_pre = *reinterpret_cast<const uint2*>(p.gain + my_orow);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.res + (size_t)my_n * p.n_out + my_orow));
+        }
+    }
+
     if (warp == 0 && lane == 0) {
         // ---- TMA producer (the first ring of weight tiles is on its way already) ----------
         const int pre = min(nk, STAGES);
@@ -279,21 +297,11 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
         // own: add what the ksplit blocks pushed for my rows, in rank order (the same for every batch)
         if (my_rows > 0) {
-            // (norm behind) what this thread's first four outputs join, asked for while the pushes travel
+            // (norm behind) what this thread's first four outputs join, read while the pushes travel
             const bool norm_behind = p.res != nullptr;
-            const int quads = owned >> 2;
             float4 res_pre = make_float4(0.f, 0.f, 0.f, 0.f);
-            uint2 gain_pre = make_uint2(0u, 0u);
-            bool pre = false;
-            if (norm_behind && (int)threadIdx.x < quads * p.m_tok && (p.n_out & 3) == 0) {
-                const int n = threadIdx.x / quads, rl = (threadIdx.x % quads) * 4;
-                const int orow = tile * G5_BM + me * owned + rl;
-                if (me * owned + rl + 3 < G5_BM && orow + 3 < p.n_out) {
-                    res_pre = *reinterpret_cast<const float4*>(p.res + (size_t)n * p.n_out + orow);
-                    gain_pre = *reinterpret_cast<const uint2*>(p.gain + orow);
-                    pre = true;
-                }
-            }
+            const bool pre = norm_behind && my_quad;
+            if (pre) res_pre = *reinterpret_cast<const float4*>(p.res + (size_t)my_n * p.n_out + my_orow);
             bool arrived = true;
             if (lane == 0) arrived = mbar_wait(inbox_bar, 0, p.status, 5);
             arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
@@ -311,10 +319,17 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     for (int e = 0; e < 4; ++e) acc[e] += src[e * COLS];
                 }
                 const float sc = scale_rows ? rstd_s[n] : 1.0f;
+                if (my_quad && idx == (int)threadIdx.x) {  // the bias is in registers already
+                    const float2 b01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bias_pre.x));
+                    const float2 b23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bias_pre.y));
+                    acc[0] = acc[0] * sc + b01.x; acc[1] = acc[1] * sc + b01.y;
+                    acc[2] = acc[2] * sc + b23.x; acc[3] = acc[3] * sc + b23.y;
+                } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    acc[e] *= sc;
-                    if (orow + e < p.n_out && p.bias) acc[e] += __bfloat162float(p.bias[orow + e]);
+                    for (int e = 0; e < 4; ++e) {
+                        acc[e] *= sc;
+                        if (orow + e < p.n_out && p.bias) acc[e] += __bfloat162float(p.bias[orow + e]);
+                    }
                 }
                 if (norm_behind) {
                     // the product joins the residual stream here; the norm behind it gets its gain
