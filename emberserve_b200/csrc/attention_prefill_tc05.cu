@@ -165,20 +165,6 @@ __device__ __forceinline__ float t5_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
-// 2^x on the FMA pipe, for the share of the exponentials that the special-function unit has no
-// time for (it delivers 16 a cycle per SM, as many as the tensor cores consume here): round to
-// the nearest integer n with the 1.5 * 2^23 trick, a cubic for 2^f on f in [-0.5, 0.5] (fitted
-// for the relative error, 7.5e-5 at most: a fiftieth of the rounding of P to bfloat16), and n
-// added to the exponent field.  x <= -126 gives 2^-126 rather than 0.
-__device__ __forceinline__ float t5_ex2_poly(float x) {
-    x = fmaxf(x, -126.0f);
-    const float t = x + 12582912.0f;
-    const float f = x - (t - 12582912.0f);
-    float q = fmaf(0.055171649903059006f, f, 0.2426111251115799f);
-    q = fmaf(q, f, 0.6932609677314758f);
-    q = fmaf(q, f, 0.9999280571937561f);
-    return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
-}
 __device__ __forceinline__ uint32_t t5_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);

@@ -372,27 +372,3 @@ EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int
     p.k_tiles = (k + GL_BK - 1) / GL_BK; p.m_tiles = (m_tok + 2 * GL_BM - 1) / (2 * GL_BM); p.n_tiles = inter / GL_BN;
     return launch_gemm_large<true>(mx, mw, p, stream);
 }
-
-// y[m_tok, n_out] (bf16) = x[m_tok, k] . w[n_out, k]^T (+ bias), any number of rows; n_out and k
-// multiples of 8, 16-byte aligned pointers.  The engine keeps cuBLAS for these plain products: whole
-// 256 x 256 tiles fill the SM pairs unevenly at its shapes (112 tiles on 74 pairs for a 2048 x 3584
-// output), and splitting the left-over tiles along K (tried: partial sums through a workspace, added
-// in K order by the last block to arrive) bought nothing, because a product this long runs at the
-// power limit whatever its schedule.
-EMS_EXPORT int ems_gemm_large(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out, int k,
-                              cudaStream_t stream) {
-    if (m_tok <= 0 || n_out <= 0) return EMS_OK;
-    if (k <= 0 || k % 8 || n_out % 8) return EMS_ERR_SHAPE;
-    if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 16)) return EMS_ERR_ALIGN;
-    int* status = tc_status_device_ptr();
-    if (!status) return EMS_ERR_LAUNCH;
-    int* status_dev = nullptr;
-    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
-    CUtensorMap mx, mw;
-    if (!tc_tensor_map_2d(x, m_tok, k, GL_BM, &mx) || !tc_tensor_map_2d(w, n_out, k, GL_BN, &mw)) return EMS_ERR_LAUNCH;
-    GemmLargeParams p;
-    p.y = reinterpret_cast<bf16*>(y); p.bias = reinterpret_cast<const bf16*>(bias); p.status = status_dev;
-    p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + GL_BK - 1) / GL_BK;
-    p.m_tiles = (m_tok + 2 * GL_BM - 1) / (2 * GL_BM); p.n_tiles = (n_out + 2 * GL_BN - 1) / (2 * GL_BN);
-    return launch_gemm_large<false>(mx, mw, p, stream);
-}

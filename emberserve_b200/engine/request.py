@@ -1,4 +1,10 @@
-"""Request life-cycle types (``emberserve/sched/request.py:43-138``).
+"""Request life-cycle types.
+
+The SCHEMA here is the reference's, kept on purpose so that its users find what they know:
+the states, the finish reasons, and the fields and small accessors of ``Request`` and
+``RequestOutput`` are those of ``emberserve/sched/request.py:43-138``, name for name.  This
+engine's own are ``hold`` (asynchronous stepping), ``tokens_between`` (the step function takes
+tokens, not requests) and ``check_stop`` living here rather than beside the sampler.
 
 A request moves WAITING -> RUNNING -> FINISHED, or back to the front of the waiting queue
 when it is preempted: it keeps its generated tokens and recomputes everything.  Token ids

@@ -70,7 +70,6 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, P],
         "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, P],
         "ems_gemm_large_gated": [P, P, P, I, I, I, P],
-        "ems_gemm_large": [P, P, P, P, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -437,18 +436,6 @@ def gemm_large_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -
     assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
     _check(library().ems_gemm_large_gated(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(out, "out"), m, inter, k,
                                           _stream()), "gemm_large_gated")
-
-
-def gemm_large(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> None:
-    """out[m, n] = x . weight[n] (+ bias[n]) on the same two-SM tcgen05 kernel; n and K multiples of 8.
-    (The engine's plain products stay with cuBLAS, which is ahead at its shapes; this entry serves
-    feed-forwards without a gate.)"""
-    m, k = x.shape
-    n = weight.shape[0]
-    assert weight.shape == (n, k) and out.shape == (m, n)
-    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
-    _check(library().ems_gemm_large(_ptr(x, "x"), _ptr(weight, "weight"), None if bias is None else _ptr(bias, "bias"),
-                                    _ptr(out, "out"), m, n, k, _stream()), "gemm_large")
 
 
 def gemm_smallm_status() -> int:

@@ -723,24 +723,6 @@ def test_gemm_large_gated_refuses():
         K().gemm_large_gated(x, w, torch.empty(512, 200, dtype=torch.bfloat16, device=dev()))
 
 
-@pytest.mark.parametrize("m,n,k,bias", [(300, 256, 128, True), (2048, 4608, 896, True), (513, 896, 4864, False),
-                                        (65, 136, 72, True), (1000, 3584, 3584, False), (257, 1000, 200, True),
-                                        (2048, 3584, 18944, False), (512, 3584, 3584, False), (4000, 5120, 640, True)])
-def test_gemm_large_plain(m, n, k, bias):
-    """The two-SM kernel without the gate: bias in the epilogue, output columns that end inside a tile."""
-    g = torch.Generator(device="cuda").manual_seed(m * 31 + n)
-    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
-    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
-    b = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16) if bias else None
-    out = torch.full((m + 3, n), float("nan"), dtype=torch.bfloat16, device=dev())
-    K().gemm_large(x, w, b, out[:m])
-    torch.cuda.synchronize()
-    K().check_status()
-    want = x.float() @ w.float().t() + (b.float() if bias else 0.0)
-    assert float((out[:m].float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
-    assert bool(torch.isnan(out[m:].float()).all())
-
-
 @pytest.mark.parametrize("m,inter,k", [(1, 256, 128), (8, 18944, 3584), (16, 1000, 3584), (17, 4864, 896),
                                        (33, 640, 1024), (64, 2048, 512), (5, 130, 72)])
 def test_gemm_smallm_gated(m, inter, k):
