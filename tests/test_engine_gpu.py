@@ -509,6 +509,55 @@ def test_norm_part_alone(dtype):
     torch.testing.assert_close(out.double().cpu(), want, rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("rows,hidden,inter", [(8, 256, 384), (1, 3584, 1024), (13, 200, 128)])
+@pytest.mark.parametrize("consumer", ["plain", "gated", "float32 weight"])
+def test_norm_split_between_the_products_around_it(rows, hidden, inter, consumer):
+    """A sub-layer's last product, asked to begin the norm behind it, and the product behind the
+    norm that finishes it (a plain one, the gated one, and one whose weight is stored in 32 bits,
+    which finishes the norm the plain way) against the chain product -> norm kernel -> product."""
+    from emberserve_b200.parts.base import ScaledRows, build_part
+    from emberserve_b200.parts.linear import gated_linear, linear
+    from emberserve_b200.parts.norm import RMSNormSpec
+
+    dtype = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(rows + hidden)
+    norm = build_part("norm", RMSNormSpec(hidden, 1e-5, "n.weight"), "n")
+    norm.bind({"weight": (1 + 0.2 * torch.randn(hidden, device=DEV, generator=g)).to(dtype)})
+    ctx = _ctx([1] * rows, list(range(rows)), dtype)
+    x = torch.randn(rows, 512, device=DEV, generator=g).to(dtype)
+    w1 = (torch.randn(hidden, 512, device=DEV, generator=g) * 0.05).to(dtype)
+    res0 = torch.randn(rows, hidden, device=DEV, generator=g)
+    n_out = 2 * inter if consumer == "gated" else inter
+    w2 = (torch.randn(n_out, hidden, device=DEV, generator=g) * 0.05).to(torch.float32 if consumer == "float32 weight" else dtype)
+    bias = None if consumer == "gated" else torch.randn(n_out, device=DEV, generator=g).to(w2.dtype)
+
+    def behind_the_norm(x_in, out):
+        if consumer == "gated":
+            assert gated_linear(x_in, w2, out)
+        else:
+            linear(x_in, w2, bias, out, ctx.scratch)
+        return out.float().clone()
+
+    # the chain of three kernels
+    res_a = res0.clone()
+    delta = linear(x, w1, None, torch.empty(rows, hidden, dtype=dtype, device=DEV), ctx.scratch)
+    normed = norm.forward(delta, res_a, ctx).clone()
+    want = behind_the_norm(normed, torch.empty(rows, inter, dtype=dtype, device=DEV))
+    # the norm split between the two products
+    res_b = res0.clone()
+    request = norm.split_request(res_b, ctx)
+    assert request is not None
+    rows_b = linear(x, w1, None, torch.empty(rows, hidden, dtype=dtype, device=DEV), ctx.scratch, request)
+    assert isinstance(rows_b, ScaledRows) and norm.forward(rows_b, res_b, ctx) is rows_b
+    torch.testing.assert_close(res_b, res_a, rtol=0, atol=2e-2 * float(delta.float().abs().max()))  # (unrounded delta)
+    torch.testing.assert_close(rows_b.materialize().float(), normed.float(), rtol=2e-2, atol=2e-2)
+    got = behind_the_norm(rows_b, torch.empty(rows, inter, dtype=dtype, device=DEV))
+    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max()) + 1e-3
+    # a step of more rows than the products take a norm for: no request, the norm is a kernel
+    assert norm.split_request(torch.zeros(17, hidden, device=DEV), _ctx([17], [0], dtype)) is None
+    assert norm.split_request(res_b.float(), _ctx([1] * rows, list(range(rows)), torch.float32)) is None
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 def test_feed_forward_part_alone(dtype):
     from emberserve_b200.parts.base import build_part
