@@ -72,32 +72,37 @@ class Scheduler:
         self._by_id: dict[str, Request] = {}
 
     # ---- queue management ------------------------------------------------------------------
+    def _why_never(self, req: Request) -> str | None:
+        """Why `req` could never be served, or None (the rules of ``scheduler.py:78-94``, plus the
+        prompt that is larger than the whole pool)."""
+        cfg, n = self.config, req.num_prompt_tokens
+        smallest_pool = min(p.num_pages for p in self.cache.pools) if self.cache.pools else None
+        rules = (
+            (req.seq_id < 0, "the engine must assign seq_id before add_request"),
+            (n == 0, "empty prompt"),
+            (n >= cfg.max_model_len, f"prompt has {n} tokens, max_model_len is {cfg.max_model_len}"),
+            (not cfg.enable_chunked_prefill and n > cfg.max_num_batched_tokens,
+             f"prompt has {n} tokens, exceeds max_num_batched_tokens {cfg.max_num_batched_tokens}"),
+            (req.request_id in self._by_id, f"duplicate request_id {req.request_id!r}"),
+            (smallest_pool is not None and self.cache.pages_needed(n + 1) > smallest_pool,
+             f"prompt has {n} tokens, the cache holds {(smallest_pool or 0) * self.cache.page_size}"),
+        )
+        return next((why for hit, why in rules if hit), None)
+
     def add_request(self, req: Request) -> None:
-        """Enqueue; refuses what can never be served (``scheduler.py:78-94``)."""
-        if req.seq_id < 0:
-            raise ValueError("the engine must assign seq_id before add_request")
-        n = req.num_prompt_tokens
-        if n == 0:
-            raise ValueError("empty prompt")
-        if n >= self.config.max_model_len:
-            raise ValueError(f"prompt has {n} tokens, max_model_len is {self.config.max_model_len}")
-        if not self.config.enable_chunked_prefill and n > self.config.max_num_batched_tokens:
-            raise ValueError(f"prompt has {n} tokens, exceeds max_num_batched_tokens "
-                             f"{self.config.max_num_batched_tokens}")
-        if req.request_id in self._by_id:
-            raise ValueError(f"duplicate request_id {req.request_id!r}")
-        if self.cache.pages_needed(n + 1) > min(p.num_pages for p in self.cache.pools):
-            raise ValueError(f"prompt has {n} tokens, the cache holds "
-                             f"{min(p.num_pages for p in self.cache.pools) * self.cache.page_size}")
+        """Put `req` at the end of the waiting queue, or refuse it with the reason."""
+        why = self._why_never(req)
+        if why is not None:
+            raise ValueError(why)
+        self._by_id[req.request_id] = req
         req.state = RequestState.WAITING
         self.waiting.append(req)
-        self._by_id[req.request_id] = req
 
     def abort_request(self, request_id: str) -> Request | None:
+        """End a request wherever it stands; None if no live request has that id."""
         req = self._by_id.get(request_id)
-        if req is None:
-            return None
-        self._retire(req, FinishReason.ABORT)
+        if req is not None:
+            self._retire(req, FinishReason.ABORT)
         return req
 
     def finish_request(self, req: Request, reason: FinishReason) -> None:
@@ -105,15 +110,17 @@ class Scheduler:
             self._retire(req, reason)
 
     def _retire(self, req: Request, reason: FinishReason) -> None:
-        if req in self.waiting:
-            self.waiting.remove(req)
-        if req in self.running:
-            self.running.remove(req)
+        """Out of whichever queue holds it, pages and slot back, marked finished."""
+        for queue in (self.waiting, self.running):
+            for i, other in enumerate(queue):  # (by identity: requests compare field by field)
+                if other is req:
+                    del queue[i]
+                    break
         self.cache.release(req.seq_id)
-        req.state = RequestState.FINISHED
+        self._by_id.pop(req.request_id, None)
         req.finish_reason = reason
         req.finished_time = time.perf_counter()
-        self._by_id.pop(req.request_id, None)
+        req.state = RequestState.FINISHED
 
     def has_unfinished_requests(self) -> bool:
         return bool(self.waiting or self.running)
@@ -146,7 +153,10 @@ class Scheduler:
         recomputation after a preemption) is under way (``scheduler.py:241-251``)."""
         return self.cache.num_tokens(req.seq_id) - req.num_computed_tokens
 
-    def _preempt_youngest(self) -> Request:
+    def _evict_newest(self) -> Request:
+        """Pages ran out: the request that was admitted last gives up everything it holds and goes
+        back to the FRONT of the waiting queue, to be recomputed from its tokens
+        (``scheduler.py:352-360``)."""
         victim = self.running.pop()
         self.cache.release(victim.seq_id)
         victim.reset_for_recompute()
@@ -154,23 +164,28 @@ class Scheduler:
         return victim
 
     def _give_decode_tokens(self, out: SchedulerOutput, skip_mid_prompt: bool) -> None:
-        i = 0
-        while i < len(self.running):
-            req = self.running[i]
-            if req.hold or (skip_mid_prompt and self._outstanding(req) > 0):
-                i += 1
+        """One more token slot for every running request that decodes, oldest first; when the
+        pool is empty the newest requests are evicted until the slot can be had, and a request
+        that would have to evict itself waits instead."""
+        evicted: set[int] = set()
+        for req in list(self.running):
+            if id(req) in evicted:  # gave its pages to an older one a moment ago
                 continue
-            try:
-                self.cache.extend(req.seq_id, self.cache.num_tokens(req.seq_id) + 1)
-            except OutOfPages:
-                victim = self._preempt_youngest()
-                out.preempted.append(victim)
-                if victim is req:
-                    break  # nothing younger to evict: it waits to be recomputed
-                continue  # try the same request again with the freed pages
+            if req.hold or (skip_mid_prompt and self._outstanding(req) > 0):
+                continue
+            while True:
+                try:
+                    self.cache.extend(req.seq_id, self.cache.num_tokens(req.seq_id) + 1)
+                except OutOfPages:
+                    victim = self._evict_newest()
+                    out.preempted.append(victim)
+                    evicted.add(id(victim))
+                    if victim is req:
+                        return  # nothing newer was left to evict, and nobody behind it either
+                    continue
+                break
             out.add(req, 1, True)
             out.num_decode_tokens += 1
-            i += 1
 
     def _admit(self, req: Request, now: float) -> None:
         self.waiting.popleft()
