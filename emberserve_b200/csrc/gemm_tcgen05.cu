@@ -556,9 +556,7 @@ template <int NT, int COLS, bool DUAL>
 static int launch_gemm5(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm5Params& p, int tiles,
                         cudaStream_t stream) {
     auto kernel = gemm_smallm_tcgen05_kernel<NT, COLS, DUAL>;
-    // (all of the SM's memory as shared memory: two blocks of the plain kernel then share an SM)
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g5_smem_bytes<NT, COLS, DUAL>()) != cudaSuccess ||
-        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g5_smem_bytes<NT, COLS, DUAL>()) != cudaSuccess)
         return EMS_ERR_LAUNCH;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
