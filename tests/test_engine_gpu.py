@@ -384,6 +384,40 @@ def test_cache_from_free_memory_leaves_room_for_the_graphs_and_the_largest_steps
     torch.cuda.empty_cache()
 
 
+def test_a_request_wider_than_the_graphs_tables_decodes_eagerly(model_dirs):
+    """Graphs are captured for contexts up to a maximum; a request that holds more pages than
+    their block tables are wide (pages were reserved for its whole prompt at admission) takes the
+    eager path instead of overflowing the graph's static buffer, and its logits are right; a
+    request that fits goes through the graph in the same run."""
+    from emberserve_b200.engine.runner import StepRow
+
+    name = "tiny_b"
+    cfg = ALL[name]
+    (_, long_toks), (_, short_toks) = rc.make_requests(cfg.vocab_size, [90, 20], seed=21)
+    cfgd, w = plain.read_model_dir(model_dirs[name])
+    runner = _runner(model_dirs[name], torch.float32, PAGE_SIZES[name], 32)
+    assert runner.enable_graphs(32, 4)  # graphs for contexts of at most 32 tokens: tables of 4 pages of 8
+    runner.cache.admit(0, 90)   # 12 pages from the start
+    runner.cache.admit(1, 12)
+    got = {0: [], 1: []}
+    runner.step([StepRow(0, long_toks[:10], 0, []), StepRow(1, short_toks[:12], 0, [])])
+    for i in range(6):  # both decode; request 0 stands at position 10..15, well inside the graphs' range
+        runner.cache.extend(1, 13 + i)
+        rows = [StepRow(0, [long_toks[10 + i]], 10 + i, [0]), StepRow(1, [short_toks[12 + i]], 12 + i, [0])]
+        assert not runner.graphs.usable(rows) and runner.graphs.usable(rows[1:])
+        out = runner.step(rows).cpu().numpy()
+        got[0].append(out[0])
+        got[1].append(out[1])
+    for seq, toks, first in ((0, long_toks, 10), (1, short_toks, 12)):
+        want = plain.forward_logits(cfgd, w, toks[:first + 6]).numpy()
+        for i in range(6):
+            assert np.abs(got[seq][i] - want[first + i]).max() <= TOL[torch.float32] * np.abs(want).max()
+    runner.cache.extend(1, 19)
+    runner.step([StepRow(1, [short_toks[18]], 18, [0])])  # alone it replays a graph
+    assert 1 in runner.graphs._graphs
+    runner.cache.check()
+
+
 # ---- faults that random weights would hide ------------------------------------------------------
 
 def _with_attention_pointing_at(model_dir, out_dir, gain=5.0):

@@ -256,6 +256,25 @@ def test_from_pretrained_leaves_the_callers_configuration_alone(model_dirs, monk
         LLMEngine.from_pretrained(model_dirs[name], cfg, no_such_knob=1)
 
 
+def test_engine_launches_on_its_runners_device_and_checks_the_feedback_size(model_dirs):
+    """What the engine launches itself (graph capture, the sampler, events) runs under a device
+    guard for the runner's GPU, whichever device is current; on the CPU harness there is nothing
+    to guard.  More sequences than sampled tokens can wait on the device are refused."""
+    import contextlib
+    import types
+
+    from emberserve_b200.engine import runner as runner_module
+
+    name = "tiny_a"
+    eng = make_llm(model_dirs[name], name).engine
+    assert isinstance(eng._on_device(), contextlib.nullcontext)
+    fake = types.SimpleNamespace(runner=types.SimpleNamespace(device=torch.device("cuda", 1)))
+    guard = LLMEngine._on_device(fake)
+    assert isinstance(guard, torch.cuda.device) and guard.idx == 1
+    with pytest.raises(ValueError, match="max_num_seqs"):
+        make_llm(model_dirs[name], name, max_num_seqs=runner_module.MAX_DEFERRED_TOKENS + 1)
+
+
 def test_repetition_penalty_steps_without_lag(model_dirs):
     """A request whose sampling reads its token history keeps the engine on plain stepping,
     and the tokens equal those of an engine with async scheduling off."""
