@@ -17,6 +17,10 @@ from emberserve_b200.parts.base import (Norm, NormRequest, ParamSpec, ScaledRows
                                         register_part)
 
 
+# EMBERSERVE_SPLIT_NORMS=0 keeps the norm a kernel of its own in every step (for comparisons).
+_SPLIT_NORMS = os.environ.get("EMBERSERVE_SPLIT_NORMS", "1") != "0"
+
+
 @dataclass(frozen=True)
 class RMSNormSpec:
     dim: int
@@ -42,7 +46,7 @@ class RMSNorm(Norm):
         # behind multiplies its rows by rsqrt(mean + eps).  (Roundings then differ from the
         # kernel's: residual * gain is rounded once, the scale is applied to a float32 result.)
         if (ctx.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and residual.is_cuda
-                and ctx.num_tokens <= K.GEMM_NORM_ROWS and os.environ.get("EMBERSERVE_SPLIT_NORMS", "1") != "0"):
+                and ctx.num_tokens <= K.GEMM_NORM_ROWS and _SPLIT_NORMS):
             return NormRequest(residual, self.weight, self.spec.eps)
         return None
 
