@@ -216,13 +216,16 @@ prefill_attention_tc05_kernel(const DecodeParams p, int* status, const __grid_co
     const uint32_t vland = bar0 + 8u * (4 * T5_STAGES + 6);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
 
-    const int b = blockIdx.z, hk = blockIdx.y;
+    // grid: x = (request, KV head), y = row tile.  Blocks are handed out x first, so the heavy row
+    // tiles (late rows, many keys) of ALL heads and requests start before any light one: with the
+    // tiles of one head after the other a second wave would begin with another head's heaviest.
+    const int b = blockIdx.x / p.nkv, hk = blockIdx.x % p.nkv;
     const int G = p.G;
     const int q0 = p.cu_q[b], qlen = p.cu_q[b + 1] - q0, start = p.starts[b];
     const int nrows = qlen * G;
     // `single`: the block owns one row tile (A) instead of two: twice the blocks, for portions whose
     // pairs of tiles would leave SMs idle; tile B's roles then have nothing to do
-    const int r0 = (int)(gridDim.x - 1 - blockIdx.x) * (single ? 1 : 2) * T5_BQ;  // heavy row tiles first
+    const int r0 = (int)(gridDim.y - 1 - blockIdx.y) * (single ? 1 : 2) * T5_BQ;  // heavy row tiles first
     if (r0 >= nrows) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -544,8 +547,8 @@ int launch_prefill_tc05(const DecodeParams& p, int B, int max_q_len, cudaStream_
         return EMS_ERR_LAUNCH;
     const int single = tiles * p.nkv * B * 2 <= sms_cached[dev] ? 1 : 0;
     if (single) tiles = ((long long)max_q_len * p.G + T5_BQ - 1) / T5_BQ;
-    if (tiles > 2147483647LL || p.nkv > 65535 || B > 65535) return EMS_ERR_SHAPE;
-    const dim3 grid((unsigned)tiles, (unsigned)p.nkv, (unsigned)B);
+    if (tiles > 65535 || (long long)p.nkv * B > 2147483647LL) return EMS_ERR_SHAPE;
+    const dim3 grid((unsigned)(p.nkv * B), (unsigned)tiles, 1u);
     kernel<<<grid, T5_THREADS, smem, stream>>>(p, status, map_k, map_v, single);
     return launch_status();
 }
