@@ -647,7 +647,8 @@ SHAPE_05B = dict(vocab_size=151936, hidden_size=896, intermediate_size=4864, num
 def run_serving(args) -> dict:
     """Continuous batching of many requests through LLM.generate(): 256 requests with
     uniform-random prompts of 64..1024 tokens and 128..512 output tokens each, Qwen2.5-0.5B
-    shape, bfloat16, random weights.  Wall clock around the whole generate() call."""
+    shape, bfloat16, random weights.  Wall clock around the whole generate() call, the second of two
+    identical calls in the process (`first_pass_seconds` is the first)."""
     import random
 
     import torch
@@ -677,9 +678,14 @@ def run_serving(args) -> dict:
     engine = LLMEngine.from_runner(runner, ecfg)
     engine.keep_stats = True
     llm = LLM.from_engine(engine)
-    llm.generate(prompts[:8], [SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)] * 8)  # warm-up
-    engine.stats.clear()
+    # Warm-up: the whole workload once.  Its steps have every row count between 1 and 256, and the
+    # first product of each row count makes the library load (and choose) a kernel for it, which
+    # costs tens of milliseconds each: a server pays that once, in its first seconds.
+    t0 = time.perf_counter()
+    llm.generate(prompts, params)
     torch.cuda.synchronize()
+    first = time.perf_counter() - t0
+    engine.stats.clear()
     with ClockSampler() as clocks:
         t0 = time.perf_counter()
         results = llm.generate(prompts, params)
@@ -689,7 +695,8 @@ def run_serving(args) -> dict:
     in_tokens = sum(len(p) for p in prompts)
     fwd = sorted(s.forward_ms + s.sample_ms for s in engine.stats)
     return {"metric": "output tok/s, continuous batching of 256 requests (Qwen2.5-0.5B shape)",
-            "value": out_tokens / dt, "unit": "tok/s", "n_gpus": 1, "seconds": dt, "requests": n_req,
+            "value": out_tokens / dt, "unit": "tok/s", "n_gpus": 1, "seconds": dt,
+            "first_pass_seconds": first, "requests": n_req,
             "output_tokens": out_tokens, "prompt_tokens": in_tokens, "steps": len(engine.stats),
             "step_ms_p50": fwd[len(fwd) // 2], "step_ms_p99": fwd[int(len(fwd) * 0.99)],
             "ms_per_step_wall": dt * 1e3 / max(1, len(engine.stats)),

@@ -95,13 +95,18 @@ B200_SMS = 148
 def sm_count(device: "torch.device | str | None" = None) -> int:
     """Streaming multiprocessors of `device` (asked once per device); the grid-shaping helpers
     (how keys or K are split over blocks) take it from here instead of a constant."""
-    dev = torch.device(device) if device is not None else torch.device("cuda", torch._C._cuda_getDevice())
-    if dev.type != "cuda" or not torch.cuda.is_available():
+    dev = torch.device(device) if device is not None else None
+    if dev is not None and dev.type != "cuda":
         return B200_SMS
-    idx = dev.index if dev.index is not None else torch._C._cuda_getDevice()
-    n = _sm_counts.get(idx)
+    key = dev.index if dev is not None and dev.index is not None else -1
+    n = _sm_counts.get(key)
     if n is None:
-        n = _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+        # (the driver is asked here only: a question about the device count at every call is slow
+        # and can wait behind other users of the driver)
+        if not torch.cuda.is_available():
+            return B200_SMS
+        idx = key if key >= 0 else torch.cuda.current_device()
+        n = _sm_counts[key] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
     return n
 
 
