@@ -587,9 +587,10 @@ def run_kernel(args) -> dict:
         ws = [(torch.randn(n_out, k, device=dev, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
         x = torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16)
         out = torch.empty(m, n_out, device=dev, dtype=torch.bfloat16)
-        if m > 64:  # prompt portions: the two-SM gated kernel against cuBLAS and its activation kernel
+        if m > 64 and (args.shape == "gate_up" or m > 128):
+            # prompt portions: the two-SM gated kernel against cuBLAS and its activation kernel
             if args.shape != "gate_up":
-                raise SystemExit("with more than 64 rows only --shape gate_up has a kernel of its own "
+                raise SystemExit("with more than 128 rows only --shape gate_up has a kernel of its own "
                                  "(the plain products of prompt steps are the library's)")
             act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
             st = {"i": 0}
@@ -611,8 +612,26 @@ def run_kernel(args) -> dict:
             return {"kernel": "gemm", "shape": args.shape, "m": m, "n": n_out, "k": k, "ms": ms,
                     "tflops": flops / ms / 1e9, "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"],
                     "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9}
-        from emberserve_b200.parts.linear import smallm_ksplit
+        from emberserve_b200.parts.linear import midm_ksplit, smallm_ksplit
 
+        if m > 16 and args.shape != "gate_up":  # the kernel for 17..128 rows
+            ksplit = args.splits or midm_ksplit(m, n_out, k)
+            st = {"i": 0}
+
+            def mid():
+                K.gemm_midm(x, ws[st["i"] % copies], None, out, ksplit=ksplit)
+                st["i"] += 1
+
+            def lib():
+                torch.mm(x, ws[st["i"] % copies].t(), out=out)
+                st["i"] += 1
+
+            ms, ms_lib = timed(mid, reps=copies), timed(lib, reps=copies)
+            K.check_status()
+            nbytes = n_out * k * 2
+            return {"kernel": "gemm", "shape": args.shape, "m": m, "n": n_out, "k": k, "ksplit": ksplit, "ms": ms,
+                    "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                    "cublas_ms": ms_lib, "cublas_gbs": nbytes / ms_lib / 1e6}
         ksplit = args.splits or smallm_ksplit(m, n_out, k)
         act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
         state = {"i": 0}

@@ -73,17 +73,6 @@ struct Gemm5Params {
 
 constexpr int G5_NORM_ROWS = 16;  // rows (tokens) of a step up to which the norms are fused into the products
 
-// 16 bytes into the shared memory of the block with rank `rank` of this cluster, at the address
-// that `addr` has in this block; the store completes 16 bytes on that block's mbarrier `bar`.
-__device__ __forceinline__ void push_f32x4(uint32_t addr, uint32_t bar, uint32_t rank, float a, float b, float c,
-                                           float d) {
-    uint32_t raddr, rbar;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(addr), "r"(rank));
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar), "r"(rank));
-    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
-                 ::"r"(raddr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(rbar) : "memory");
-}
-
 template <int N> __device__ __forceinline__ void tc_ld_cols(uint32_t taddr, float (&v)[N]);
 template <> __device__ __forceinline__ void tc_ld_cols<16>(uint32_t taddr, float (&v)[16]) { tc_ld16(taddr, v); }
 

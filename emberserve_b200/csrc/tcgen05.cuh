@@ -76,6 +76,33 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive float32 columns of this thread's accumulator lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// `bytes` (a multiple of 16) from this block's shared memory at `src` into the shared memory of the
+// block with rank `rank` of this cluster, at the address that `dst` has in this block; the copy
+// completes its bytes on that block's mbarrier `bar`.  The source must stay allocated until the
+// destination has seen them.
+__device__ __forceinline__ void bulk_push(uint32_t dst, uint32_t src, uint32_t bytes, uint32_t bar, uint32_t rank) {
+    uint32_t rdst, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rdst) : "r"(dst), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar), "r"(rank));
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(rdst), "r"(src), "r"(bytes), "r"(rbar) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1024 bytes apart (stride byte offset), version 1, layout type 2.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -92,6 +119,16 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr, uint32_t rank)
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
     return v;
+}
+// 16 bytes into the shared memory of the block with rank `rank` of this cluster, at the address
+// that `addr` has in this block; the store completes 16 bytes on that block's mbarrier `bar`.
+__device__ __forceinline__ void push_f32x4(uint32_t addr, uint32_t bar, uint32_t rank, float a, float b, float c,
+                                           float d) {
+    uint32_t raddr, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar), "r"(rank));
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(raddr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(rbar) : "memory");
 }
 // true in exactly one lane of a converged warp
 __device__ __forceinline__ bool elect_one() {

@@ -69,6 +69,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
         "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, P],
         "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, P],
+        "ems_gemm_midm": [P, P, P, P, I, I, I, I, P],
+        "ems_gemm_midm_max_clusters": [I, I],
         "ems_gemm_large_gated": [P, P, P, I, I, I, P],
     }
     for name, args in sigs.items():
@@ -411,6 +413,40 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     _check(library().ems_gemm_smallm(
         _ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
         *behind, *_norm_before_args(norm_before, m), _stream()), "gemm_smallm")
+
+
+GEMM_MIDM_ROWS = 128
+_midm_clusters: dict[tuple[int, int, int], int] = {}
+
+
+def gemm_midm_max_clusters(m: int, ksplit: int, device: "torch.device | None" = None) -> int:
+    """How many clusters of `ksplit` blocks of the kernel for `m` rows (one block per SM) the device
+    holds at once; a cluster lives inside one of the GPU's processing clusters, so this is less than
+    SMs // ksplit (a B200 holds 148, 74, 45, 33, 26, 22, 15, 15 for 1..8).  Asked once per size."""
+    nt = 32 if m <= 32 else (64 if m <= 64 else 128)
+    idx = -1 if device is None or device.index is None else device.index
+    key = (idx, nt, ksplit)
+    n = _midm_clusters.get(key)
+    if n is None:
+        n = int(library().ems_gemm_midm_max_clusters(nt, ksplit))
+        if n < 0:
+            raise KernelError(f"gemm_midm: the occupancy of clusters of {ksplit} could not be asked")
+        _midm_clusters[key] = n
+    return n
+
+
+def gemm_midm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
+              ksplit: int = 1) -> None:
+    """out[m, n] = x[m, k] @ weight[n, k].T (+ bias) in bfloat16 for up to 128 rows: the tcgen05
+    kernel with one block per SM and a deep ring.  `ksplit` (1..8) blocks share K as a cluster;
+    the caller picks it so that all blocks start in one wave."""
+    m, k = x.shape
+    n = weight.shape[0]
+    assert x.dtype == weight.dtype == out.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
+    assert x.is_contiguous() and weight.is_contiguous() and out.is_contiguous()
+    assert weight.shape[1] == k and out.shape == (m, n)
+    _check(library().ems_gemm_midm(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"),
+                                   m, n, k, ksplit, _stream()), "gemm_midm")
 
 
 def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,

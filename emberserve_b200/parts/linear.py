@@ -62,6 +62,42 @@ def smallm_ksplit(m_tok: int, n_out: int, k: int, sms: int | None = None) -> int
     return best
 
 
+def midm_ksplit(m_tok: int, n_out: int, k: int, clusters=None) -> int:
+    """Over how many blocks (one cluster, at most 8) the kernel for 17..128 rows splits K: it keeps
+    one block per SM, so the largest split of which the device holds as many clusters at once as
+    the product has 128-row tiles (`clusters(split)`, by default asked from the device); a K range
+    keeps at least two 64-column tiles.  A function of the shape and the device alone."""
+    clusters = clusters or (lambda split: K.gemm_midm_max_clusters(m_tok, split))
+    tiles = -(-n_out // 128)
+    k_tiles = -(-k // 64)
+    best = 1
+    for split in range(2, _MAX_KSPLIT + 1):
+        if k_tiles // split < 2:
+            break
+        if tiles <= clusters(split):
+            best = split
+    return best
+
+
+def _use_midm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> int:
+    """The K split with which the tcgen05 kernel for 17..128 rows takes the product, or 0 where
+    cuBLAS stays.  It takes products with a long K and few output tiles (K >= 2 N: the down
+    projection of a gated feed-forward), where the library does not split K well: 7B shape
+    (3584 x 18944) 27.0 / 28.6 / 31.7 us at 17 / 64 / 96 rows against 31.7 / 32.1 / 32.7, 0.5B
+    shape (896 x 4864) 4.8 / 6.4 against 8.7 / 8.4 at 17 / 64.  At squarer shapes (qkv, o) its fixed
+    cost (set-up, and the partial sums of up to 64 KB per block that cross the cluster) leaves it
+    0.3..2.6 us behind the library's 8..9 us, and from 97 rows on the activation tiles, as large as
+    the weight tiles, take the SMs' inbound bandwidth."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if not (_SMALLM_ROWS < m <= 96 and k >= 2 * n and _use_smallm(x, weight, bias, out, 96)):
+        return 0
+    ksplit = midm_ksplit(m, n, k)
+    if m > 64 and -(-k // 64) // ksplit < 32:
+        return 0
+    return ksplit
+
+
 def _use_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
                 rows: int = _SMALLM_ROWS) -> bool:
     return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
@@ -130,6 +166,11 @@ def linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, bias: torch.Ten
             return rows
         K.gemm_smallm(x, weight, bias, out, ksplit=ksplit, norm_before=before)
         return out
+    if scratch is not None:
+        ksplit = _use_midm(x, weight, bias, out)
+        if ksplit:
+            K.gemm_midm(x, weight, bias, out, ksplit=ksplit)
+            return out
     same = weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
     if same and out.dtype == x.dtype:
         if bias is None:

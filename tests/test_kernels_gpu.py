@@ -602,6 +602,63 @@ def test_gemm_smallm_cluster_split(m, n, k, ksplit):
     assert torch.equal(out, again)  # fixed order of additions
 
 
+@pytest.mark.parametrize("m,n,k,ksplit", [(17, 256, 128, 1), (32, 384, 512, 2), (33, 4608, 3584, 4), (64, 3584, 3584, 5),
+                                          (65, 3584, 18944, 4), (128, 3584, 18944, 5), (100, 896, 4864, 8),
+                                          (127, 1152, 896, 7), (50, 200, 72, 1), (50, 200, 520, 3), (77, 130, 1000, 6),
+                                          (128, 1000, 2048, 8), (20, 128, 256, 8), (5, 300, 640, 2), (96, 5120, 1024, 3)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_midm_tcgen05(m, n, k, ksplit, with_bias):
+    """The tcgen05 GEMM for 17..128 rows (one block per SM, partial sums carried into their owners'
+    shared memory by bulk copies) against a float32 product of the same bfloat16 inputs: row counts
+    around its column tiles (32, 64, 128) and no multiple of four, widths that are no multiple of
+    128, K that is no multiple of 64, every cluster size; the same bits at every call."""
+    g = torch.Generator(device="cuda").manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16) if with_bias else None
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev())
+    before = K().launch_count()
+    K().gemm_midm(x, w, bias, out, ksplit=ksplit)
+    assert K().launch_count() - before == 1
+    torch.cuda.synchronize()
+    K().check_status()
+    want = x.float() @ w.float().t()
+    if with_bias:
+        want = want + bias.float()
+    scale = float(want.abs().max())
+    assert float((out.float() - want).abs().max()) <= 8e-3 * scale + 1e-3, (m, n, k, ksplit)
+    again = torch.empty_like(out)
+    K().gemm_midm(x, w, bias, again, ksplit=ksplit)
+    assert torch.equal(out, again)  # fixed order of additions
+
+
+def test_gemm_midm_split_fits_the_device():
+    """The K split that `linear` picks for the kernel above lets all clusters of the product start
+    at once, and the products it hands to the kernel equal the library's."""
+    from emberserve_b200.parts import linear as L
+
+    for m, n, k in [(17, 3584, 18944), (64, 896, 4864), (96, 5120, 27648), (40, 1536, 8960)]:
+        split = L.midm_ksplit(m, n, k)
+        assert 1 <= split <= 8 and -(-n // 128) <= K().gemm_midm_max_clusters(m, split)
+        g = torch.Generator(device="cuda").manual_seed(n)
+        x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=dev(), generator=g) * 0.02).to(torch.bfloat16)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev())
+        assert L._use_midm(x, w, None, out) == split
+        before = K().launch_count()
+        L.linear(x, w, None, out, scratch=lambda *a: None)
+        assert K().launch_count() - before == 1  # the kernel of this library, not cuBLAS
+        want = x.float() @ w.float().t()
+        assert float((out.float() - want).abs().max()) <= 8e-3 * float(want.abs().max()) + 1e-3
+    # squarer products and more rows stay with the library
+    x = torch.zeros(64, 3584, dtype=torch.bfloat16, device=dev())
+    assert L._use_midm(x, torch.zeros(4608, 3584, dtype=torch.bfloat16, device=dev()), None,
+                       torch.empty(64, 4608, dtype=torch.bfloat16, device=dev())) == 0
+    x = torch.zeros(128, 4864, dtype=torch.bfloat16, device=dev())
+    assert L._use_midm(x, torch.zeros(896, 4864, dtype=torch.bfloat16, device=dev()), None,
+                       torch.empty(128, 896, dtype=torch.bfloat16, device=dev())) == 0
+
+
 @pytest.mark.parametrize("m,n,k,ksplit", [(8, 3584, 3584, 5), (1, 896, 4864, 8), (16, 3584, 18944, 5), (5, 200, 640, 1),
                                           (8, 5120, 1024, 2), (13, 130, 512, 3)])
 @pytest.mark.parametrize("with_bias", [False, True])
