@@ -17,7 +17,7 @@
 // 77-79); at these row counts the library reaches about half of the memory bandwidth.
 //
 // Every wait on an mbarrier is bounded: if it runs out, the block records a code in the status
-// word shared by the tcgen05 kernels (codes 11..15 here), stops issuing work, lets what it has
+// word shared by the tcgen05 kernels (codes 31..35 here: producer, MMA issuer, epilogue, drain, arrival of the partials), stops issuing work, lets what it has
 // in flight land, frees its tensor memory and returns.
 #include <cuda.h>
 
@@ -123,7 +123,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         for (int it = pre; it < nk && ok; ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-            ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 11);
+            ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, p.status, 31);
             if (!ok) break;
             mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
             const int k0 = (kt_begin + it) * G6_BK;
@@ -133,7 +133,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         }
         if (!ok) {  // let the copies that were issued land before the block leaves
             for (int it = max(0, armed - STAGES); it < armed; ++it)
-                mbar_wait(full0 + 8 * (it % STAGES), (uint32_t)(it / STAGES) & 1u, p.status, 14);
+                mbar_wait(full0 + 8 * (it % STAGES), (uint32_t)(it / STAGES) & 1u, p.status, 34);
         }
     } else if (warp == 1) {
         // ---- MMA issue: the warp runs the loop, one elected lane issues ---------------------
@@ -141,7 +141,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         for (int it = 0; it < nk && ok; ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph, p.status, 12));
+            ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph, p.status, 32));
             if (!ok) break;
             tc_fence_after();
             const uint64_t da = smem_desc_sw128(a_s + s * A_BYTES), db = smem_desc_sw128(b_s + s * B_BYTES);
@@ -161,7 +161,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     grid_dependency_wait();  // (the producer has passed it already; this orders the stores below)
     allow_dependent_launch();
     bool done = true;
-    if (lane == 0) done = mbar_wait(done_bar, 0, p.status, 13);
+    if (lane == 0) done = mbar_wait(done_bar, 0, p.status, 33);
     done = __shfl_sync(0xffffffffu, done ? 1 : 0, 0) != 0;
     tc_fence_after();
     const int row_local = warp * 32 + lane;
@@ -221,7 +221,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                       (uint32_t)r);
         }
         bool arrived = true;
-        if (lane == 0) arrived = mbar_wait(inbox_bar, 0, p.status, 15);
+        if (lane == 0) arrived = mbar_wait(inbox_bar, 0, p.status, 35);
         arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
         if (arrived) mbar_try_wait(inbox_bar, 0);  // (every thread observes the completed phase itself)
         // every copy INTO this block has landed; the others may leave once they know

@@ -483,7 +483,9 @@ def gemm_smallm_status() -> int:
     """0, or the code of the first bounded wait that ran out in the tcgen05 kernel (after a
     synchronisation point): 1 producer, 2 MMA issuer, 3 epilogue, 4 drain, 5 arrival of the split-K
     partials of the small-row kernel;
-    11 producer, 12 and 13 MMA issuer, 14 epilogue of the two-SM kernel."""
+    11 producer, 12 and 13 MMA issuer, 14 epilogue of the two-SM kernel; 31 producer, 32 MMA issuer,
+    33 epilogue, 34 drain, 35 arrival of the partials of the kernel for 17..128 rows; 20 and up: the
+    prompt attention."""
     return int(library().ems_gemm_smallm_status())
 
 
