@@ -38,19 +38,29 @@ class Request:
     request_id: str
     prompt_token_ids: list[int]
     sampling_params: SamplingParams
-    seq_id: int = -1  # integer id used by the cache manager; assigned by the engine
-    arrival_time: float = field(default_factory=time.perf_counter)
+    # -- where it stands ------------------------------------------------------------------
     state: RequestState = RequestState.WAITING
-    output_token_ids: list[int] = field(default_factory=list)
     finish_reason: FinishReason | None = None
-    num_computed_tokens: int = 0
+    seq_id: int = -1  # integer id used by the cache manager; assigned by the engine
+    num_computed_tokens: int = 0  # its position in the cache
+    output_token_ids: list[int] = field(default_factory=list)
+    # Set while the request's last token is still on its way from the device and is known to end
+    # it (max_tokens or the model length): the scheduler gives it no further token.
+    hold: bool = False
+    # -- clock readings (time.perf_counter) for the metrics of its final output ---------------
+    arrival_time: float = field(default_factory=time.perf_counter)
     first_scheduled_time: float | None = None
     first_token_time: float | None = None
     finished_time: float | None = None
     metadata: dict = field(default_factory=dict)
-    # Set while the request's last token is still on its way from the device and is known to end
-    # it (max_tokens or the model length): the scheduler gives it no further token.
-    hold: bool = False
+
+    @property
+    def is_finished(self) -> bool:
+        return self.state == RequestState.FINISHED
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
 
     @property
     def num_prompt_tokens(self) -> int:
@@ -61,14 +71,11 @@ class Request:
         return len(self.output_token_ids)
 
     @property
-    def num_tokens(self) -> int:
-        return len(self.prompt_token_ids) + len(self.output_token_ids)
-
-    @property
     def all_token_ids(self) -> list[int]:
         return self.prompt_token_ids + self.output_token_ids
 
     def tokens_between(self, start: int, end: int) -> list[int]:
+        """Tokens [start, end) of prompt + output: what a step that computes these positions is fed."""
         n = len(self.prompt_token_ids)
         if end <= n:
             return self.prompt_token_ids[start:end]
@@ -76,18 +83,14 @@ class Request:
             return self.output_token_ids[start - n:end - n]
         return self.prompt_token_ids[start:] + self.output_token_ids[:end - n]
 
-    @property
-    def is_finished(self) -> bool:
-        return self.state == RequestState.FINISHED
-
     def append_output(self, token_id: int) -> None:
         self.output_token_ids.append(token_id)
 
     def reset_for_recompute(self) -> None:
         """Preemption by recompute: keep the generated tokens, drop the cache position
         (``request.py:120-124``)."""
-        self.num_computed_tokens = 0
         self.state = RequestState.PREEMPTED
+        self.num_computed_tokens = 0
 
 
 @dataclass
