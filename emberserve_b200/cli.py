@@ -37,13 +37,17 @@ def _add_engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--enable-chunked-prefill", dest="enable_chunked_prefill", action="store_true",
                    default=True, help="mix decode tokens and prompt portions in every step (default)")
     p.add_argument("--no-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
-    p.add_argument("--no-cuda-graphs", dest="enable_cuda_graphs", action="store_false", default=True)
+    p.add_argument("--enable-cuda-graphs", dest="enable_cuda_graphs", action="store_true", default=True,
+                   help="replay decode steps from CUDA graphs (default)")
+    p.add_argument("--no-cuda-graphs", dest="enable_cuda_graphs", action="store_false")
     p.add_argument("--attn-backend", choices=["auto", "mma", "generic"], default="auto",
                    help="attention kernels of the bfloat16 path: the fastest that takes the case, the mma.sync "
                         "kernels only, or the 32-bit CUDA-core kernel everywhere")
     p.add_argument("--debug-scratch-guard", type=int, default=0, metavar="N",
                    help="debugging: N guard elements around every scratch buffer, checked after each step")
-    p.add_argument("--no-async-scheduling", dest="async_scheduling", action="store_false", default=True,
+    p.add_argument("--async-scheduling", dest="async_scheduling", action="store_true", default=True,
+                   help="launch a step before the tokens of the step before it are read (default)")
+    p.add_argument("--no-async-scheduling", dest="async_scheduling", action="store_false",
                    help="read every step's tokens before the next step is planned")
 
 

@@ -117,3 +117,9 @@ def test_command_line_options_map_to_the_engine_configuration():
     assert cfg.max_num_batched_tokens == 8192  # 2048 with chunked prefill, as in the reference
     chunked = engine_config_from_args(build_parser().parse_args(["generate", "--model", "m", "--prompt", "x", "--chat"]))
     assert chunked.enable_chunked_prefill and chunked.max_num_batched_tokens == 2048 and chunked.attn_backend == "auto"
+    assert chunked.enable_cuda_graphs and chunked.async_scheduling  # on unless switched off
+    # the reference's switches that turn on what is on here by default are accepted as they are
+    same = engine_config_from_args(build_parser().parse_args(
+        ["generate", "--model", "m", "--prompt", "x", "--enable-cuda-graphs", "--async-scheduling",
+         "--enable-chunked-prefill"]))
+    assert same.enable_cuda_graphs and same.async_scheduling and same.enable_chunked_prefill
