@@ -152,7 +152,8 @@ def run_ours(args) -> dict:
     pages = max_b * (ctx_cap // PAGE_SIZE + 1) + 2 * (ptoks // PAGE_SIZE) + 64
     dtype = torch.float32 if args.dtype == "float32" else torch.bfloat16
     runner = ModelRunner.from_random(cfg, seed=0, dtype=dtype, device="cuda:0",
-                                     page_size=PAGE_SIZE, num_pages=pages)
+                                     page_size=PAGE_SIZE, num_pages=pages,
+                                     tiled_weight_copies=False if args.no_tiled_weights else None)
     if not args.no_graphs:
         runner.enable_graphs(ctx_cap + 64, max_b)
     for t in runner.storage.tensors:  # keys and values of the "earlier" tokens: random, not zero
@@ -317,7 +318,8 @@ def run_ours(args) -> dict:
         d = decode(args.batch, args.steps, args.warmup, context=args.decode_context)
         out = {"only": "decode", "dtype": args.dtype, "batch": args.batch, "layers": layers,
                "shape": args.model_shape, "context": args.decode_context, "ms_per_step": d["ms"],
-               "tok_s": d["tok_s"], "hbm_frac": d["gbs"] / peaks["hbm_gbs"]}
+               "tok_s": d["tok_s"], "hbm_frac": d["gbs"] / peaks["hbm_gbs"],
+               "tiled_weight_copy_gb": round(runner.tiled_weight_bytes / 1e9, 2)}
         if args.kernel_times:
             out["kernels"] = kernel_times(lambda: decode(args.batch, args.steps, args.warmup,
                                                          context=args.decode_context))
@@ -328,6 +330,7 @@ def run_ours(args) -> dict:
             out["kernels"] = kernel_times(lambda: prefill(1))
         return out
     used_graphs = bool(runner.use_graphs)
+    tiled_gb = round(runner.tiled_weight_bytes / 1e9, 2)
     main = decode(args.batch, args.steps, args.warmup, sample_clocks=True)
     pre = prefill()
     b1 = decode(1, min(args.steps, 32), 3)
@@ -370,7 +373,7 @@ def run_ours(args) -> dict:
                    "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE,
                    "prefill_tokens": PREFILL_TOKENS, "parallelism": "1gpu",
                    "l2": "inputs larger than L2", "cuda_graphs": used_graphs,
-                   "peaks": peaks["source"]},
+                   "tiled_weight_copy_gb": tiled_gb, "peaks": peaks["source"]},
         "clocks": main["clocks"], "gpu_launches": main["launches"], "e2e": e2e,
         "prefill": pre,
         "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -886,6 +889,9 @@ def main() -> int:
                     help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
+    ap.add_argument("--no-tiled-weights", action="store_true",
+                    help="without the engine's second, tiled copy of the projection weights (by default it is "
+                         "made where it takes at most a tenth of the device's memory, as here)")
     ap.add_argument("--only", choices=["decode", "prefill", "kernel"], default=None,
                     help="run one small part only (for profiling): decode at --batch, the prefill, or "
                          "one kernel alone (--kernel)")

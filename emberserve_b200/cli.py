@@ -43,6 +43,9 @@ def _add_engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--attn-backend", choices=["auto", "mma", "generic"], default="auto",
                    help="attention kernels of the bfloat16 path: the fastest that takes the case, the mma.sync "
                         "kernels only, or the 32-bit CUDA-core kernel everywhere")
+    p.add_argument("--tiled-weight-copies", choices=["auto", "on", "off"], default="auto",
+                   help="a second, tiled copy of the projection weights for the decode kernels: faster decode "
+                        "steps for the weights' size again (auto: where that is at most a tenth of the memory)")
     p.add_argument("--debug-scratch-guard", type=int, default=0, metavar="N",
                    help="debugging: N guard elements around every scratch buffer, checked after each step")
     p.add_argument("--async-scheduling", dest="async_scheduling", action="store_true", default=True,
@@ -64,7 +67,8 @@ def engine_config_from_args(args: argparse.Namespace):
                         enable_chunked_prefill=args.enable_chunked_prefill,
                         enable_cuda_graphs=args.enable_cuda_graphs,
                         async_scheduling=args.async_scheduling,
-                        debug_scratch_guard=args.debug_scratch_guard, attn_backend=args.attn_backend)
+                        debug_scratch_guard=args.debug_scratch_guard, attn_backend=args.attn_backend,
+                        tiled_weight_copies={"auto": None, "on": True, "off": False}[args.tiled_weight_copies])
 
 
 def build_parser() -> argparse.ArgumentParser:

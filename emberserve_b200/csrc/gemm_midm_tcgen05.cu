@@ -45,6 +45,7 @@ struct Gemm6Params {
     int* status;
     int m_tok, n_out, k_tiles, ksplit;
     int cols;            // m_tok rounded up to 4: the token columns that are pushed and summed
+    int tiled;           // the weight map is that of the tiled copy (see tc_weight_map)
 };
 
 // NT: token columns of the MMA (32, 64 or 128); the activation tile of a stage has NT rows, of
@@ -84,6 +85,10 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const int my_rows = max(0, min(owned, G6_BM - me * owned));
     const int cols = p.cols;
 
+    auto load_w = [&](uint32_t dst, int kt, uint32_t bar) {  // the weight tile of K tile `kt` into a stage
+        if (p.tiled) tma_load_2d(dst, &map_w, 0, (tile * p.k_tiles + kt) * G6_BM, bar);
+        else tma_load_2d(dst, &map_w, kt * G6_BK, tile * G6_BM, bar);
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done_bar, 1);
@@ -96,7 +101,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         const int pre = min(nk, STAGES);
         for (int it = 0; it < pre; ++it) {
             mbar_expect_tx(full0 + 8 * it, A_BYTES + B_BYTES);
-            tma_load_2d(a_s + it * A_BYTES, &map_w, (kt_begin + it) * G6_BK, tile * G6_BM, full0 + 8 * it);
+            load_w(a_s + it * A_BYTES, kt_begin + it, full0 + 8 * it);
         }
     }
     if (warp == 1) {  // tensor memory for the accumulator: NT columns x 128 lanes
@@ -127,7 +132,7 @@ gemm_midm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             if (!ok) break;
             mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
             const int k0 = (kt_begin + it) * G6_BK;
-            tma_load_2d(a_s + s * A_BYTES, &map_w, k0, tile * G6_BM, full0 + 8 * s);
+            load_w(a_s + s * A_BYTES, kt_begin + it, full0 + 8 * s);
             tma_load_2d(b_s + s * B_BYTES, &map_x, k0, 0, full0 + 8 * s);
             armed = it + 1;
         }
@@ -331,10 +336,10 @@ EMS_EXPORT int ems_gemm_midm_max_clusters(int m_tok, int ksplit) {
 
 // y[m_tok, n_out] (bf16) = x[m_tok, k] (bf16, row-major) . w[n_out, k]^T (+ bias), m_tok <= 128;
 // k a multiple of 8; 16-byte aligned x and w.  ksplit in 1..8 blocks share K as one thread-block
-// cluster.  One block per SM: the caller chooses ksplit so that n_out / 128 * ksplit blocks start
+// cluster.  `tiled`: w is the tiled copy of the weight (tc_weight_map).  One block per SM: the caller chooses ksplit so that n_out / 128 * ksplit blocks start
 // in one wave.
 EMS_EXPORT int ems_gemm_midm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out, int k,
-                             int ksplit, cudaStream_t stream) {
+                             int ksplit, int tiled, cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;
     if (m_tok > 128 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 8) return EMS_ERR_SHAPE;  // 8: the portable cluster size
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2) || y == nullptr) return EMS_ERR_ALIGN;
@@ -344,11 +349,12 @@ EMS_EXPORT int ems_gemm_midm(const void* x, const void* w, const void* bias, voi
     if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_ptr), status_dev, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
     const int nt = m_tok <= 32 ? 32 : (m_tok <= 64 ? 64 : 128);
     CUtensorMap mw, mx;
-    if (!tc_tensor_map_2d(w, n_out, k, G6_BM, &mw) || !tc_tensor_map_2d(x, m_tok, k, nt, &mx)) return EMS_ERR_LAUNCH;
+    if (!tc_weight_map(w, n_out, k, tiled != 0, &mw) || !tc_tensor_map_2d(x, m_tok, k, nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm6Params p;
     p.y = reinterpret_cast<bf16*>(y); p.bias = reinterpret_cast<const bf16*>(bias); p.status = dev_ptr;
     p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G6_BK - 1) / G6_BK; p.ksplit = ksplit;
     p.cols = (m_tok + 3) & ~3;
+    p.tiled = tiled ? 1 : 0;
     const int tiles = (n_out + G6_BM - 1) / G6_BM;
     if (nt == 32) return launch_gemm6<32>(mw, mx, p, tiles, stream);
     if (nt == 64) return launch_gemm6<64>(mw, mx, p, tiles, stream);

@@ -55,6 +55,10 @@ struct Gemm5Params {
     int m_tok, n_out, k_tiles;
     int ksplit;          // > 1: the ksplit blocks of a row tile are a cluster and reduce on chip
     int dual_offset;     // DUAL kernels: row distance between the two weight tiles
+    // The weights as a TILED copy: the 128 x 64 tile (row tile r, K tile kt) is 16 KB of contiguous
+    // memory at tile index r * k_tiles + kt, so that a TMA load reads whole DRAM pages instead of
+    // 128 bytes from each of 128 rows.  0: the row-major matrix itself.
+    int tiled;
     // The norm that stands BEHIND this product, begun in its epilogue (plain kernels, at most 16
     // rows): the product is added into the float32 residual stream `res` [m_tok, n_out] instead
     // of being stored, `scaled` gets bf16(res * gain), and every block leaves the sum of res^2
@@ -126,6 +130,16 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int owned = (((G5_BM + p.ksplit - 1) / p.ksplit) + 3) & ~3;
     const int my_rows = max(0, min(owned, G5_BM - me * owned));
 
+    // the weight tile(s) of K tile `kt` into a stage
+    auto load_w = [&](uint32_t dst, int kt, uint32_t bar) {
+        if (p.tiled) {
+            tma_load_2d(dst, &map_w, 0, (tile * p.k_tiles + kt) * G5_BM, bar);
+            if (DUAL) tma_load_2d(dst + W_BYTES, &map_w, 0, ((p.dual_offset / G5_BM + tile) * p.k_tiles + kt) * G5_BM, bar);
+        } else {
+            tma_load_2d(dst, &map_w, kt * G5_BK, tile * G5_BM, bar);
+            if (DUAL) tma_load_2d(dst + W_BYTES, &map_w, kt * G5_BK, p.dual_offset + tile * G5_BM, bar);
+        }
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done_bar, 1);
@@ -139,9 +153,7 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int pre = min(nk, STAGES);
         for (int it = 0; it < pre; ++it) {
             mbar_expect_tx(full0 + 8 * it, A_BYTES + B_BYTES);
-            const int k0 = (kt_begin + it) * G5_BK;
-            tma_load_2d(a_s + it * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * it);
-            if (DUAL) tma_load_2d(a_s + it * A_BYTES + W_BYTES, &map_w, k0, p.dual_offset + tile * G5_BM, full0 + 8 * it);
+            load_w(a_s + it * A_BYTES, kt_begin + it, full0 + 8 * it);
         }
     }
     if (warp == 1) {  // tensor memory for the accumulators: TMEM_COLS columns x 128 lanes
@@ -190,8 +202,7 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             if (!ok) break;
             mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
             const int k0 = (kt_begin + it) * G5_BK;
-            tma_load_2d(a_s + s * A_BYTES, &map_w, k0, tile * G5_BM, full0 + 8 * s);
-            if (DUAL) tma_load_2d(a_s + s * A_BYTES + W_BYTES, &map_w, k0, p.dual_offset + tile * G5_BM, full0 + 8 * s);
+            load_w(a_s + s * A_BYTES, kt_begin + it, full0 + 8 * s);
             tma_load_2d(b_s + s * B_BYTES, &map_x, k0, 0, full0 + 8 * s);
             armed = it + 1;
         }
@@ -495,6 +506,15 @@ static bool tensor_map_2d(const void* ptr, long long rows, long long cols, int b
     return true;
 }
 
+// The tensor map of a weight [rows, cols] for 128-row boxes: of the row-major matrix, or of its
+// tiled copy (rows and cols multiples of 128 and 64), which is a matrix of 64 columns whose rows
+// [t * 128, +128) are tile t = row tile * (cols / 64) + K tile.
+static bool weight_map(const void* w, long long rows, long long cols, bool tiled, CUtensorMap* out) {
+    if (!tiled) return tensor_map_2d(w, rows, cols, G5_BM, out);
+    if (rows % G5_BM || cols % G5_BK) return false;
+    return tensor_map_2d(w, rows * (cols / G5_BK), G5_BK, G5_BM, out);
+}
+
 static int* status_word() {  // host-mapped, so the host reads it without a CUDA call
     static int* host = nullptr;
     static std::once_flag once;
@@ -509,6 +529,9 @@ static int* status_word() {  // host-mapped, so the host reads it without a CUDA
 int* tc_status_device_ptr() { return status_word(); }
 bool tc_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
     return tensor_map_2d(ptr, rows, cols, box_rows, out);
+}
+bool tc_weight_map(const void* w, long long rows, long long cols, bool tiled, CUtensorMap* out) {
+    return weight_map(w, rows, cols, tiled, out);
 }
 
 template <int NT, int COLS, bool DUAL> constexpr int g5_smem_bytes() {
@@ -595,7 +618,7 @@ static bool fill_norm_before(Gemm5Params& p, const float* sumsq_in, int in_parts
 // sumsq_in[part, n] / in_width + in_eps) before the bias is added (the norm before it).
 EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
                                int k, int ksplit, float* res, const void* gain, void* scaled, float* sumsq_out,
-                               const float* sumsq_in, int in_parts, int in_width, float in_eps,
+                               const float* sumsq_in, int in_parts, int in_width, float in_eps, int tiled,
                                cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;
     if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 8) return EMS_ERR_SHAPE;  // 8: the portable cluster size
@@ -609,8 +632,9 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
     if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
     const int nt = nt_for(m_tok);
     CUtensorMap mw, mx;
-    if (!tensor_map_2d(w, n_out, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
+    if (!weight_map(w, n_out, k, tiled != 0, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm5Params p;
+    p.tiled = tiled ? 1 : 0;
     p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
     p.status = status_dev; p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = ksplit;
     p.dual_offset = 0;
@@ -628,7 +652,7 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
 // feed-forward's first two projections and its activation in one kernel.  w: [2*inter, k].
 // `sumsq_in` ...: the norm before the product, as for ems_gemm_smallm (both halves are scaled).
 EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, int m_tok, int inter, int k,
-                                     const float* sumsq_in, int in_parts, int in_width, float in_eps,
+                                     const float* sumsq_in, int in_parts, int in_width, float in_eps, int tiled,
                                      cudaStream_t stream) {
     if (m_tok <= 0 || inter <= 0) return EMS_OK;
     if (m_tok > 64 || k <= 0 || k % 8) return EMS_ERR_SHAPE;
@@ -639,8 +663,10 @@ EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, in
     if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
     const int nt = nt_for(m_tok);
     CUtensorMap mw, mx;
-    if (!tensor_map_2d(w, 2LL * inter, k, G5_BM, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
+    if (tiled && inter % G5_BM) return EMS_ERR_SHAPE;
+    if (!weight_map(w, 2LL * inter, k, tiled != 0, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm5Params p;
+    p.tiled = tiled ? 1 : 0;
     p.y = act; p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
     p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = 1; p.dual_offset = inter;
     p.res = nullptr; p.gain = nullptr; p.scaled = nullptr; p.sumsq_out = nullptr;

@@ -15,6 +15,10 @@ constexpr uint32_t G5_SPIN_LIMIT = 1u << 18;  // tries of a wait; each try may i
 // (row-major bf16 matrix, box [box_rows, 64 columns], 128-byte swizzle) serve every tcgen05 kernel.
 int* tc_status_device_ptr();
 bool tc_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out);
+// The map of a weight [rows, cols] for boxes of 128 rows: of the row-major matrix, or (`tiled`) of
+// its tiled copy, in which the 128 x 64 tile (row tile r, K tile kt) is 16 KB of contiguous memory
+// at tile index r * (cols / 64) + kt (a matrix of 64 columns; rows and cols multiples of 128 and 64).
+bool tc_weight_map(const void* w, long long rows, long long cols, bool tiled, CUtensorMap* out);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -139,7 +139,8 @@ class LLMEngine:
         return dict(page_size=cfg.block_size, num_pages=cfg.num_gpu_blocks, max_pages=useful,
                     num_state_slots=cfg.max_num_seqs, gpu_memory_utilization=cfg.gpu_memory_utilization,
                     max_step_tokens=chunk, max_graph_rows=cfg.max_num_seqs if cfg.enable_cuda_graphs else 0,
-                    max_logit_rows=cfg.max_num_seqs, scratch_guard=cfg.debug_scratch_guard)
+                    max_logit_rows=cfg.max_num_seqs, scratch_guard=cfg.debug_scratch_guard,
+                    tiled_weight_copies=cfg.tiled_weight_copies)
 
     @classmethod
     def from_runner(cls, runner: ModelRunner, engine_config: EngineConfig | None = None) -> "LLMEngine":

@@ -123,7 +123,8 @@ class ModelRunner:
                  num_pages: int | None = None, max_pages: int | None = None,
                  num_state_slots: int = 256, gpu_memory_utilization: float = 0.90,
                  reserve_bytes: int | None = None, max_step_tokens: int = 8192, max_graph_rows: int = 256,
-                 max_logit_rows: int = 256, scratch_guard: int = 0) -> None:
+                 max_logit_rows: int = 256, scratch_guard: int = 0,
+                 tiled_weight_copies: bool | None = None) -> None:
         self.device = torch.device(device)
         if self._require_cuda and (self.device.type != "cuda" or not torch.cuda.is_available()):
             raise RuntimeError("emberserve_b200 runs on a CUDA GPU only; there is no CPU path "
@@ -140,6 +141,7 @@ class ModelRunner:
         self.page_size = page_size
         self.vocab_size = decoder.spec.vocab_size
         self.max_positions = decoder.spec.max_positions
+        self.tiled_weight_bytes = self._give_tiled_twins(tiled_weight_copies)
         self.groups = plan_groups(decoder.cache_entries())
         paged = [g for g in self.groups if g.paged]
         has_state = any(not g.paged for g in self.groups)
@@ -174,6 +176,24 @@ class ModelRunner:
         self.use_graphs = False
         self.graphs = None
         self._has_state = has_state
+
+    def _give_tiled_twins(self, wanted: bool | None) -> int:
+        """A second, tiled copy of the weight matrices that decode steps stream, for the
+        weight-streaming kernels (`kernels.tile_weight`: they read whole DRAM pages from it and a
+        decode step of the 7B shape gets 3 % shorter); the bytes taken.  It costs the weights'
+        size again (embedding and head not counted), so by default (`wanted` None) it is made
+        only where that is at most a tenth of the device's memory; the cache is sized from
+        what is left."""
+        if wanted is False or not self._on_cuda or self.dtype != torch.bfloat16:
+            return 0
+        from emberserve_b200.parts.linear import give_tiled_twin
+
+        weights = [w for w in self.decoder.streamed_weights() if K.tile_weight_shape_ok(w)]
+        need = sum(w.numel() * w.element_size() for w in weights)
+        if wanted is None and need > torch.cuda.get_device_properties(self.device).total_memory // 10:
+            return 0
+        with torch.cuda.device(self.device):
+            return sum(give_tiled_twin(w) for w in weights)
 
     def enable_graphs(self, max_ctx_len: int, max_rows: int) -> bool:
         """Replay pure-decode steps of up to `max_rows` rows and contexts up to `max_ctx_len`

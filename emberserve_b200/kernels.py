@@ -67,9 +67,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_argmax": [P, P, I, I, P, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
-        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, P],
-        "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, P],
-        "ems_gemm_midm": [P, P, P, P, I, I, I, I, P],
+        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, I, P],
+        "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, I, P],
+        "ems_gemm_midm": [P, P, P, P, I, I, I, I, I, P],
         "ems_gemm_midm_max_clusters": [I, I],
         "ems_gemm_large_gated": [P, P, P, I, I, I, P],
     }
@@ -385,9 +385,37 @@ def _norm_before_args(nb: "NormBefore | None", m: int) -> tuple:
     return (_ptr(nb.sumsq, "sumsq"), nb.parts, nb.width, float(nb.eps))
 
 
+def tile_weight_shape_ok(weight: torch.Tensor) -> bool:
+    """Whether `tile_weight` has a tiled form for this weight."""
+    return (weight.dim() == 2 and weight.dtype == torch.bfloat16 and weight.is_cuda and weight.is_contiguous()
+            and weight.shape[0] % 128 == 0 and weight.shape[1] % 64 == 0)
+
+
+def tile_weight(weight: torch.Tensor) -> torch.Tensor | None:
+    """The tiled copy of a bfloat16 weight [n, k] that the weight-streaming kernels read faster: the
+    128 x 64 tile (row tile r, K tile kt) as 16 KB of contiguous memory at tile index
+    r * (k / 64) + kt, so that one TMA load reads whole DRAM pages instead of 128 bytes from each of
+    128 rows (7B shape: gate / up product 45.1 -> 43.9 us, down 25.2 -> 24.5, the decode step at
+    batch 8 2.90 -> 2.82 ms).  None where n or k is no multiple of 128 / 64.  The copy has the
+    shape [n * k / 64, 64]; it is passed as `twin` beside the weight it was made of."""
+    if not tile_weight_shape_ok(weight):
+        return None
+    n, k = weight.shape
+    return weight.view(n // 128, 128, k // 64, 64).permute(0, 2, 1, 3).contiguous().view(n * (k // 64), 64)
+
+
+def _weight_ptr(weight: torch.Tensor, twin: torch.Tensor | None) -> tuple[int | None, int]:
+    if twin is None:
+        return _ptr(weight, "weight"), 0
+    n, k = weight.shape
+    assert twin.dtype == weight.dtype and twin.shape == (n * (k // 64), 64) and n % 128 == 0 and k % 64 == 0
+    assert twin.is_contiguous()
+    return _ptr(twin, "twin"), 1
+
+
 def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor | None,
                 ksplit: int = 1, norm_behind: NormBehind | None = None,
-                norm_before: NormBefore | None = None) -> None:
+                norm_before: NormBefore | None = None, twin: torch.Tensor | None = None) -> None:
     """out[m, n] = x[m, :] . weight[n, :] (+ bias[n]) in bfloat16 with float32 accumulation, for
     m <= 64 rows: the weight-streaming tcgen05 kernel.  `ksplit` blocks (up to 8) share K: they
     form a thread-block cluster and add their accumulators on chip, in rank order.  With
@@ -410,9 +438,10 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
                   _ptr(nb.sumsq, "sumsq"))
     else:
         assert out is not None
+    wptr, tiled = _weight_ptr(weight, twin)
     _check(library().ems_gemm_smallm(
-        _ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
-        *behind, *_norm_before_args(norm_before, m), _stream()), "gemm_smallm")
+        _ptr(x, "x"), wptr, _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
+        *behind, *_norm_before_args(norm_before, m), tiled, _stream()), "gemm_smallm")
 
 
 GEMM_MIDM_ROWS = 128
@@ -436,7 +465,7 @@ def gemm_midm_max_clusters(m: int, ksplit: int, device: "torch.device | None" = 
 
 
 def gemm_midm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
-              ksplit: int = 1) -> None:
+              ksplit: int = 1, twin: torch.Tensor | None = None) -> None:
     """out[m, n] = x[m, k] @ weight[n, k].T (+ bias) in bfloat16 for up to 128 rows: the tcgen05
     kernel with one block per SM and a deep ring.  `ksplit` (1..8) blocks share K as a cluster;
     the caller picks it so that all blocks start in one wave."""
@@ -445,12 +474,13 @@ def gemm_midm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
     assert x.dtype == weight.dtype == out.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
     assert x.is_contiguous() and weight.is_contiguous() and out.is_contiguous()
     assert weight.shape[1] == k and out.shape == (m, n)
-    _check(library().ems_gemm_midm(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(bias, "bias"), _ptr(out, "out"),
-                                   m, n, k, ksplit, _stream()), "gemm_midm")
+    wptr, tiled = _weight_ptr(weight, twin)
+    _check(library().ems_gemm_midm(_ptr(x, "x"), wptr, _ptr(bias, "bias"), _ptr(out, "out"),
+                                   m, n, k, ksplit, tiled, _stream()), "gemm_midm")
 
 
 def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                      norm_before: NormBefore | None = None) -> None:
+                      norm_before: NormBefore | None = None, twin: torch.Tensor | None = None) -> None:
     """out[m, i] = silu(x . weight[i]) * (x . weight[I + i]) for weight [2 I, K]: gate and up
     projections of a gated feed-forward and its activation in one tcgen05 kernel, m <= 64.  With
     `norm_before` (m <= 16) both projections' rows are scaled first, as in `gemm_smallm`."""
@@ -458,8 +488,9 @@ def gemm_smallm_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
     inter = out.shape[1]
     assert weight.shape == (2 * inter, k) and out.shape[0] == m
     assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
-    _check(library().ems_gemm_smallm_gated(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(out, "out"), m, inter, k,
-                                           *_norm_before_args(norm_before, m), _stream()), "gemm_smallm_gated")
+    wptr, tiled = _weight_ptr(weight, twin)
+    _check(library().ems_gemm_smallm_gated(_ptr(x, "x"), wptr, _ptr(out, "out"), m, inter, k,
+                                           *_norm_before_args(norm_before, m), tiled, _stream()), "gemm_smallm_gated")
 
 
 def gemm_large_gated_supported(m: int, inter: int, k: int) -> bool:

@@ -112,6 +112,9 @@ class GQAttention(Mixer):
                                       init="bias")
         return specs
 
+    def streamed_params(self) -> list[str]:
+        return ["wqkv", "wo"]
+
     def scratch_elements_per_token(self) -> int:
         # qkv, attn_out, mixer_out
         return self.q_size + 2 * self.kv_size + self.q_size + self.spec.hidden

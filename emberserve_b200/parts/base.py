@@ -221,6 +221,13 @@ class Part:
     def children(self) -> dict[str, "Part"]:
         return {}
 
+    def streamed_params(self) -> list[str]:
+        """Local names of the weight matrices that `forward` hands to ``parts.linear`` in steps of few
+        rows, where every weight is read once per step: the engine may keep a second, tiled copy of
+        these for the weight-streaming kernels (``parts.linear.give_tiled_twin``).  Naming none is
+        always right."""
+        return []
+
     def scratch_elements_per_token(self) -> int:
         """Elements of the activation dtype that `forward` asks of ``ctx.scratch`` per token of a
         step, children not counted.  Only used to keep memory free for the steps when the

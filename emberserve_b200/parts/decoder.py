@@ -118,6 +118,16 @@ class Decoder:
                 table[f"{path}.{local}"] = ps
         return table
 
+    def streamed_weights(self) -> list[torch.Tensor]:
+        """The weight matrices that steps of few rows stream (`Part.streamed_params` of every part),
+        each tensor once."""
+        seen: dict[int, torch.Tensor] = {}
+        for _, part in self._walk():
+            for local in part.streamed_params():
+                w = getattr(part, local)
+                seen.setdefault(id(w), w)
+        return list(seen.values())
+
     def scratch_bytes_per_token(self, esize: int) -> int:
         """Bytes of step scratch per token of a step, for an activation type of `esize` bytes:
         the 32-bit residual, and every named buffer once (all blocks share the buffers by name,

@@ -62,6 +62,22 @@ def smallm_ksplit(m_tok: int, n_out: int, k: int, sms: int | None = None) -> int
     return best
 
 
+def tiled_twin(weight: torch.Tensor) -> torch.Tensor | None:
+    """The tiled copy of `weight` for the weight-streaming kernels, if the engine made one
+    (`give_tiled_twin`)."""
+    return getattr(weight, "tiled_twin", None)
+
+
+def give_tiled_twin(weight: torch.Tensor) -> int:
+    """Make the tiled copy of a weight that decode steps stream (`kernels.tile_weight`) and hang it
+    on the tensor; the bytes it takes (0 where the shape has none)."""
+    twin = K.tile_weight(weight)
+    if twin is None:
+        return 0
+    weight.tiled_twin = twin
+    return twin.numel() * twin.element_size()
+
+
 def midm_ksplit(m_tok: int, n_out: int, k: int, clusters=None) -> int:
     """Over how many blocks (one cluster, at most 8) the kernel for 17..128 rows splits K: it keeps
     one block per SM, so the largest split of which the device holds as many clusters at once as
@@ -121,11 +137,11 @@ def gated_linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, out: torc
     (9.7 us against 11.9): inside a graph one launch less weighs more than the kernel's fixed cost."""
     if isinstance(x, ScaledRows):  # a norm that this product has to finish
         if _use_smallm(x.x, weight, None, out, K.GEMM_NORM_ROWS):
-            K.gemm_smallm_gated(x.x, weight, out, norm_before=_norm_before(x))
+            K.gemm_smallm_gated(x.x, weight, out, norm_before=_norm_before(x), twin=tiled_twin(weight))
             return True
         x = x.materialize()
     if _use_smallm(x, weight, None, out, _GATED_ROWS):
-        K.gemm_smallm_gated(x, weight, out)
+        K.gemm_smallm_gated(x, weight, out, twin=tiled_twin(weight))
         return True
     if _use_smallm(x, weight, None, out, 1 << 30) and K.gemm_large_gated_supported(
             x.shape[0], out.shape[1], x.shape[1]):
@@ -161,15 +177,15 @@ def linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, bias: torch.Ten
             parts = -(-n // 128) * ksplit
             rows = ScaledRows(scratch("normed", (m, n), torch.bfloat16),
                               scratch("norm_sumsq", (parts, K.GEMM_NORM_ROWS), torch.float32), parts, behind.eps)
-            K.gemm_smallm(x, weight, bias, None, ksplit=ksplit, norm_before=before,
+            K.gemm_smallm(x, weight, bias, None, ksplit=ksplit, norm_before=before, twin=tiled_twin(weight),
                           norm_behind=K.NormBehind(behind.residual, behind.gain, rows.x, rows.sumsq))
             return rows
-        K.gemm_smallm(x, weight, bias, out, ksplit=ksplit, norm_before=before)
+        K.gemm_smallm(x, weight, bias, out, ksplit=ksplit, norm_before=before, twin=tiled_twin(weight))
         return out
     if scratch is not None:
         ksplit = _use_midm(x, weight, bias, out)
         if ksplit:
-            K.gemm_midm(x, weight, bias, out, ksplit=ksplit)
+            K.gemm_midm(x, weight, bias, out, ksplit=ksplit, twin=tiled_twin(weight))
             return out
     same = weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
     if same and out.dtype == x.dtype:

@@ -42,6 +42,9 @@ class SwiGLU(FeedForward):
             "wdown": ParamSpec((s.hidden, i), [Source(s.down_name + ".weight")]),
         }
 
+    def streamed_params(self) -> list[str]:
+        return ["wgu", "wdown"]
+
     def scratch_elements_per_token(self) -> int:
         # ffn_act, ffn_out, and gate_up for the steps in which no fused kernel takes the sizes
         return 3 * self.spec.intermediate + self.spec.hidden

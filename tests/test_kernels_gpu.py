@@ -632,6 +632,49 @@ def test_gemm_midm_tcgen05(m, n, k, ksplit, with_bias):
     assert torch.equal(out, again)  # fixed order of additions
 
 
+def test_tiled_weight_copy_changes_no_bit():
+    """The tiled copy of a weight (`kernels.tile_weight`: tile (r, kt) of 128 x 64 contiguous at index
+    r * K/64 + kt) holds the same numbers, and the three weight-streaming kernels produce the same
+    bits from it as from the row-major matrix; shapes without a tiled form have none."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    n, k = 384, 448
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    twin = K().tile_weight(w)
+    assert twin.shape == (n * (k // 64), 64)
+    for r, kt in [(0, 0), (1, 3), (2, 6)]:
+        tile = twin[(r * (k // 64) + kt) * 128:][:128]
+        assert torch.equal(tile, w[r * 128:(r + 1) * 128, kt * 64:(kt + 1) * 64])
+    assert K().tile_weight(w[:, :400].contiguous()) is None and K().tile_weight(w[:200].contiguous()) is None
+    assert K().tile_weight(w.float()) is None
+    for m, n, k, ksplit in [(8, 3584, 3584, 8), (3, 256, 128, 1), (16, 4608, 3584, 7), (13, 1152, 896, 3)]:
+        x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+        bias = torch.randn(n, device=dev(), generator=g).to(torch.bfloat16)
+        twin = K().tile_weight(w)
+        a, b = torch.empty(m, n, dtype=torch.bfloat16, device=dev()), torch.empty(m, n, dtype=torch.bfloat16, device=dev())
+        K().gemm_smallm(x, w, bias, a, ksplit=ksplit)
+        K().gemm_smallm(x, w, bias, b, ksplit=ksplit, twin=twin)
+        assert torch.equal(a, b), ("smallm", m, n, k)
+    for m, n, k, ksplit in [(17, 3584, 18944, 4), (64, 896, 4864, 8), (96, 256, 128, 1), (128, 1152, 896, 5)]:
+        x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+        twin = K().tile_weight(w)
+        a, b = torch.empty(m, n, dtype=torch.bfloat16, device=dev()), torch.empty(m, n, dtype=torch.bfloat16, device=dev())
+        K().gemm_midm(x, w, None, a, ksplit=ksplit)
+        K().gemm_midm(x, w, None, b, ksplit=ksplit, twin=twin)
+        assert torch.equal(a, b), ("midm", m, n, k)
+    for m, inter, k in [(8, 18944, 3584), (1, 4864, 896), (40, 256, 128), (64, 1280, 512)]:
+        x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+        w = (torch.randn(2 * inter, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+        twin = K().tile_weight(w)
+        a, b = torch.empty(m, inter, dtype=torch.bfloat16, device=dev()), torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+        K().gemm_smallm_gated(x, w, a)
+        K().gemm_smallm_gated(x, w, b, twin=twin)
+        assert torch.equal(a, b), ("gated", m, inter, k)
+    torch.cuda.synchronize()
+    K().check_status()
+
+
 def test_gemm_midm_split_fits_the_device():
     """The K split that `linear` picks for the kernel above lets all clusters of the product start
     at once, and the products it hands to the kernel equal the library's."""

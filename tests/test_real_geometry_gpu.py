@@ -124,3 +124,41 @@ def test_long_prompt_through_the_tcgen05_attention(name, tmp_path):
         K.check_status()
         runner.cache.check()
         runner.verify_scratch()
+
+
+@pytest.mark.parametrize("name", ["qwen2.5-0.5b", "qwen2.5-7b"])
+def test_tiled_weight_copies_change_no_logit(name, tmp_path):
+    """The engine's second, tiled copy of the projection weights (made by default where it is
+    small beside the device's memory) feeds the decode kernels the same numbers: the logits of
+    prompt portions and of decode steps of 1, 8 and 40 rows are the same bits with and without it."""
+    from emberserve_b200.engine.runner import ModelRunner, StepRow
+    from emberserve_b200.weights.loader import write_random_model
+    from emberserve_b200 import kernels as K
+
+    cfg = config_of(name)
+    folder = write_random_model(cfg, tmp_path / "m", seed=21)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist()
+               for n in torch.randint(3, 60, (40,), generator=g)]
+    got = {}
+    for copies in (False, None, True):
+        runner = ModelRunner.from_dir(folder, torch.bfloat16, page_size=16, num_pages=40 * 5 + 8,
+                                      tiled_weight_copies=copies)
+        if copies is False:
+            assert runner.tiled_weight_bytes == 0
+        else:  # (None: a model this small is far below a tenth of the memory)
+            twins = sum(w.numel() * 2 for w in runner.decoder.streamed_weights())
+            assert runner.tiled_weight_bytes == twins > 0
+        outs = []
+        for i, p in enumerate(prompts):
+            runner.cache.admit(i, len(p) + 8)
+        outs.append(runner.step([StepRow(i, p, 0, [len(p) - 1]) for i, p in enumerate(prompts)]).clone())
+        for rows in (1, 8, 40):
+            for step in range(2):
+                batch = [StepRow(i, [7 + i + step], runner.cache.committed(i), [0]) for i in range(rows)]
+                outs.append(runner.step(batch).clone())
+        torch.cuda.synchronize()
+        K.check_status()
+        got[copies] = outs
+    for a, b, c in zip(got[False], got[None], got[True]):
+        assert torch.equal(a, b) and torch.equal(a, c)

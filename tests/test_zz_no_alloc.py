@@ -13,6 +13,7 @@ stops at the first failure has then already run every other test.
 from __future__ import annotations
 
 import ctypes
+import gc
 import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -85,12 +86,20 @@ def test_static_scratch_entry_equals_the_allocating_one_twice_in_a_row(dtype, ge
             assert _call(fn, qkv, got, kc, vc, bt, cu, starts, b, b, nh, nkv, d, window, 1, splits) == 0
             got.fill_(float("nan"))
         torch.cuda.synchronize()
-        before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info(DEV)[0]
-        rc = _call(fn, qkv, got, kc, vc, bt, cu, starts, b, b, nh, nkv, d, window, 1, splits)
-        torch.cuda.synchronize()
+        # (what earlier tests left behind in reference cycles is collected now, not during the call,
+        # where it would move torch's counter)
+        gc.collect()
+        gc.disable()
+        try:
+            before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info(DEV)[0]
+            rc = _call(fn, qkv, got, kc, vc, bt, cu, starts, b, b, nh, nkv, d, window, 1, splits)
+            torch.cuda.synchronize()
+            after, free_after = torch.cuda.memory_allocated(), torch.cuda.mem_get_info(DEV)[0]
+        finally:
+            gc.enable()
         assert rc == 0, f"call {call}: status {rc}"
-        assert torch.cuda.memory_allocated() == before
-        assert torch.cuda.mem_get_info(DEV)[0] == free_before, "the call changed the device's free memory"
+        assert after == before, "the call moved torch's allocator"
+        assert free_after == free_before, "the call changed the device's free memory"
         assert torch.equal(got, want), f"call {call}: {(got.float() - want.float()).abs().max()}"
 
 
