@@ -598,8 +598,14 @@ def run_kernel(args) -> dict:
             act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
             st = {"i": 0}
 
+            twins = [K.tile_weight(w) for w in ws]
+
             def ours_large():
                 K.gemm_large_gated(x, ws[st["i"] % copies], act)
+                st["i"] += 1
+
+            def ours_large_tiled():
+                K.gemm_large_gated(x, ws[st["i"] % copies], act, twin=twins[st["i"] % copies])
                 st["i"] += 1
 
             def lib_large():
@@ -609,12 +615,13 @@ def run_kernel(args) -> dict:
                 st["i"] += 1
 
             ms = timed(ours_large, reps=copies)
+            ms_tiled = timed(ours_large_tiled, reps=copies)
             ms_lib = timed(lib_large, reps=copies)
             K.check_status()
             flops = 2.0 * m * n_out * k
             return {"kernel": "gemm", "shape": args.shape, "m": m, "n": n_out, "k": k, "ms": ms,
                     "tflops": flops / ms / 1e9, "frac_bf16": flops / ms / 1e9 / peaks["bf16_tflops"],
-                    "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9}
+                    "ms_tiled_copy": ms_tiled, "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9}
         from emberserve_b200.parts.linear import midm_ksplit, smallm_ksplit
 
         if m > 16 and args.shape != "gate_up":  # the kernel for 17..128 rows

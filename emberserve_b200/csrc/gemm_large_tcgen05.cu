@@ -50,6 +50,7 @@ struct GemmLargeParams {
     int k_tiles;
     int m_tiles;        // of 256 token rows
     int n_tiles;        // GATED: of 128 outputs; else of 256
+    int tiled;          // the weight map is that of the tiled copy (tc_weight_map)
 };
 
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
@@ -172,6 +173,11 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     if (warp == 0 && lane == 0) {
         // ---- TMA producer (each block loads its own halves; completion counts on the leader) ----
         const uint32_t lead_full0 = map_to_rank(full0, 0);
+        // this block's 128 weight rows of K step `kb` (row-major matrix, or its tiled copy)
+        auto load_w = [&](uint32_t dst, int kb, int w_row, uint32_t bar) {
+            if (p.tiled) tma_load_2d_pair(dst, &map_w, 0, ((w_row / GL_BN) * p.k_tiles + kb) * GL_BN, bar);
+            else tma_load_2d_pair(dst, &map_w, kb * GL_BK, w_row, bar);
+        };
         bool ok = true;
         int it = 0;
         // The weights do not depend on the kernel before this one (the launch is a programmatic
@@ -183,7 +189,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             const int w_row = GATED ? (int)rank * p.n_out + n_tile * GL_BN : n_tile * 2 * GL_BN + (int)rank * GL_BN;
             for (int kb = 0; kb < pre; ++kb) {
                 if (rank == 0) mbar_expect_tx(full0 + 8 * kb, 2 * GL_STAGE_BYTES);
-                tma_load_2d_pair(base + kb * GL_STAGE_BYTES + GL_TILE_BYTES, &map_w, kb * GL_BK, w_row, lead_full0 + 8 * kb);
+                load_w(base + kb * GL_STAGE_BYTES + GL_TILE_BYTES, kb, w_row, lead_full0 + 8 * kb);
             }
         }
         grid_dependency_wait();
@@ -203,7 +209,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 if (!ok) break;
                 if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * GL_STAGE_BYTES);
                 tma_load_2d_pair(dst, &map_x, kb * GL_BK, x_row, lead_full0 + 8 * s);
-                tma_load_2d_pair(dst + GL_TILE_BYTES, &map_w, kb * GL_BK, w_row, lead_full0 + 8 * s);
+                load_w(dst + GL_TILE_BYTES, kb, w_row, lead_full0 + 8 * s);
             }
         }
         if (!ok)  // copies in flight may still land in this block's shared memory: give them time
@@ -355,7 +361,7 @@ EMS_EXPORT int ems_gemm_large_gated_supported(int m_tok, int inter, int k) {
 
 // act[m_tok, inter] (bf16) = silu(x . w[0:inter]^T) * (x . w[inter:2*inter]^T), w: [2*inter, k],
 // for any number of rows; inter a multiple of 128, k a multiple of 8, 16-byte aligned pointers.
-EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int m_tok, int inter, int k,
+EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int m_tok, int inter, int k, int tiled,
                                     cudaStream_t stream) {
     if (m_tok <= 0 || inter <= 0) return EMS_OK;
     if (!ems_gemm_large_gated_supported(m_tok, inter, k)) return EMS_ERR_SHAPE;
@@ -365,10 +371,11 @@ EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int
     int* status_dev = nullptr;
     if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status, 0) != cudaSuccess) return EMS_ERR_LAUNCH;
     CUtensorMap mx, mw;
-    if (!tc_tensor_map_2d(x, m_tok, k, GL_BM, &mx) || !tc_tensor_map_2d(w, 2LL * inter, k, GL_BN, &mw))
+    if (!tc_tensor_map_2d(x, m_tok, k, GL_BM, &mx) || !tc_weight_map(w, 2LL * inter, k, tiled != 0, &mw))
         return EMS_ERR_LAUNCH;
     GemmLargeParams p;
     p.y = reinterpret_cast<bf16*>(act); p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
     p.k_tiles = (k + GL_BK - 1) / GL_BK; p.m_tiles = (m_tok + 2 * GL_BM - 1) / (2 * GL_BM); p.n_tiles = inter / GL_BN;
+    p.tiled = tiled ? 1 : 0;
     return launch_gemm_large<true>(mx, mw, p, stream);
 }

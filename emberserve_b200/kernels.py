@@ -71,7 +71,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, I, P],
         "ems_gemm_midm": [P, P, P, P, I, I, I, I, I, P],
         "ems_gemm_midm_max_clusters": [I, I],
-        "ems_gemm_large_gated": [P, P, P, I, I, I, P],
+        "ems_gemm_large_gated": [P, P, P, I, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -498,7 +498,8 @@ def gemm_large_gated_supported(m: int, inter: int, k: int) -> bool:
     return bool(library().ems_gemm_large_gated_supported(m, inter, k))
 
 
-def gemm_large_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+def gemm_large_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                     twin: torch.Tensor | None = None) -> None:
     """out[m, i] = silu(x . weight[i]) * (x . weight[I + i]) for weight [2 I, K] and any number
     of rows m: the two-SM tcgen05 kernel of prompt steps (256 x 256 tiles, persistent grid), with
     the activation in its epilogue.  I a multiple of 128, K a multiple of 8."""
@@ -506,7 +507,8 @@ def gemm_large_gated(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -
     inter = out.shape[1]
     assert weight.shape == (2 * inter, k) and out.shape[0] == m
     assert x.dtype == weight.dtype == out.dtype == torch.bfloat16
-    _check(library().ems_gemm_large_gated(_ptr(x, "x"), _ptr(weight, "weight"), _ptr(out, "out"), m, inter, k,
+    wptr, tiled = _weight_ptr(weight, twin)
+    _check(library().ems_gemm_large_gated(_ptr(x, "x"), wptr, _ptr(out, "out"), m, inter, k, tiled,
                                           _stream()), "gemm_large_gated")
 
 

@@ -671,6 +671,14 @@ def test_tiled_weight_copy_changes_no_bit():
         K().gemm_smallm_gated(x, w, a)
         K().gemm_smallm_gated(x, w, b, twin=twin)
         assert torch.equal(a, b), ("gated", m, inter, k)
+    for m, inter, k in [(100, 1280, 512), (256, 4864, 896), (300, 256, 128)]:
+        x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+        w = (torch.randn(2 * inter, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+        twin = K().tile_weight(w)
+        a, b = torch.empty(m, inter, dtype=torch.bfloat16, device=dev()), torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+        K().gemm_large_gated(x, w, a)
+        K().gemm_large_gated(x, w, b, twin=twin)
+        assert torch.equal(a, b), ("two-SM gated", m, inter, k)
     torch.cuda.synchronize()
     K().check_status()
 
