@@ -628,8 +628,10 @@ def run_kernel(args) -> dict:
             ksplit = args.splits or midm_ksplit(m, n_out, k)
             st = {"i": 0}
 
+            twins = [K.tile_weight(w) for w in ws]  # as the engine runs it: from the tiled copy
+
             def mid():
-                K.gemm_midm(x, ws[st["i"] % copies], None, out, ksplit=ksplit)
+                K.gemm_midm(x, ws[st["i"] % copies], None, out, ksplit=ksplit, twin=twins[st["i"] % copies])
                 st["i"] += 1
 
             def lib():
@@ -646,11 +648,14 @@ def run_kernel(args) -> dict:
         act = torch.empty(m, n_out // 2, device=dev, dtype=torch.bfloat16)
         state = {"i": 0}
 
+        twins = [None if args.no_tiled_weights else K.tile_weight(w) for w in ws]
+
         def ours():
+            i = state["i"] % copies
             if args.shape == "gate_up":  # as the engine runs it: both halves and SiLU in one kernel
-                K.gemm_smallm_gated(x, ws[state["i"] % copies], act)
+                K.gemm_smallm_gated(x, ws[i], act, twin=twins[i])
             else:
-                K.gemm_smallm(x, ws[state["i"] % copies], None, out, ksplit=ksplit)
+                K.gemm_smallm(x, ws[i], None, out, ksplit=ksplit, twin=twins[i])
             state["i"] += 1
 
         def cublas():

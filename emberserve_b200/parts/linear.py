@@ -99,7 +99,8 @@ def _use_midm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
     """The K split with which the tcgen05 kernel for 17..128 rows takes the product, or 0 where
     cuBLAS stays.  It takes products with a long K and few output tiles (K >= 2 N: the down
     projection of a gated feed-forward), where the library does not split K well: 7B shape
-    (3584 x 18944) 27.0 / 28.6 / 31.7 us at 17 / 64 / 96 rows against 31.7 / 32.1 / 32.7, 0.5B
+    (3584 x 18944) 27.0 / 28.6 / 31.7 us at 17 / 64 / 96 rows (25.8 / 27.8 / 30.9 from the tiled copy
+    of the weight) against 31.7 / 32.1 / 32.7, 0.5B
     shape (896 x 4864) 4.8 / 6.4 against 8.7 / 8.4 at 17 / 64.  At squarer shapes (qkv, o) its fixed
     cost (set-up, and the partial sums of up to 64 KB per block that cross the cluster) leaves it
     0.3..2.6 us behind the library's 8..9 us, and from 97 rows on the activation tiles, as large as
