@@ -49,7 +49,8 @@ constexpr int G5_INBOX_ROWS = 128 + 4 * 8;
 template <int COLS, bool DUAL> constexpr int g5_inbox_bytes() { return DUAL ? 0 : G5_INBOX_ROWS * COLS * 4; }
 
 struct Gemm5Params {
-    void* y;             // [M_tok, N_out] bf16
+    void* y;             // [M_tok, N_out] bf16, or float32 (y_f32: unsplit plain products only)
+    int y_f32;
     const bf16* bias;    // [N_out] or null
     int* status;         // device-visible status word
     int m_tok, n_out, k_tiles;
@@ -417,7 +418,10 @@ gemm_smallm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     if (c0 + i >= p.m_tok) continue;
                     const float out = v[i] * (scale_rows ? rstd_s[c0 + i] : 1.0f) + bias;
                     if (!norm_behind) {
-                        if (row < p.n_out) y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(out);
+                        if (row < p.n_out) {
+                            if (p.y_f32) reinterpret_cast<float*>(p.y)[(size_t)(c0 + i) * p.n_out + row] = out;
+                            else y[(size_t)(c0 + i) * p.n_out + row] = __float2bfloat16_rn(out);
+                        }
                         continue;
                     }
                     float sq = 0.f;
@@ -616,11 +620,16 @@ static bool fill_norm_before(Gemm5Params& p, const float* sumsq_in, int in_parts
 // every block's share of each row's sum of squares (the norm behind the product).  With `sumsq_in`
 // (m_tok <= 16): row n of the product is multiplied by 1 / sqrt(sum over in_parts of
 // sumsq_in[part, n] / in_width + in_eps) before the bias is added (the norm before it).
+// `tiled`: w is the tiled copy of the weight (tc_weight_map).  `y_f32`: y is float32 and takes the
+// sums unrounded (ksplit 1, no `res`).
 EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, void* y, int m_tok, int n_out,
                                int k, int ksplit, float* res, const void* gain, void* scaled, float* sumsq_out,
                                const float* sumsq_in, int in_parts, int in_width, float in_eps, int tiled,
-                               cudaStream_t stream) {
+                               int y_f32, cudaStream_t stream) {
     if (m_tok <= 0 || n_out <= 0) return EMS_OK;
+    // (float32 output, the logits of a language-model head: never rounded, so only where one block
+    // holds the whole sum and stores it itself)
+    if (y_f32 && (ksplit != 1 || res != nullptr || ((uintptr_t)y % 4))) return EMS_ERR_SHAPE;
     if (m_tok > 64 || k <= 0 || k % 8 || ksplit < 1 || ksplit > 8) return EMS_ERR_SHAPE;  // 8: the portable cluster size
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)y % 2)) return EMS_ERR_ALIGN;
     if (res != nullptr && (m_tok > G5_NORM_ROWS || gain == nullptr || scaled == nullptr || sumsq_out == nullptr))
@@ -635,6 +644,7 @@ EMS_EXPORT int ems_gemm_smallm(const void* x, const void* w, const void* bias, v
     if (!weight_map(w, n_out, k, tiled != 0, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm5Params p;
     p.tiled = tiled ? 1 : 0;
+    p.y_f32 = y_f32 ? 1 : 0;
     p.y = y; p.bias = reinterpret_cast<const bf16*>(bias);
     p.status = status_dev; p.m_tok = m_tok; p.n_out = n_out; p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = ksplit;
     p.dual_offset = 0;
@@ -667,6 +677,7 @@ EMS_EXPORT int ems_gemm_smallm_gated(const void* x, const void* w, void* act, in
     if (!weight_map(w, 2LL * inter, k, tiled != 0, &mw) || !tensor_map_2d(x, m_tok, k, m_tok <= 8 ? 8 : nt, &mx)) return EMS_ERR_LAUNCH;
     Gemm5Params p;
     p.tiled = tiled ? 1 : 0;
+    p.y_f32 = 0;
     p.y = act; p.bias = nullptr; p.status = status_dev; p.m_tok = m_tok; p.n_out = inter;
     p.k_tiles = (k + G5_BK - 1) / G5_BK; p.ksplit = 1; p.dual_offset = inter;
     p.res = nullptr; p.gain = nullptr; p.scaled = nullptr; p.sumsq_out = nullptr;

@@ -181,7 +181,8 @@ class ModelRunner:
         """A second, tiled copy of the weight matrices that decode steps stream, for the
         weight-streaming kernels (`kernels.tile_weight`: they read whole DRAM pages from it and a
         decode step of the 7B shape gets 3 % shorter); the bytes taken.  It costs the weights'
-        size again (embedding and head not counted), so by default (`wanted` None) it is made
+        size again (the embedding not counted unless it is the head too), so by default
+        (`wanted` None) it is made
         only where that is at most a tenth of the device's memory; the cache is sized from
         what is left."""
         if wanted is False or not self._on_cuda or self.dtype != torch.bfloat16:

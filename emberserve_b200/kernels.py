@@ -67,7 +67,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_argmax": [P, P, I, I, P, P],
         "ems_repetition_penalty": [P, I, I, P, P, P, P],
         "ems_sample": [P, I, I, P, P, P, P, P, P, P],
-        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, I, P],
+        "ems_gemm_smallm": [P, P, P, P, I, I, I, I, P, P, P, P, P, I, I, F, I, I, P],
         "ems_gemm_smallm_gated": [P, P, P, I, I, I, P, I, I, F, I, P],
         "ems_gemm_midm": [P, P, P, P, I, I, I, I, I, P],
         "ems_gemm_midm_max_clusters": [I, I],
@@ -424,7 +424,10 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     m, k = x.shape
     n = weight.shape[0]
     assert weight.shape[1] == k and (out is None or out.shape == (m, n))
-    assert x.dtype == weight.dtype == torch.bfloat16 and (out is None or out.dtype == torch.bfloat16)
+    assert x.dtype == weight.dtype == torch.bfloat16
+    # (a float32 `out` takes the sums unrounded: only where one block holds the whole sum)
+    f32 = out is not None and out.dtype == torch.float32
+    assert out is None or out.dtype == torch.bfloat16 or (f32 and ksplit == 1 and norm_behind is None)
     assert bias is None or (bias.dtype == torch.bfloat16 and bias.numel() == n)
     behind = (None, None, None, None)
     if norm_behind is not None:
@@ -441,7 +444,7 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     wptr, tiled = _weight_ptr(weight, twin)
     _check(library().ems_gemm_smallm(
         _ptr(x, "x"), wptr, _ptr(bias, "bias"), _ptr(out, "out"), m, n, k, ksplit,
-        *behind, *_norm_before_args(norm_before, m), tiled, _stream()), "gemm_smallm")
+        *behind, *_norm_before_args(norm_before, m), tiled, 1 if f32 else 0, _stream()), "gemm_smallm")
 
 
 GEMM_MIDM_ROWS = 128

@@ -119,9 +119,9 @@ class Decoder:
         return table
 
     def streamed_weights(self) -> list[torch.Tensor]:
-        """The weight matrices that steps of few rows stream (`Part.streamed_params` of every part),
-        each tensor once."""
-        seen: dict[int, torch.Tensor] = {}
+        """The weight matrices that steps of few rows stream (the head, and `Part.streamed_params` of
+        every part), each tensor once."""
+        seen: dict[int, torch.Tensor] = {id(self.head): self.head}  # (the head of a decode step has few rows too)
         for _, part in self._walk():
             for local in part.streamed_params():
                 w = getattr(part, local)

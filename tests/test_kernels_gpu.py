@@ -579,6 +579,28 @@ def test_gemm_smallm_tcgen05(m, n, k, ksplit, with_bias):
     assert float((out.float() - want).abs().max()) <= 8e-3 * scale + 1e-3, (m, n, k, ksplit)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 152064, 896), (8, 1000, 3584), (16, 2048, 1024), (5, 130, 72)])
+def test_gemm_smallm_float32_output(m, n, k):
+    """The same kernel storing its float32 sums unrounded (the logits of the head), from the
+    row-major weight and from its tiled copy: against a float64 product of the same bfloat16 inputs,
+    to float32 accuracy."""
+    g = torch.Generator(device="cuda").manual_seed(m + n)
+    x = torch.randn(m, k, device=dev(), generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.05).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    outs = []
+    for twin in (None, K().tile_weight(w)):
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device=dev())
+        K().gemm_smallm(x, w, None, out, ksplit=1, twin=twin)
+        torch.cuda.synchronize()
+        K().check_status()
+        assert float((out.double() - want).abs().max()) <= 2e-5 * float(want.abs().max()) + 1e-6
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    with pytest.raises(AssertionError):  # a split K would have to round or to add in another block
+        K().gemm_smallm(x, w, None, outs[0], ksplit=2)
+
+
 @pytest.mark.parametrize("m,n,k,ksplit", [(1, 256, 512, 2), (8, 4608, 3584, 8), (8, 3584, 3584, 5), (16, 1000, 3584, 7),
                                           (17, 384, 18944, 3), (32, 3584, 18944, 5), (5, 130, 200, 2), (64, 256, 1024, 6)])
 def test_gemm_smallm_cluster_split(m, n, k, ksplit):
