@@ -537,6 +537,9 @@ def run_kernel(args) -> dict:
         out = torch.empty(b, nh * d, device=dev, dtype=torch.bfloat16)
         cu = torch.arange(b + 1, device=dev, dtype=torch.int32)
         st = torch.full((b,), ctx - 1, device=dev, dtype=torch.int32)
+        if args.varied_context:  # requests of a serving batch: contexts spread evenly over 64..ctx
+            st = torch.randint(63, ctx, (b,), device=dev, generator=g).to(torch.int32)
+            nbytes = 2 * int((st.long() + 1).sum()) * nkv * d * 2
         rows = torch.arange(b, device=dev, dtype=torch.int32)
         from emberserve_b200.parts.attention import decode_splits
         from emberserve_b200.parts.rope import inv_frequencies
@@ -900,6 +903,8 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true",
                     help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--varied-context", action="store_true",
+                    help="with --kernel decode_attention: contexts spread evenly over 64..--context")
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly")
     ap.add_argument("--no-tiled-weights", action="store_true",
                     help="without the engine's second, tiled copy of the projection weights (by default it is "

@@ -29,7 +29,7 @@
 
 namespace ems {
 
-constexpr int DEC_WARPS = 4;
+constexpr int DEC_WARPS_MIN = 4;
 constexpr int DEC_STAGES_MIN = 3;  // tiles in flight per warp
 constexpr int DEC_TK = 16;  // keys per warp tile
 
@@ -68,7 +68,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // PAGE16: the page size is a multiple of 16, so the 16 keys of a tile (tiles are aligned to
 // multiples of 16 in absolute position) lie in one page, contiguously: one block-table
 // lookup per tile instead of one per key row.
-template <int D, bool PAGE16, int DEC_STAGES>
+template <int D, bool PAGE16, int DEC_STAGES, int DEC_WARPS>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_mma_kernel(const DecodeParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::);
@@ -370,10 +370,10 @@ decode_attention_mma_kernel(const DecodeParams p) {
     }
 }
 
-template <int D, bool PAGE16, int STAGES>
+template <int D, bool PAGE16, int STAGES, int WARPS>
 int launch_decode_mma_staged(const DecodeParams& p, int B, cudaStream_t stream, int device) {
-    constexpr int smem = DEC_WARPS * STAGES * 2 * DEC_TK * D * 2;
-    auto kernel = decode_attention_mma_kernel<D, PAGE16, STAGES>;
+    constexpr int smem = WARPS * STAGES * 2 * DEC_TK * D * 2;
+    auto kernel = decode_attention_mma_kernel<D, PAGE16, STAGES, WARPS>;
     // (dynamic + the kernel's few static bytes pass the 48 KB default at D = 64); once per device
     static int raised_on = -1;
     if (raised_on != device) {
@@ -382,7 +382,7 @@ int launch_decode_mma_staged(const DecodeParams& p, int B, cudaStream_t stream, 
         raised_on = device;
     }
     const dim3 grid((unsigned)p.splits, (unsigned)p.nkv, (unsigned)B);
-    return launch_pdl(kernel, grid, dim3(DEC_WARPS * 32), smem, stream, p);
+    return launch_pdl(kernel, grid, dim3(WARPS * 32), smem, stream, p);
 }
 
 template <int D, bool PAGE16>
@@ -394,15 +394,17 @@ int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t stream) {
         cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         return EMS_ERR_LAUNCH;
     if (p.nkv > 65535 || B > 65535) return EMS_ERR_SHAPE;
-    // A ring of 24 KB per warp lets two blocks live on an SM, one of 12 KB four.  At head size 64
-    // the deeper ring (six tiles in flight per warp) is faster as long as all blocks of the step
-    // are resident at once at two per SM; with more blocks than that the shallow one wins
-    // (256 rows x 2 KV heads, 1024 keys: 26 us against 34; 128 rows: 19 against 16).
+    // Four warps with rings of three tiles are 48 KB at head size 64: four blocks per SM.  While all
+    // blocks of the step are resident at once at TWO per SM, eight warps per block are faster (a
+    // request's keys are walked by twice the warps, so the longest request of the step ends sooner):
+    // 128 rows x 2 KV heads with contexts spread over 64..1536 take 17.8 us against 20.6 (four warps
+    // with six tiles in flight each, the same shared memory), with contexts of 1536 21.3 against
+    // 23.3; with more blocks than that the small blocks win (256 rows, 1024 keys: 26 us against 34).
     if constexpr (D == 64) {
         if ((long long)p.splits * p.nkv * B <= 2LL * sms_of[device])
-            return launch_decode_mma_staged<D, PAGE16, 2 * DEC_STAGES_MIN>(p, B, stream, device);
+            return launch_decode_mma_staged<D, PAGE16, DEC_STAGES_MIN, 2 * DEC_WARPS_MIN>(p, B, stream, device);
     }
-    return launch_decode_mma_staged<D, PAGE16, DEC_STAGES_MIN>(p, B, stream, device);
+    return launch_decode_mma_staged<D, PAGE16, DEC_STAGES_MIN, DEC_WARPS_MIN>(p, B, stream, device);
 }
 
 // Whether the tensor-core decode kernel takes this case; otherwise the generic kernel runs.
