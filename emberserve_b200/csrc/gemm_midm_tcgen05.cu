@@ -10,15 +10,18 @@
 // As in the kernel for few rows (gemm_tcgen05.cu) the WEIGHT matrix is on the 128-row side of
 // tcgen05.mma and the tokens on its N side (32, 64 or 128 columns); weight and activation
 // tiles arrive by TMA (128-byte swizzle, no multicast), the first ring of weight tiles before
-// the wait on the kernel before; the blocks that share K are a thread-block cluster and push
-// their partials into the owners' shared memory (st.async counted by an mbarrier).
+// the wait on the kernel before.  The blocks that share K are a thread-block cluster: each lays
+// its partial sums out in its ring memory, one slab per owner, and one bulk copy per owner
+// (cp.async.bulk from shared memory into the owner's shared memory, counted by the owner's
+// mbarrier) carries a slab into that owner's inbox; the owner adds the slabs in rank order.
 //
 // The reference's engine calls cuBLAS for these products (emberserve/model/qwen2.py:57-58,
 // 77-79); at these row counts the library reaches about half of the memory bandwidth.
 //
 // Every wait on an mbarrier is bounded: if it runs out, the block records a code in the status
-// word shared by the tcgen05 kernels (codes 31..35 here: producer, MMA issuer, epilogue, drain, arrival of the partials), stops issuing work, lets what it has
-// in flight land, frees its tensor memory and returns.
+// word shared by the tcgen05 kernels (codes 31..35 here: producer, MMA issuer, epilogue, drain,
+// arrival of the partials), stops issuing work, lets what it has in flight land, frees its
+// tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
