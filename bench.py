@@ -350,6 +350,9 @@ def run_ours(args) -> dict:
     mixed = mixed_step()
     points["mixed_32dec_512prefill_tok_s"] = mixed["tok_s"]
     points["mixed_32dec_512prefill_ms"] = mixed["ms"]
+    # the reference's own profiled mixed step (docs/results.md:452-459: 39 decode rows beside a
+    # 300-token chunk, 27.25 ms of GPU time on an A100 in fp16), here with contexts of 4096
+    points["mixed_39dec_300prefill_ms"] = mixed_step(39, 300)["ms"]
     if not args.no_extras:
         # free this model before others are built (the child processes need the memory)
         runner.graphs = None
